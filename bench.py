@@ -1,0 +1,494 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse graph-attention hot path (forward + backward) in edges/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--dtype fp32|bf16]
+
+One *step* is one forward+backward of the attention over one synthetic batch; one *edge* is one
+(source, destination) pair evaluated for all 8 heads of the model.
+
+N = 1   The 64K-node micro-benchmark batch (64,001 rows, 526,450 edges, 8 heads x 8, fp32, scalar edge
+        bias).  ``value`` times the C-ABI calls (captured once in a CUDA graph, inputs resident in HBM,
+        four rotating input sets so no step finds its inputs in L2); ``e2e`` goes through the public
+        Python API from pinned host buffers (uploads of q, k, v, bias, dO and the edge list, layout
+        build, forward, backward, download of out, dq, dk, dv, dbias — every step).
+N > 1   One process per GPU under torchrun.  Weak scaling of the Ulysses layer: every rank owns 64,000
+        nodes of an N x 64,000-node graph and all 8 heads outside attention; the step is
+        DistributedAttentionNoMerge forward+backward (all-to-all, attention over all rows with 8/N heads,
+        all-to-all back, and the reverse in backward).  value = N x 526,450 edges / max-over-ranks time.
+
+``--impl reference`` times the reference's own CPU implementation of the path (its PyTorch operation
+sequence restated in oracle/, all host threads) on the same workload, rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HEADS, HEAD_DIM = 8, 8
+NODES_PER_RANK = 64000
+ROTATING_SETS = 4
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
+# summarised in profiles/ (None until a capture exists for the current kernel).
+NCU_TRAFFIC_BYTES = {"fwd_kernel": None, "bwd_dq_kernel": None, "bwd_dkv_kernel": None}
+
+
+def measured_hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def algorithmic_bytes(n_rows, n_edges, heads, head_dim, elem, bias_bytes):
+    """Bytes the op must move: Q read + per-edge K/V/bias gathers + output write, and the matching
+    terms of the two backward passes.  Indices and row statistics are not counted."""
+    r = heads * head_dim * elem
+    fwd = 2 * n_rows * r + n_edges * (2 * r + bias_bytes)
+    dq = 4 * n_rows * r + n_edges * (2 * r + bias_bytes)
+    dkv = 4 * n_rows * r + n_edges * (2 * r + bias_bytes)
+    return {"fwd_kernel": fwd, "bwd_dq_kernel": dq, "bwd_dkv_kernel": dkv}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed regions run."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s, p in zip(sm, power) if p >= 0.5 * max(power)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power)}
+
+
+# ---------------------------------------------------------------------------------------------------
+def make_inputs(n_rows, n_edges, dtype, seed, device):
+    gen = torch.Generator().manual_seed(seed)
+    q, k, v, dout = (torch.randn(n_rows, HEADS, HEAD_DIM, generator=gen) for _ in range(4))
+    bias = torch.randn(n_edges, generator=gen) * 0.1
+    cast = lambda t: t.to(dtype).to(device) if device is not None else t.to(dtype)
+    return cast(q), cast(k), cast(v), cast(dout), (bias.to(device) if device is not None else bias)
+
+
+def cpu_reference_rate(edge_index, n_rows, steps, warmup, budget_s=20.0, seed=1234):
+    """Edges/s of the reference's CPU operation sequence (oracle/sparse_attn_oracle.sparse_attention_ops,
+    float32, autograd backward) with all host threads, on a bounded edge sample of the workload."""
+    from oracle.sparse_attn_oracle import sparse_attention_ops
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    q, k, v, dout, bias = make_inputs(n_rows, edge_index.shape[1], torch.float32, seed, None)
+
+    def one(ei, b):
+        qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
+        t0 = time.perf_counter()
+        out = sparse_attention_ops(qq, kk, vv, ei, b)
+        out.backward(dout)
+        return time.perf_counter() - t0
+
+    n_edges = edge_index.shape[1]
+    probe_edges = min(n_edges, 65536)
+    probe = edge_index[:, torch.randperm(n_edges, generator=torch.Generator().manual_seed(1))[:probe_edges]]
+    one(probe, bias[:probe_edges])
+    t_probe = one(probe, bias[:probe_edges])
+    per_edge = t_probe / probe_edges
+    sample_edges = int(min(n_edges, max(probe_edges, budget_s / max(steps + warmup, 1) / per_edge)))
+    if sample_edges >= n_edges:
+        ei, b, what = edge_index, bias, f"full workload ({n_edges} edges, {n_rows} rows)"
+    else:
+        sel = torch.randperm(n_edges, generator=torch.Generator().manual_seed(2))[:sample_edges]
+        ei, b = edge_index[:, sel].contiguous(), bias[sel].contiguous()
+        what = f"random sample of {sample_edges} of {n_edges} edges over all {n_rows} rows"
+    for _ in range(warmup):
+        one(ei, b)
+    times = [one(ei, b) for _ in range(steps)]
+    mean = sum(times) / len(times)
+    return {"value": ei.shape[1] / mean, "unit": "edges/s", "cores": cores, "kind": "port",
+            "sample": f"{what}; {warmup} warm-up + {steps} timed fwd+bwd, mean {mean * 1e3:.1f} ms"}, mean
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    from torchgt_b200.synthetic import benchmark_64k
+    edge_index, n_rows = benchmark_64k(ranks=args.gpus)
+    base, mean = cpu_reference_rate(edge_index, n_rows, args.steps, max(args.warmup, 1), budget_s=150.0)
+    line = {
+        "impl": "reference", "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": base["value"],
+        "unit": "edges/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus, n_rows, edge_index.shape[1], "fp32") | {"device": "host CPU"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus, n_rows, n_edges, dtype):
+    return {"workload": "sparse-attention op microbench: 64,000 nodes per GPU + global node, 8 clusters of 8,000 "
+                        "per GPU, 17.5% of edges crossing clusters, scalar edge bias, fwd+bwd",
+            "rows": n_rows, "edges": n_edges, "heads": HEADS, "head_dim": HEAD_DIM, "io_dtype": dtype,
+            "parallelism": "single GPU" if n_gpus == 1 else f"Ulysses sequence parallel x{n_gpus} (heads sharded)",
+            "l2": f"{ROTATING_SETS} rotating input sets, footprint > 126 MB L2, no explicit flush"}
+
+
+# ---------------------------------------------------------------------------------------------------
+class OpBuffers:
+    """Device tensors of one input set for direct C-ABI calls (nothing allocated inside the timing)."""
+
+    def __init__(self, graph, dtype, seed, with_bias=True):
+        from torchgt_b200 import _cabi
+        dev = graph.device
+        n, e = graph.n_rows, graph.n_edges
+        self.q, self.k, self.v, self.dout, bias = make_inputs(n, e, dtype, seed, dev)
+        self.bias = bias if with_bias else None
+        self.out = torch.empty_like(self.q)
+        self.z = torch.empty(n, HEADS, dtype=torch.float32, device=dev)
+        self.dq, self.dk, self.dv = (torch.empty_like(self.q) for _ in range(3))
+        self.dbias = torch.empty_like(bias) if with_bias else None
+        lib = _cabi.load()
+        nb = ctypes.c_size_t()
+        _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), graph.by_src.byref(), HEADS, HEAD_DIM,
+                                                      1, ctypes.byref(nb)))
+        nf = ctypes.c_size_t()
+        _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), None, HEADS, HEAD_DIM, 0,
+                                                      ctypes.byref(nf)))
+        self.scratch_f = torch.empty(max(nf.value, 16), dtype=torch.uint8, device=dev)
+        self.scratch_b = torch.empty(max(nb.value, 16), dtype=torch.uint8, device=dev)
+        self.code = _cabi.TGT_F32 if dtype == torch.float32 else _cabi.TGT_BF16
+        self.graph = graph
+
+    def fwd(self, stream):
+        from torchgt_b200 import _cabi
+        lib = _cabi.load()
+        p = lambda t: None if t is None else t.data_ptr()
+        _cabi.check(lib.tgt_sparse_attn_fwd(p(self.q), p(self.k), p(self.v), p(self.bias), 1 if self.bias is not None else 0,
+                                            self.graph.by_dst.byref(), p(self.out), p(self.z), HEADS, HEAD_DIM,
+                                            self.code, p(self.scratch_f), self.scratch_f.numel(), stream))
+
+    def bwd(self, stream, passes):
+        from torchgt_b200 import _cabi
+        lib = _cabi.load()
+        p = lambda t: None if t is None else t.data_ptr()
+        _cabi.check(lib.tgt_sparse_attn_bwd_passes(
+            p(self.dout), p(self.q), p(self.k), p(self.v), p(self.bias), 1 if self.bias is not None else 0,
+            p(self.out), p(self.z), self.graph.by_dst.byref(), self.graph.by_src.byref(), p(self.dq), p(self.dk),
+            p(self.dv), p(self.dbias), HEADS, HEAD_DIM, self.code, p(self.scratch_b), self.scratch_b.numel(),
+            stream, passes))
+
+
+def capture(fn):
+    """Capture the launches ``fn(stream)`` makes into a CUDA graph."""
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn(side.cuda_stream)      # warm-up outside capture (module load, first-launch work)
+    side.synchronize()
+    with torch.cuda.graph(g, stream=side):
+        fn(torch.cuda.current_stream().cuda_stream)
+    return g
+
+
+def kernels_per_step(graph):
+    per = lambda lay: 1 + (2 if lay.n_chunks > 0 else 0)
+    return 2 * per(graph.by_dst) + per(graph.by_src)
+
+
+def run_single_gpu(args, dtype):
+    from torchgt_b200 import SparseGraph, sparse_graph_attention
+    from torchgt_b200.synthetic import benchmark_64k
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    edge_index, n_rows = benchmark_64k()
+    n_edges = edge_index.shape[1]
+    graph = SparseGraph(edge_index.to(dev), n_rows)
+    graph.by_src  # build both layouts before timing
+    sets = [OpBuffers(graph, dtype, 1234 + i) for i in range(ROTATING_SETS)]
+    step_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 3))) for b in sets]
+    phase_graphs = [[capture(lambda s, b=b: b.fwd(s)), capture(lambda s, b=b: b.bwd(s, 1)),
+                     capture(lambda s, b=b: b.bwd(s, 2))] for b in sets]
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(0)
+    # ---- device-resident throughput: K back-to-back steps over rotating input sets -------------------
+    for i in range(args.warmup):
+        step_graphs[i % ROTATING_SETS].replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        step_graphs[i % ROTATING_SETS].replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms_per_step = start.elapsed_time(stop) / args.steps
+
+    # ---- per-phase durations (each phase its own graph, events around every replay) ------------------
+    names = ["fwd_kernel", "bwd_dq_kernel", "bwd_dkv_kernel"]
+    phase_steps = min(args.steps, 200)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(phase_steps)]
+    for i in range(phase_steps):
+        for j in range(3):
+            evs[i][j].record()
+            phase_graphs[i % ROTATING_SETS][j].replay()
+        evs[i][3].record()
+    torch.cuda.synchronize()
+    phase_ms = {n: statistics.mean(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(phase_steps))
+                for j, n in enumerate(names)}
+
+    # ---- end to end through the public API from pinned host memory -----------------------------------
+    hq, hk, hv, hdout, hbias = (t.pin_memory() for t in make_inputs(n_rows, n_edges, dtype, 99, None))
+    hei = edge_index.pin_memory()
+    host_out = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+    host_dbias = torch.empty_like(hbias).pin_memory()
+
+    def e2e_step(resident_graph=None):
+        q, k, v = (t.to(dev, non_blocking=True).requires_grad_() for t in (hq, hk, hv))
+        bias = hbias.to(dev, non_blocking=True).requires_grad_()
+        dout = hdout.to(dev, non_blocking=True)
+        g = resident_graph if resident_graph is not None else SparseGraph(hei.to(dev, non_blocking=True), n_rows)
+        out = sparse_graph_attention(q, k, v, g, bias)
+        out.backward(dout)
+        for dst, src in zip(host_out, (out.detach(), q.grad, k.grad, v.grad)):
+            dst.copy_(src, non_blocking=True)
+        host_dbias.copy_(bias.grad, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_steps = max(3, min(args.steps, 30))
+    results = {}
+    for label, g in (("full", None), ("graph_resident", graph)):
+        for _ in range(3):
+            e2e_step(g)
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step(g)
+        results[label] = (time.perf_counter() - t0) / e2e_steps
+    clocks = sampler.stop()
+
+    elem = 4 if dtype == torch.float32 else 2
+    h2d = 4 * n_rows * HEADS * HEAD_DIM * elem + n_edges * 4 + 2 * n_edges * 8
+    d2h = 4 * n_rows * HEADS * HEAD_DIM * elem + n_edges * 4
+    peak, peak_kind = measured_hbm_peak()
+    bytes_ = algorithmic_bytes(n_rows, n_edges, HEADS, HEAD_DIM, elem, 4)
+    dominant = max(names, key=lambda n: phase_ms[n])
+    achieved = bytes_[dominant] / (phase_ms[dominant] * 1e-3) / 1e9
+    step_bytes = sum(bytes_.values())
+    step_achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    cpu, _ = cpu_reference_rate(edge_index, n_rows, steps=5, warmup=2, budget_s=20.0)
+    line = {
+        "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": n_edges / (ms_per_step * 1e-3),
+        "unit": "edges/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32" if dtype == torch.float32 else "bf16 i/o, f32 math", "data": "synthetic",
+        "config": workload_config(1, n_rows, n_edges, args.dtype),
+        "clocks": clocks,
+        "e2e": {"value": n_edges / results["full"], "unit": "edges/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": results["full"] * 1e3,
+                "includes": "pinned-host uploads of q,k,v,bias,dO and the int64 edge list, both edge layouts "
+                            "built, forward, backward, downloads of out,dq,dk,dv,dbias, every step",
+                "graph_resident_value": n_edges / results["graph_resident"],
+                "graph_resident_ms_per_step": results["graph_resident"] * 1e3},
+        "gpu_launches": kernels_per_step(graph) * args.steps,
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                     "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+                     "algorithmic_bytes_per_launch": bytes_[dominant],
+                     "phases_ms": phase_ms,
+                     "phases_frac": {n: bytes_[n] / (phase_ms[n] * 1e-3) / 1e9 / peak for n in names},
+                     "step": {"algorithmic_bytes": step_bytes, "achieved": step_achieved,
+                              "frac": step_achieved / peak, "frac_of_nominal_8TBs": step_achieved / 8000.0}},
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+def run_multi_gpu(args, dtype, rank, world):
+    import torch.distributed as dist
+    from torchgt_b200 import CoreAttention, SparseGraph
+    from torchgt_b200.gt_sp import initialize as sp
+    from torchgt_b200.gt_sp.layer import DistributedAttentionNoMerge
+    from torchgt_b200.gt_sp.utils import adjust_edge_index_nomerge
+    from torchgt_b200.synthetic import benchmark_64k
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    sp.set_global_token_num(1)
+    sp.initialize_sequence_parallel(NODES_PER_RANK * world, 1, 1, world)
+    L = NODES_PER_RANK
+    sp.set_global_token_indices(list(range(0, world * (L + 1), L + 1)))
+    edge_index, _ = benchmark_64k(ranks=world)                       # ids 0..S, same on every rank
+    edge_index = adjust_edge_index_nomerge(edge_index, L)
+    n_rows, n_edges = world * (L + 1), edge_index.shape[1]
+    graph = SparseGraph(edge_index.to(dev), n_rows)
+    graph.by_src
+    core = CoreAttention(HEADS * HEAD_DIM, 0.0, HEADS, 1)
+    layer = DistributedAttentionNoMerge(core, sp.get_sequence_parallel_group()).train()
+    sets = []
+    for i in range(ROTATING_SETS):
+        gen = torch.Generator().manual_seed(4321 + 17 * rank + i)
+        q, k, v = (torch.randn(1, L + 1, HEADS, HEAD_DIM, generator=gen).to(dtype).to(dev).requires_grad_()
+                   for _ in range(3))
+        dout = torch.randn(1, L + 1, HEADS * HEAD_DIM, generator=gen).to(dtype).to(dev)
+        sets.append((q, k, v, dout))
+
+    def step(i):
+        q, k, v, dout = sets[i % ROTATING_SETS]
+        out = layer(q, k, v, None, graph, "sparse")
+        out.backward(dout)
+        q.grad = k.grad = v.grad = None
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        step(i)
+    stop.record()
+    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item())
+
+    # end to end: this rank's q, k, v, dO come from pinned host memory, the result goes back
+    host = [t.detach().cpu().pin_memory() for t in sets[0]]
+    host_out = [torch.empty_like(host[0].view(1, L + 1, -1)).pin_memory()] + \
+               [torch.empty_like(host[0]).pin_memory() for _ in range(3)]
+
+    def e2e_step():
+        q, k, v = (t.to(dev, non_blocking=True).requires_grad_() for t in host[:3])
+        dout = host[3].to(dev, non_blocking=True)
+        out = layer(q, k, v, None, graph, "sparse")
+        out.backward(dout)
+        for dst, src in zip(host_out, (out.detach(), q.grad, k.grad, v.grad)):
+            dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_steps = max(3, min(args.steps, 30))
+    for _ in range(3):
+        e2e_step()
+    dist.barrier(); torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    dist.barrier()
+    e2e_s = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=dev)
+    dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if sampler else None
+
+    if rank == 0:
+        elem = 4 if dtype == torch.float32 else 2
+        heads_local = HEADS // world
+        peak, peak_kind = measured_hbm_peak()
+        bytes_ = algorithmic_bytes(n_rows, n_edges, heads_local, HEAD_DIM, elem, 0)
+        step_bytes = sum(bytes_.values())
+        per_rank_io = 4 * (L + 1) * HEADS * HEAD_DIM * elem
+        # kernels: 3 attention phases (+ hub kernels), pack/unpack around 4 exchanges, 2 global-row kernels
+        launches = kernels_per_step(graph) + 8 + 2
+        line = {
+            "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": n_edges / (ms_per_step * 1e-3),
+            "unit": "edges/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32" if dtype == torch.float32 else "bf16 i/o, f32 math", "data": "synthetic",
+            "config": workload_config(world, n_rows, n_edges, args.dtype) |
+                      {"step": "DistributedAttentionNoMerge fwd+bwd: all-to-all(q,k,v) -> attention with "
+                               f"{heads_local} head(s) over all rows -> all-to-all(out), reversed in backward",
+                       "bias": "none (the models pass attn_bias=None on this path)"},
+            "clocks": clocks,
+            "e2e": {"value": n_edges / float(e2e_s.item()), "unit": "edges/s", "h2d_bytes_per_step": per_rank_io,
+                    "d2h_bytes_per_step": per_rank_io, "ms_per_step": float(e2e_s.item()) * 1e3,
+                    "includes": "per rank: pinned-host uploads of q,k,v,dO, layer forward+backward with both "
+                                "exchanges, downloads of out,dq,dk,dv; edge layouts resident"},
+            "gpu_launches": launches * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "whole step per GPU (attention phases + exchange)",
+                         "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
+                         "traffic": None, "algorithmic_bytes_per_launch": step_bytes},
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--dtype", choices=["fp32", "bf16"], default="fp32")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    dtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (torchgt_b200 has no CPU path); "
+                         "use --impl reference for the CPU baseline")
+    if world > 1:
+        if world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+        run_multi_gpu(args, dtype, rank, world)
+    else:
+        if args.gpus != 1:
+            raise SystemExit("for --gpus N > 1 launch with torch.distributed.run (one process per GPU)")
+        run_single_gpu(args, dtype)
+
+
+if __name__ == "__main__":
+    main()

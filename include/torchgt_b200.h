@@ -1,0 +1,215 @@
+/*
+ * torchgt_b200 — C ABI of the sparse graph-attention hot path for NVIDIA B200 (sm_100a).
+ *
+ * One shared library (libtorchgt_b200.so) exports the functions below.  Signatures use only plain
+ * pointers and sizes.  Every pointer named "device" must point into CUDA device memory of the
+ * current device, be 16-byte aligned and densely packed.  Nothing here allocates device memory
+ * unless the comment on the entry point says otherwise: scratch is passed in by the caller after a
+ * size query.  Kernels are enqueued on the `stream` argument (a cudaStream_t passed as void*;
+ * NULL = legacy default stream) and the calls do not synchronise unless stated.
+ *
+ * Every function returns TGT_OK (0) or a TGT_ERR_* code; tgt_last_error() gives the message of the
+ * last failure on the calling thread.  Argument checks run before any launch.
+ *
+ * The reference (zxmeng98/torchgt) is pure PyTorch and has no FFI; each entry point below cites the
+ * reference Python code it replaces (path inside that project : lines).
+ */
+#ifndef TORCHGT_B200_H
+#define TORCHGT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TGT_API __attribute__((visibility("default")))
+#else
+#define TGT_API
+#endif
+
+#define TGT_OK 0
+#define TGT_ERR_INVALID 1      /* null / misaligned pointer, negative size, inconsistent layout   */
+#define TGT_ERR_CUDA 2         /* a CUDA runtime call or a launch failed                          */
+#define TGT_ERR_UNSUPPORTED 3  /* head_dim / head count / dtype combination not built             */
+#define TGT_ERR_WORKSPACE 4    /* scratch or workspace smaller than the size query says           */
+#define TGT_ERR_INDEX_RANGE 5  /* edge_index holds a node id outside [0, n_rows)                  */
+
+#define TGT_F32 0
+#define TGT_BF16 1
+
+/* bias_heads values: per-edge additive score bias given in ORIGINAL edge order (fp32).           */
+#define TGT_BIAS_NONE 0 /* no bias                                                                */
+/* 1      -> bias[E]     one value per edge shared by all heads                                   */
+/* heads  -> bias[E, H]  one value per edge and head                                              */
+
+/*
+ * Edges grouped by one endpoint ("segment layout").  Built by tgt_edge_layout_build.
+ *   group_by = 1 : grouped by destination (edge_index row 1) — CSR used by forward and by the
+ *                  dQ pass; `other` holds the source of every edge.
+ *   group_by = 0 : grouped by source (edge_index row 0) — CSC used by the dK/dV pass; `other`
+ *                  holds the destination.
+ * Definition (bit-exact contract): perm = stable argsort of the grouping endpoint,
+ * other = other_endpoint[perm], ptr = exclusive prefix sum of bincount(grouping endpoint, n_rows).
+ * Rows with more than `chunk_edges` edges ("hub rows", e.g. Graphormer's global token) are listed
+ * in hub_row[n_hubs] in ascending row order and cut into chunks of chunk_edges consecutive edges:
+ * chunks hub_chunk_ptr[i] .. hub_chunk_ptr[i+1]-1 belong to hub_row[i]; chunk c covers edges
+ * chunk_begin[c] .. min(chunk_begin[c]+chunk_edges, ptr[chunk_row[c]+1]) - 1.
+ */
+typedef struct tgt_layout {
+  int64_t n_rows;
+  int64_t n_edges;
+  const int32_t* ptr;   /* device [n_rows + 1] */
+  const int32_t* other; /* device [n_edges]    */
+  const int32_t* perm;  /* device [n_edges]    */
+  int32_t chunk_edges;
+  int32_t n_chunks;
+  int32_t n_hubs;
+  int32_t reserved;
+  const int32_t* chunk_row;     /* device [n_chunks]   */
+  const int32_t* chunk_begin;   /* device [n_chunks]   */
+  const int32_t* hub_row;       /* device [n_hubs]     */
+  const int32_t* hub_chunk_ptr; /* device [n_hubs + 1] */
+} tgt_layout;
+
+/* Library version (major * 100 + minor). */
+TGT_API int tgt_version(void);
+
+/* Message of the last error returned on this thread ("" if none).  Never NULL. */
+TGT_API const char* tgt_last_error(void);
+
+/*
+ * Capacity query for tgt_edge_layout_build: upper bounds on the number of chunks and hub rows for
+ * any graph with n_edges edges, and the bytes of device workspace the build needs.
+ * Replaces nothing in the reference (the reference keeps edges as an unsorted COO list).
+ */
+TGT_API int tgt_edge_layout_sizes(int64_t n_rows, int64_t n_edges, int32_t chunk_edges,
+                          int64_t* max_chunks, int64_t* max_hubs, size_t* workspace_bytes);
+
+/*
+ * Build one segment layout from the COO edge list the reference's batch packing produces
+ * (gt_sp/utils.py:34-58 fix_edge_index / adjust_edge_index_nomerge, gt_sp/utils.py:409-520
+ * get_batch_reorder_blockize, data/collator_sp_sparse.py:126-133 flatten_edge_index_nopad):
+ * edge_index is a device int64 [2, n_edges] array, row 0 = source (K/V row), row 1 = destination
+ * (Q / output row), exactly as consumed by CoreAttention.sparse_attention (attn_module.py:146-147).
+ * Output arrays are device buffers sized by tgt_edge_layout_sizes (ptr: n_rows+1, other/perm:
+ * n_edges, chunk_row/chunk_begin: max_chunks, hub_row: max_hubs, hub_chunk_ptr: max_hubs+1).
+ * counts_host[0] = n_chunks, counts_host[1] = n_hubs on return.
+ * This call SYNCHRONISES the stream once (it is made once per batch, not per layer) and returns
+ * TGT_ERR_INDEX_RANGE if any node id is outside [0, n_rows).
+ */
+TGT_API int tgt_edge_layout_build(const int64_t* edge_index, int64_t n_edges, int64_t n_rows, int group_by,
+                          int32_t chunk_edges, int32_t* ptr, int32_t* other, int32_t* perm,
+                          int32_t* chunk_row, int32_t* chunk_begin, int32_t* hub_row,
+                          int32_t* hub_chunk_ptr, int64_t* counts_host, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/*
+ * Bytes of scratch tgt_sparse_attn_fwd (phase 0) / tgt_sparse_attn_bwd (phase 1) need for these
+ * layouts.  by_src may be NULL for phase 0.
+ */
+TGT_API int tgt_sparse_attn_scratch_bytes(const tgt_layout* by_dst, const tgt_layout* by_src, int heads,
+                                  int head_dim, int phase, size_t* bytes);
+
+/*
+ * Forward of the topology-aware sparse attention: for every edge e = (s -> d) and head h
+ *   raw = sum_j K[s,h,j] * Q[d,h,j] / sqrt(head_dim);  t = clamp(raw, -5, 5) + bias[e(,h)]
+ *   w = exp(t);  U[d,h,:] += w * V[s,h,:];  Z[d,h] += w;      out = U / (Z + 1e-6)
+ * Replaces CoreAttention.sparse_attention (attn_module.py:133-189) and the sparse_attention_bias
+ * copies (models/graphormer_dist_node_level.py:69-127, models/gt_dist_node_level.py:83-142,
+ * models/graphormer_dist_graph_level.py:238-292, models/gt_dist_graph_level.py:83-137) including
+ * the two torch_scatter.scatter(reduce='add') calls.  No per-edge tensor is materialised.
+ * q, k, v, out: device [n_rows, heads, head_dim] of `dtype`; z: device fp32 [n_rows, heads]
+ * (saved for backward); bias: device fp32 in ORIGINAL edge order or NULL (see bias_heads).
+ * Rows without in-edges produce exactly 0.  Deterministic (no atomics).
+ */
+TGT_API int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, const float* bias,
+                        int bias_heads, const tgt_layout* by_dst, void* out, float* z, int heads,
+                        int head_dim, int dtype, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Backward of the same op (the reference has no hand-written backward; this replaces the autograd
+ * graph of attn_module.py:141-187: three index_put_(accumulate=True), two gathers and the
+ * elementwise chain).  With G = dout, inv = 1/(Z+1e-6):
+ *   dw = (G_d . V_s - G_d . O_d) * inv_d;  dV_s += w * inv_d * G_d;  dt = dw * w  (= dbias)
+ *   da = dt * [-5 <= raw <= 5];  dQ_d += da * K_s / sqrt(D);  dK_s += da * Q_d / sqrt(D)
+ * Pass A walks by_dst (dQ, dbias, per-row statistics), pass B walks by_src (dK, dV); scores are
+ * recomputed, nothing per-edge is read from forward.  dbias is device fp32 in ORIGINAL edge order
+ * with the shape bias has, or NULL when not wanted.  Deterministic (no atomics).
+ */
+TGT_API int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
+                        const float* bias, int bias_heads, const void* out, const float* z,
+                        const tgt_layout* by_dst, const tgt_layout* by_src, void* dq, void* dk,
+                        void* dv, float* dbias, int heads, int head_dim, int dtype, void* scratch,
+                        size_t scratch_bytes, void* stream);
+
+/*
+ * The same backward with the two passes selectable: passes = 1 runs pass A only (dQ, dbias, row
+ * statistics into `scratch`), 2 runs pass B only (dK, dV; needs the statistics a pass A left in the
+ * same scratch for the same inputs), 3 runs both (= tgt_sparse_attn_bwd).  Lets a caller time or
+ * overlap the passes separately; replaces the same reference code as tgt_sparse_attn_bwd.
+ */
+TGT_API int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const void* k, const void* v,
+                                       const float* bias, int bias_heads, const void* out,
+                                       const float* z, const tgt_layout* by_dst,
+                                       const tgt_layout* by_src, void* dq, void* dk, void* dv,
+                                       float* dbias, int heads, int head_dim, int dtype,
+                                       void* scratch, size_t scratch_bytes, void* stream, int passes);
+
+/*
+ * Ulysses head<->sequence exchange: local re-layout kernels around ONE all-to-all.
+ *
+ * The reference's _SeqAllToAll (gt_sp/layer.py:30-49, gt_sp/gt_layer.py:30-49) does
+ * tensor_split(scatter_idx) + contiguous() per chunk, a list all_to_all, and cat(gather_idx)
+ * .contiguous(), once per tensor (q, k, v: gt_sp/layer.py:516-518; context: :545).  Here up to three
+ * tensors share one peer-major staging buffer
+ *     stage[world][n_tensors][batch][seq_local][width_local]
+ * (chunk `peer` is what is sent to / received from that rank), so one collective moves them all.
+ * width_local = (heads / world) * head_dim elements; `dtype` only fixes the element size.
+ *
+ *   tgt_a2a_pack_heads  : x_t [batch, seq_local, world*width_local]  -> stage   (scatter_idx = 2)
+ *   tgt_a2a_unpack_seq  : stage -> y_t [batch, world*seq_local, width_local]    (gather_idx  = 1)
+ *   tgt_a2a_pack_seq    : x_t [batch, world*seq_local, width_local]  -> stage   (scatter_idx = 1)
+ *   tgt_a2a_unpack_heads: stage -> y_t [batch, seq_local, world*width_local]    (gather_idx  = 2)
+ *
+ * pack_heads + unpack_seq is the q/k/v direction (and the backward of the context direction);
+ * pack_seq + unpack_heads is the context direction (and the backward of the q/k/v direction).
+ * Unused tensor slots (t >= n_tensors) must be NULL.
+ */
+TGT_API int tgt_a2a_pack_heads(const void* x0, const void* x1, const void* x2, int n_tensors, void* stage,
+                       int64_t batch, int64_t seq_local, int64_t width_local, int world, int dtype,
+                       void* stream);
+TGT_API int tgt_a2a_unpack_seq(const void* stage, int n_tensors, void* y0, void* y1, void* y2,
+                       int64_t batch, int64_t seq_local, int64_t width_local, int world, int dtype,
+                       void* stream);
+TGT_API int tgt_a2a_pack_seq(const void* x0, const void* x1, const void* x2, int n_tensors, void* stage,
+                     int64_t batch, int64_t seq_local, int64_t width_local, int world, int dtype,
+                     void* stream);
+TGT_API int tgt_a2a_unpack_heads(const void* stage, int n_tensors, void* y0, void* y1, void* y2,
+                         int64_t batch, int64_t seq_local, int64_t width_local, int world,
+                         int dtype, void* stream);
+
+/*
+ * copy_global_token0 (gt_sp/utils.py:817-838): x [batch, seq, width]; every row listed in
+ * global_rows (device int32 [n_global], e.g. r*(L+1) for r = 0..P-1) is overwritten in place with
+ * row 0 of the same batch entry.  The reference builds and uploads the index tensor on every call;
+ * here it stays on the device.
+ */
+TGT_API int tgt_global_rows_broadcast(void* x, const int32_t* global_rows, int n_global, int64_t batch,
+                              int64_t seq, int64_t width, int dtype, void* stream);
+
+/*
+ * Backward of tgt_global_rows_broadcast (autograd of the in-place index assignment at
+ * gt_sp/utils.py:836): dx[b, 0, :] = sum over listed rows of dx[b, row, :] (summed in list order,
+ * fp32 accumulation; plus dx[b, 0, :] itself when row 0 is not listed), then every listed row
+ * other than 0 is set to zero.
+ */
+TGT_API int tgt_global_rows_reduce(void* dx, const int32_t* global_rows, int n_global, int64_t batch,
+                           int64_t seq, int64_t width, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TORCHGT_B200_H */

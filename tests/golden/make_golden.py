@@ -1,0 +1,218 @@
+"""Generate the golden vectors under tests/golden/ by RUNNING THE REFERENCE ITSELF on CPU.
+
+Run from the repository root on a machine that has the reference checkout:
+
+    python tests/golden/make_golden.py --reference /path/to/torchgt
+
+The reference imports torch_scatter / torch_sparse / torch_geometric / dgl, none of which are needed
+by the code paths exercised here; they are replaced by minimal stand-ins
+(``torch_scatter.scatter(src, index, dim=0, out=out, reduce='add')`` -> ``out.index_add_(0, index,
+src)``, the documented semantics of torch-scatter 2.1.1).  gloo has no list all-to-all, so inside the
+worker processes ``torch.distributed.all_to_all`` is routed through ``all_to_all_single``.
+
+Outputs (all small .npz files, committed):
+  attn_*.npz     CoreAttention.sparse_attention_bias forward + autograd gradients
+  edges.npz      fix_edge_index / adjust_edge_index_nomerge / flatten_edge_index_nopad known answers
+  ulysses_P*.npz _SeqAllToAll both directions and the DistributedAttentionNoMerge layer, P ranks
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+from pathlib import Path
+
+import numpy as np
+import torch
+
+OUT_DIR = Path(__file__).resolve().parent
+
+
+def install_shims():
+    def scatter(src, index, dim=0, out=None, reduce="add"):
+        assert dim == 0 and reduce == "add" and out is not None
+        out.index_add_(0, index.to(torch.long), src)
+        return out
+
+    ts = types.ModuleType("torch_scatter"); ts.scatter = scatter
+    tsp = types.ModuleType("torch_sparse"); tsp.SparseTensor = object; tsp.matmul = None
+    tg = types.ModuleType("torch_geometric"); tgu = types.ModuleType("torch_geometric.utils")
+    for name in ("degree", "to_undirected", "remove_self_loops", "add_self_loops", "subgraph"):
+        setattr(tgu, name, None)
+    tg.utils = tgu
+    dgl = types.ModuleType("dgl")
+    sys.modules.update({"torch_scatter": ts, "torch_sparse": tsp, "torch_geometric": tg,
+                        "torch_geometric.utils": tgu, "dgl": dgl})
+
+
+def random_graph(gen, n, avg_in_degree, hub=True, duplicates=False):
+    """Directed edges [2, E]: random in-edges + self loops (+ a hub row 0 connected to everyone)."""
+    e = int(n * avg_in_degree)
+    src = torch.randint(0, n, (e,), generator=gen)
+    dst = torch.randint(0, n, (e,), generator=gen)
+    parts = [torch.stack([src, dst])]
+    loops = torch.arange(n)
+    parts.append(torch.stack([loops, loops]))
+    if hub:
+        others = torch.arange(1, n)
+        zeros = torch.zeros(n - 1, dtype=torch.long)
+        parts += [torch.stack([others, zeros]), torch.stack([zeros, others])]
+    ei = torch.cat(parts, dim=1)
+    if not duplicates:
+        ei = torch.unique(ei, dim=1)
+    ei = ei[:, torch.randperm(ei.shape[1], generator=gen)]
+    # leave some rows without in-edges
+    keep = ei[1] % 7 != 3
+    return ei[:, keep].contiguous()
+
+
+def make_attention_cases():
+    from models.graphormer_dist_graph_level import CoreAttention as GraphLevelCore  # (k, q, v, ...)
+    from models.gt_dist_node_level import CoreAttention as GtNodeCore               # (q, k, v, ...)
+
+    cases = [
+        # name, N, H, D, avg_deg, input scale, bias, duplicates
+        ("small_nobias", 97, 8, 8, 4.0, 1.0, None, True),
+        ("clamped_nobias", 64, 4, 16, 6.0, 3.0, None, True),
+        ("dense_bias", 80, 8, 8, 5.0, 1.5, "dense", False),
+        ("one_head", 50, 1, 8, 3.0, 2.0, "dense", False),
+        ("wide_head", 40, 2, 32, 3.0, 1.0, None, True),
+    ]
+    for idx, (name, n, h, d, deg, scale, bias_kind, dup) in enumerate(cases):
+        gen = torch.Generator().manual_seed(1000 + idx)
+        ei = random_graph(gen, n, deg, hub=True, duplicates=dup)
+        q = (torch.randn(1, n, h, d, generator=gen) * scale).requires_grad_()
+        k = (torch.randn(1, n, h, d, generator=gen) * scale).requires_grad_()
+        v = torch.randn(1, n, h, d, generator=gen).requires_grad_()
+        dout = torch.randn(n, h, d, generator=gen)
+        attn_bias = None
+        if bias_kind == "dense":
+            attn_bias = (torch.randn(1, h, n, n, generator=gen) * 0.5).requires_grad_()
+        core = GraphLevelCore(h * d, 0.0, h)
+        core.num_attention_heads_per_partition = h
+        out = core.sparse_attention_bias(k, q, v, ei, attn_bias)       # [N, H, D]
+        (out * dout).sum().backward()
+        rec = dict(q=q.detach()[0].numpy(), k=k.detach()[0].numpy(), v=v.detach()[0].numpy(),
+                   edge_index=ei.numpy(), dout=dout.numpy(), out=out.detach().numpy(),
+                   dq=q.grad[0].numpy(), dk=k.grad[0].numpy(), dv=v.grad[0].numpy())
+        if attn_bias is not None:
+            rec["attn_bias"] = attn_bias.detach().numpy()
+            rec["dattn_bias"] = attn_bias.grad.numpy()
+        else:
+            # same inputs through the GT node-level copy (argument order q, k, v): must agree exactly
+            core2 = GtNodeCore(h * d, 0.0, h)
+            core2.num_attention_heads_per_partition = h
+            core2.train()
+            out2 = core2.sparse_attention_bias(q.detach(), k.detach(), v.detach(), ei, None)
+            assert torch.equal(out2, out.detach()), name
+        np.savez_compressed(OUT_DIR / f"attn_{name}.npz", **rec)
+        print("wrote", f"attn_{name}.npz", "N", n, "E", ei.shape[1])
+
+
+def make_edge_cases():
+    from data.collator_sp_sparse import (adjust_edge_index_nomerge, fix_edge_index,
+                                         flatten_edge_index_nopad)
+    import gt_sp.utils as ref_utils
+    rec = {}
+    ring = torch.tensor([[0, 1, 2, 3], [1, 2, 3, 0]])
+    fixed = fix_edge_index(ring, 4)
+    assert torch.equal(fixed, ref_utils.fix_edge_index(ring, 4))
+    adj = adjust_edge_index_nomerge(fixed, 2)
+    assert torch.equal(adj, ref_utils.adjust_edge_index_nomerge(fixed, 2))
+    rec["ring"], rec["ring_fixed"], rec["ring_adjusted_L2"] = ring.numpy(), fixed.numpy(), adj.numpy()
+    rec["ring_flat_6"] = flatten_edge_index_nopad([adj, adj[:, :3]], 6).numpy()
+    gen = torch.Generator().manual_seed(7)
+    for i, (n, e, sub) in enumerate([(12, 30, 3), (64, 300, 16), (1000, 5000, 125), (4096, 9000, 512)]):
+        x = torch.randint(0, n, (2, e), generator=gen)
+        fixed = fix_edge_index(x, n)
+        adj = adjust_edge_index_nomerge(fixed, sub)
+        rec[f"rand{i}_in"], rec[f"rand{i}_n"], rec[f"rand{i}_sub"] = x.numpy(), np.int64(n), np.int64(sub)
+        rec[f"rand{i}_fixed"], rec[f"rand{i}_adjusted"] = fixed.numpy(), adj.numpy()
+    g0 = torch.randint(0, 9, (2, 20), generator=gen)
+    g1 = torch.randint(0, 9, (2, 11), generator=gen)
+    g2 = torch.randint(0, 9, (2, 17), generator=gen)
+    rec["flat_in0"], rec["flat_in1"], rec["flat_in2"] = g0.numpy(), g1.numpy(), g2.numpy()
+    rec["flat_out_10"] = flatten_edge_index_nopad([g0, g1, g2], 10).numpy()
+    np.savez_compressed(OUT_DIR / "edges.npz", **rec)
+    print("wrote edges.npz")
+
+
+def _ulysses_worker(rank, world, ref_path, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ref_path)
+    install_shims()
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def all_to_all_via_single(output_list, input_list, group=None):
+        out = torch.empty_like(torch.stack(input_list))
+        dist.all_to_all_single(out, torch.stack(input_list).contiguous(), group=group)
+        for o, chunk in zip(output_list, out):
+            o.copy_(chunk)
+    dist.all_to_all = all_to_all_via_single
+    torch.distributed.all_to_all = all_to_all_via_single
+
+    import gt_sp.initialize as init
+    L, H, D = 6, 8, 8
+    S = L * world
+    init._GLOBAL_TOKEN_NUM = 1
+    init.initialize_sequence_parallel(S, 1, 1, world)
+    init.set_global_token_indices(list(range(0, world * (L + 1), L + 1)))
+    from gt_sp.layer import DistributedAttentionNoMerge, _SeqAllToAll
+    from models.graphormer_dist_node_level import CoreAttention
+    from gt_sp.utils import adjust_edge_index_nomerge, fix_edge_index
+
+    gen = torch.Generator().manual_seed(500 + rank)
+    q = torch.randn(1, L + 1, H, D, generator=gen).requires_grad_()
+    k = torch.randn(1, L + 1, H, D, generator=gen).requires_grad_()
+    v = torch.randn(1, L + 1, H, D, generator=gen).requires_grad_()
+    dout = torch.randn(1, L + 1, H * D, generator=gen)
+    group = init.get_sequence_parallel_group()
+    a2a_21 = _SeqAllToAll.apply(group, q.detach(), 2, 1)
+    ctx_like = torch.randn(1, world * (L + 1), (H // world) * D, generator=gen)
+    a2a_12 = _SeqAllToAll.apply(group, ctx_like, 1, 2)
+
+    ggen = torch.Generator().manual_seed(77)      # same graph on every rank
+    raw = torch.randint(0, S, (2, 5 * S), generator=ggen)
+    ei = adjust_edge_index_nomerge(fix_edge_index(raw, S), L)
+    core = CoreAttention(H * D, 0.0, H, 1)
+    layer = DistributedAttentionNoMerge(core, group)
+    layer.train()
+    out = layer(q, k, v, None, ei, "sparse")
+    (out * dout).sum().backward()
+    rec = dict(q=q.detach().numpy(), k=k.detach().numpy(), v=v.detach().numpy(), dout=dout.numpy(),
+               a2a_21=a2a_21.numpy(), ctx_like=ctx_like.numpy(), a2a_12=a2a_12.numpy(),
+               edge_index=ei.numpy(), out=out.detach().numpy(), dq=q.grad.numpy(), dk=k.grad.numpy(),
+               dv=v.grad.numpy())
+    gathered = [None] * world
+    dist.all_gather_object(gathered, rec)
+    if rank == 0:
+        flat = {f"r{r}_{name}": val for r, g in enumerate(gathered) for name, val in g.items()}
+        flat["L"], flat["H"], flat["D"] = np.int64(L), np.int64(H), np.int64(D)
+        np.savez_compressed(out_path, **flat)
+        print("wrote", out_path)
+    dist.destroy_process_group()
+
+
+def make_ulysses_cases(ref_path):
+    import torch.multiprocessing as mp
+    for i, world in enumerate((2, 4)):
+        mp.spawn(_ulysses_worker, args=(world, ref_path, 29611 + i, str(OUT_DIR / f"ulysses_P{world}.npz")),
+                 nprocs=world, join=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    install_shims()
+    torch.set_num_threads(1)
+    make_attention_cases()
+    make_edge_cases()
+    make_ulysses_cases(args.reference)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,228 @@
+"""The fused CUDA sparse attention against the CPU oracle and the reference's golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL_BF16, TOL_F32, clustered_graph, load_golden, random_graph, rel_err
+from oracle import sparse_attn_oracle as sao
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_cuda(q, k, v, ei, dout, bias=None, dtype=torch.float32, chunk_edges=128, bias_grad=True):
+    from torchgt_b200 import SparseGraph, sparse_graph_attention
+    dev = "cuda"
+    qc, kc, vc = (torch.as_tensor(t).to(dev, dtype).requires_grad_() for t in (q, k, v))
+    bc = None
+    if bias is not None:
+        bc = torch.as_tensor(bias).to(dev, torch.float32).requires_grad_(bias_grad)
+    graph = SparseGraph(torch.as_tensor(ei).to(dev), qc.shape[0], chunk_edges=chunk_edges)
+    out = sparse_graph_attention(qc, kc, vc, graph, bc)
+    out.backward(torch.as_tensor(dout).to(dev, dtype))
+    res = dict(out=out.detach(), dq=qc.grad, dk=kc.grad, dv=vc.grad)
+    if bc is not None and bias_grad:
+        res["dbias"] = bc.grad
+    return res
+
+
+def _check_against_closed_form(q, k, v, ei, dout, bias, res, tol, per_head_bias=True):
+    out, _ = sao.forward_closed_form(q, k, v, ei, bias)
+    dq, dk, dv, dt = sao.backward_closed_form(q, k, v, ei, dout, bias)
+    assert rel_err(res["out"].float(), out) < tol
+    assert rel_err(res["dq"].float(), dq) < tol
+    assert rel_err(res["dk"].float(), dk) < tol
+    assert rel_err(res["dv"].float(), dv) < tol
+    if "dbias" in res:
+        ref = dt if per_head_bias else dt.sum(axis=1)
+        assert rel_err(res["dbias"], ref) < tol
+
+
+@pytest.mark.parametrize("case", ["small_nobias", "clamped_nobias", "dense_bias", "one_head", "wide_head"])
+def test_reference_golden_vectors(case):
+    g = load_golden(f"attn_{case}.npz")
+    bias = None
+    if "attn_bias" in g:
+        bias = sao.dense_bias_to_edges(torch.from_numpy(g["attn_bias"]), torch.from_numpy(g["edge_index"])).numpy()
+    for chunk in (128, 8):   # 8 forces the hub (chunked) path on most rows with some degree
+        res = _run_cuda(g["q"], g["k"], g["v"], g["edge_index"], g["dout"], bias, chunk_edges=chunk)
+        assert rel_err(res["out"], g["out"]) < TOL_F32
+        assert rel_err(res["dq"], g["dq"]) < TOL_F32
+        assert rel_err(res["dk"], g["dk"]) < TOL_F32
+        assert rel_err(res["dv"], g["dv"]) < TOL_F32
+        if bias is not None:
+            n, h = g["q"].shape[0], g["q"].shape[1]
+            dense = np.zeros((1, h, n, n))
+            np.add.at(dense[0].transpose(1, 2, 0), (g["edge_index"][0], g["edge_index"][1]),
+                      res["dbias"].double().cpu().numpy())
+            assert rel_err(dense, g["dattn_bias"]) < TOL_F32
+        deg = np.bincount(g["edge_index"][1], minlength=g["q"].shape[0])
+        assert torch.all(res["out"][torch.from_numpy(deg == 0).cuda()] == 0)
+
+
+SHAPES = [  # heads, head_dim  (fp32 lanes per row: heads*head_dim/4)
+    (1, 8), (2, 8), (4, 8), (8, 8), (4, 16), (8, 16), (2, 32), (1, 64), (3, 8), (6, 16), (16, 8), (12, 8),
+    (1, 4), (1, 128), (2, 128),
+]
+
+
+@pytest.mark.parametrize("heads,head_dim", SHAPES)
+@pytest.mark.parametrize("bias_kind", ["none", "edge", "edge_head"])
+def test_shapes_fp32(heads, head_dim, bias_kind):
+    n = 300
+    ei = random_graph(100 + heads * head_dim, n, 5.0)
+    gen = torch.Generator().manual_seed(heads * 1000 + head_dim)
+    q, k = (torch.randn(n, heads, head_dim, generator=gen) * 1.5 for _ in range(2))
+    v, dout = (torch.randn(n, heads, head_dim, generator=gen) for _ in range(2))
+    e = ei.shape[1]
+    bias = {"none": None, "edge": torch.randn(e, generator=gen) * 0.3,
+            "edge_head": torch.randn(e, heads, generator=gen) * 0.3}[bias_kind]
+    res = _run_cuda(q, k, v, ei, dout, bias, chunk_edges=32)
+    _check_against_closed_form(q, k, v, ei, dout, bias, res, TOL_F32, per_head_bias=bias_kind == "edge_head")
+
+
+@pytest.mark.parametrize("heads,head_dim", [(1, 8), (2, 8), (8, 8), (4, 16), (8, 16), (2, 64), (3, 8)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_shapes_bf16(heads, head_dim, with_bias):
+    n = 300
+    ei = random_graph(200 + heads * head_dim, n, 5.0)
+    gen = torch.Generator().manual_seed(heads * 77 + head_dim)
+    # the oracle sees the bf16-rounded inputs
+    q, k, v, dout = (torch.randn(n, heads, head_dim, generator=gen).bfloat16().float() for _ in range(4))
+    bias = torch.randn(ei.shape[1], generator=gen) * 0.3 if with_bias else None
+    res = _run_cuda(q, k, v, ei, dout, bias, dtype=torch.bfloat16, chunk_edges=32)
+    assert res["out"].dtype == torch.bfloat16 and res["dq"].dtype == torch.bfloat16
+    _check_against_closed_form(q, k, v, ei, dout, bias, res, TOL_BF16, per_head_bias=False)
+
+
+def test_edge_cases_empty_graph_single_row_and_self_loop_only():
+    gen = torch.Generator().manual_seed(0)
+    q, k, v, dout = (torch.randn(6, 8, 8, generator=gen) for _ in range(4))
+    # no edges at all: output and all gradients are exactly zero
+    res = _run_cuda(q, k, v, torch.zeros((2, 0), dtype=torch.long), dout)
+    for t in res.values():
+        assert torch.count_nonzero(t) == 0
+    # one row, one self loop: out = v * w/(w + 1e-6)
+    res = _run_cuda(q[:1], k[:1], v[:1], torch.zeros((2, 1), dtype=torch.long), dout[:1])
+    _check_against_closed_form(q[:1], k[:1], v[:1], torch.zeros((2, 1), dtype=torch.long), dout[:1], None, res, TOL_F32)
+    # duplicate edges count twice
+    ei = torch.tensor([[1, 1, 2, 2, 2], [0, 0, 0, 3, 3]])
+    res = _run_cuda(q, k, v, ei, dout)
+    _check_against_closed_form(q, k, v, ei, dout, None, res, TOL_F32)
+
+
+def test_clamp_boundaries_and_saturated_scores():
+    n, heads, head_dim = 64, 8, 8
+    gen = torch.Generator().manual_seed(3)
+    ei = random_graph(9, n, 6.0)
+    q, k = (torch.randn(n, heads, head_dim, generator=gen) * 4.0 for _ in range(2))   # most |raw| > 5
+    v, dout = (torch.randn(n, heads, head_dim, generator=gen) for _ in range(2))
+    res = _run_cuda(q, k, v, ei, dout)
+    _check_against_closed_form(q, k, v, ei, dout, None, res, TOL_F32)
+    # raw exactly +5 and -5 (head_dim 4 makes the scale an exact 1/2): the clamp passes the gradient
+    # on both boundaries (inclusive mask, as torch.clamp's backward does)
+    q2 = torch.zeros(2, 1, 4); k2 = torch.zeros(2, 1, 4)
+    q2[0, 0, 0], k2[1, 0, 0] = 10.0, 1.0       # edge 1 -> 0 has raw = 5
+    q2[1, 0, 0], k2[0, 0, 0] = -10.0, 1.0      # edge 0 -> 1 has raw = -5
+    v2, d2 = torch.randn(2, 1, 4, generator=gen), torch.randn(2, 1, 4, generator=gen)
+    ei2 = torch.tensor([[1, 0, 0, 1], [0, 1, 0, 1]])
+    res = _run_cuda(q2, k2, v2, ei2, d2)
+    _check_against_closed_form(q2, k2, v2, ei2, d2, None, res, TOL_F32)
+    assert torch.count_nonzero(res["dq"]) > 0
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q2, k2, v2))
+    sao.sparse_attention_ops(qr, kr, vr, ei2).backward(d2)
+    assert rel_err(res["dq"], qr.grad) < TOL_F32 and rel_err(res["dk"], kr.grad) < TOL_F32
+
+
+@pytest.mark.parametrize("heads", [8, 4, 2, 1])
+def test_long_hub_row_and_column(heads):
+    """A global-token-like row with in-degree and out-degree n (split into chunks and reduced)."""
+    n = 5000
+    gen = torch.Generator().manual_seed(heads)
+    ei = random_graph(21, n, 2.0, hub=True)
+    q, k, v, dout = (torch.randn(n, heads, 8, generator=gen) for _ in range(4))
+    bias = torch.randn(ei.shape[1], generator=gen) * 0.1
+    res = _run_cuda(q, k, v, ei, dout, bias)
+    _check_against_closed_form(q, k, v, ei, dout, bias, res, TOL_F32, per_head_bias=False)
+
+
+def test_run_to_run_bitwise_determinism():
+    ei, n = clustered_graph(7, 8000, 8, 40000, 0.17)
+    gen = torch.Generator().manual_seed(1)
+    q, k, v, dout = (torch.randn(n, 8, 8, generator=gen) for _ in range(4))
+    bias = torch.randn(ei.shape[1], generator=gen) * 0.1
+    a = _run_cuda(q, k, v, ei, dout, bias)
+    b = _run_cuda(q, k, v, ei, dout, bias)
+    for name in a:
+        assert torch.equal(a[name], b[name]), name
+
+
+def test_node_level_training_graph_4096_nodes_vs_ops_oracle():
+    """4,096 nodes + global node, 8 random in-edges per node + self loops, through the reference's edge
+    helpers; compared with the op-by-op fp32 restatement of the reference and its autograd."""
+    from oracle import edge_layout_oracle as elo
+    gen = torch.Generator().manual_seed(42)
+    n = 4096
+    dst = torch.arange(n).repeat_interleave(8)
+    src = torch.randint(0, n, (n * 8,), generator=gen)
+    raw = torch.cat([torch.stack([src, dst]), torch.stack([torch.arange(n), torch.arange(n)])], dim=1)
+    ei = torch.from_numpy(elo.fix_edge_index(raw.numpy(), n))
+    assert ei.shape[1] == 45056
+    q, k, v, dout = (torch.randn(n + 1, 8, 8, generator=gen) for _ in range(4))
+    res = _run_cuda(q, k, v, ei, dout)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+    out = sao.sparse_attention_ops(qr, kr, vr, ei)
+    out.backward(dout)
+    assert rel_err(res["out"], out) < TOL_F32
+    assert rel_err(res["dq"], qr.grad) < TOL_F32
+    assert rel_err(res["dk"], kr.grad) < TOL_F32
+    assert rel_err(res["dv"], vr.grad) < TOL_F32
+    _check_against_closed_form(q, k, v, ei, dout, None, res, TOL_F32)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+def test_benchmark_workload_64k_nodes(dtype, tol):
+    """The 64K-node micro-benchmark shape: 64,001 rows, ~526K edges, 8 heads x 8, scalar edge bias."""
+    ei, n = clustered_graph(1234, 64000, 8, 334000, 0.17)
+    gen = torch.Generator().manual_seed(1234)
+    q, k, v, dout = (torch.randn(n, 8, 8, generator=gen).to(dtype).float() for _ in range(4))
+    bias = torch.randn(ei.shape[1], generator=gen) * 0.1
+    res = _run_cuda(q, k, v, ei, dout, bias, dtype=dtype)
+    _check_against_closed_form(q, k, v, ei, dout, bias, res, tol, per_head_bias=False)
+
+
+def test_size_independent_properties_at_full_size():
+    """Properties that need no oracle: out is linear in V; with V = 1 every output equals Z/(Z+1e-6);
+    permuting the edge list leaves the result unchanged up to summation order."""
+    from torchgt_b200 import SparseGraph, sparse_graph_attention
+    ei, n = clustered_graph(99, 64000, 8, 334000, 0.17)
+    gen = torch.Generator().manual_seed(5)
+    q, k, v1, v2 = (torch.randn(n, 8, 8, generator=gen).cuda() for _ in range(4))
+    graph = SparseGraph(ei.cuda(), n)
+    o1 = sparse_graph_attention(q, k, v1, graph)
+    o2 = sparse_graph_attention(q, k, v2, graph)
+    o12 = sparse_graph_attention(q, k, 2.0 * v1 - 3.0 * v2, graph)
+    assert rel_err(o12, 2.0 * o1 - 3.0 * o2) < TOL_F32
+    ones = sparse_graph_attention(q, k, torch.ones_like(v1), graph)
+    deg = torch.bincount(ei[1], minlength=n).cuda()
+    assert torch.all(ones[deg == 0] == 0)
+    assert torch.all((ones[deg > 0] > 0.99) & (ones[deg > 0] <= 1.0))
+    shuffled = ei[:, torch.randperm(ei.shape[1], generator=gen)]
+    o1s = sparse_graph_attention(q, k, v1, SparseGraph(shuffled.cuda(), n))
+    assert rel_err(o1s, o1) < TOL_F32
+
+
+def test_no_cpu_fallback_and_argument_errors():
+    from torchgt_b200 import sparse_graph_attention
+    from torchgt_b200._cabi import TgtError
+    q = torch.randn(4, 8, 8)
+    ei = torch.tensor([[0, 1], [1, 2]])
+    with pytest.raises(RuntimeError, match="CUDA"):
+        sparse_graph_attention(q, q, q, ei)
+    qc = q.cuda()
+    with pytest.raises(TgtError, match="UNSUPPORTED"):      # head_dim 12 is not a power of two
+        sparse_graph_attention(torch.randn(4, 2, 12).cuda(), torch.randn(4, 2, 12).cuda(),
+                               torch.randn(4, 2, 12).cuda(), ei.cuda())
+    with pytest.raises(ValueError):
+        sparse_graph_attention(qc, qc, qc, ei.cuda(), bias=torch.zeros(5).cuda())
+    with pytest.raises(TypeError):
+        sparse_graph_attention(qc.half(), qc.half(), qc.half(), ei.cuda())

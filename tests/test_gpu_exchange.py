@@ -1,0 +1,139 @@
+"""Re-layout kernels of the Ulysses exchange on one GPU: all ranks' buffers are processed in turn and the
+collective itself is emulated by indexing, then compared with the CPU restatement of _SeqAllToAll."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import load_golden
+from oracle import ulysses_oracle as uo
+
+pytestmark = pytest.mark.gpu
+
+
+def _emulated_exchange(xs_per_rank, s, g, world):
+    """xs_per_rank[r] = list of tensors of rank r.  Runs pack (per rank) -> all-to-all by indexing ->
+    unpack (per rank) through the C ABI, exactly as torchgt_b200.gt_sp.exchange does with NCCL."""
+    import math
+    from torchgt_b200 import _cabi
+    from torchgt_b200.gt_sp.utils import _elem
+    lib = _cabi.load()
+    n_t = len(xs_per_rank[0])
+    x0 = xs_per_rank[0][0]
+    shape = list(x0.shape)
+    chunk = shape.copy(); chunk[s] //= world
+    per_peer = math.prod(chunk)
+    outer_s, width_s = math.prod(shape[:s]), chunk[s] * math.prod(shape[s + 1:])
+    out_shape = chunk.copy(); out_shape[g] *= world
+    outer_g, width_g = math.prod(chunk[:g]), math.prod(chunk[g:])
+    dtype, mult = _elem(x0)
+    stream = torch.cuda.current_stream().cuda_stream
+    sends = []
+    for xs in xs_per_rank:
+        send = torch.empty((world, n_t * per_peer), dtype=x0.dtype, device="cuda")
+        ptrs = [t.data_ptr() for t in xs] + [None] * (3 - n_t)
+        _cabi.check(lib.tgt_a2a_pack_heads(ptrs[0], ptrs[1], ptrs[2], n_t, send.data_ptr(), 1, outer_s,
+                                           width_s * mult, world, dtype, stream))
+        sends.append(send)
+    outs_per_rank = []
+    for r in range(world):
+        recv = torch.stack([sends[src][r] for src in range(world)]).contiguous()
+        outs = [torch.empty(out_shape, dtype=x0.dtype, device="cuda") for _ in range(n_t)]
+        optrs = [t.data_ptr() for t in outs] + [None] * (3 - n_t)
+        _cabi.check(lib.tgt_a2a_unpack_heads(recv.data_ptr(), n_t, optrs[0], optrs[1], optrs[2], 1, outer_g,
+                                             width_g * mult, world, dtype, stream))
+        outs_per_rank.append(outs)
+    return outs_per_rank
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,s,g,n_t", [((1, 7, 8, 8), 2, 1, 3), ((2, 5, 8, 8), 2, 1, 3), ((1, 16, 64), 1, 2, 1),
+                                           ((3, 8, 24), 1, 2, 2), ((1, 8, 6, 9, 8), 3, 1, 1), ((2, 8, 16, 5), 1, 2, 1)])
+def test_relayout_kernels_match_all_to_all_semantics(world, dtype, shape, s, g, n_t):
+    if shape[s] % world != 0:
+        pytest.skip("scatter axis not divisible")
+    gen = torch.Generator().manual_seed(world * 31 + n_t)
+    xs_per_rank = [[torch.randn(shape, generator=gen).to(dtype).cuda() for _ in range(n_t)] for _ in range(world)]
+    outs = _emulated_exchange(xs_per_rank, s, g, world)
+    for t in range(n_t):
+        ref = uo.seq_all_to_all([xs_per_rank[r][t].float().cpu().numpy() for r in range(world)], s, g)
+        for r in range(world):
+            assert np.array_equal(outs[r][t].float().cpu().numpy(), ref[r])
+
+
+def test_named_entry_points_for_the_two_directions():
+    """tgt_a2a_pack_heads/unpack_seq (q, k, v direction) and tgt_a2a_pack_seq/unpack_heads (context
+    direction) with their natural [batch, seq, width] arguments, against the reference's golden maps."""
+    from torchgt_b200 import _cabi
+    lib = _cabi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    for world in (2, 4):
+        g = load_golden(f"ulysses_P{world}.npz")
+        L1, H, D = int(g["L"]) + 1, int(g["H"]), int(g["D"])
+        W = (H // world) * D
+        sends = []
+        for r in range(world):
+            q = torch.from_numpy(g[f"r{r}_q"]).cuda()
+            send = torch.empty(world * L1 * W, device="cuda")
+            _cabi.check(lib.tgt_a2a_pack_heads(q.data_ptr(), None, None, 1, send.data_ptr(), 1, L1, W, world,
+                                               _cabi.TGT_F32, stream))
+            sends.append(send.view(world, -1))
+        for r in range(world):
+            recv = torch.stack([sends[src][r] for src in range(world)]).contiguous()
+            y = torch.empty(1, world * L1, H // world, D, device="cuda")
+            _cabi.check(lib.tgt_a2a_unpack_seq(recv.data_ptr(), 1, y.data_ptr(), None, None, 1, L1, W, world,
+                                               _cabi.TGT_F32, stream))
+            assert np.array_equal(y.cpu().numpy(), g[f"r{r}_a2a_21"])
+        sends = []
+        for r in range(world):
+            c = torch.from_numpy(g[f"r{r}_ctx_like"]).cuda()
+            send = torch.empty(world * L1 * W, device="cuda")
+            _cabi.check(lib.tgt_a2a_pack_seq(c.data_ptr(), None, None, 1, send.data_ptr(), 1, L1, W, world,
+                                             _cabi.TGT_F32, stream))
+            sends.append(send.view(world, -1))
+        for r in range(world):
+            recv = torch.stack([sends[src][r] for src in range(world)]).contiguous()
+            y = torch.empty(1, L1, H * D, device="cuda")
+            _cabi.check(lib.tgt_a2a_unpack_heads(recv.data_ptr(), 1, y.data_ptr(), None, None, 1, L1, W, world,
+                                                 _cabi.TGT_F32, stream))
+            assert np.array_equal(y.cpu().numpy(), g[f"r{r}_a2a_12"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_global_rows_broadcast_and_its_backward(dtype):
+    import torchgt_b200.gt_sp.initialize as init
+    from torchgt_b200.gt_sp.utils import copy_global_token0
+    init.destroy_sequence_parallel()
+    init._state.group, init._state.world_size, init._state.rank = object(), 4, 0
+    rows = [0, 6, 12, 18]
+    init.set_global_token_indices(rows)
+    try:
+        gen = torch.Generator().manual_seed(4)
+        x = torch.randn(2, 24, 16, generator=gen).to(dtype)
+        xc = x.cuda().requires_grad_()
+        y = copy_global_token0(xc * 1.0, 1)
+        ref = uo.copy_global_token0(x.float().numpy(), rows)
+        assert np.array_equal(y.detach().float().cpu().numpy(), ref)
+        w = torch.randn(2, 24, 16, generator=gen).to(dtype)
+        (y * w.cuda()).sum().backward()
+        xr = x.float().clone().requires_grad_()
+        yr = xr * 1.0
+        yr[:, rows, :] = yr[:, 0:1, :].expand(-1, 4, -1)
+        (yr * w.float()).sum().backward()
+        tol = 1e-6 if dtype == torch.float32 else 2e-2
+        assert torch.allclose(xc.grad.float().cpu(), xr.grad, rtol=tol, atol=tol)
+    finally:
+        init.destroy_sequence_parallel()
+
+
+def test_relayout_argument_errors():
+    from torchgt_b200 import _cabi
+    lib = _cabi.load()
+    x = torch.zeros(64, device="cuda")
+    assert lib.tgt_a2a_pack_heads(x.data_ptr(), None, None, 2, x.data_ptr(), 1, 4, 4, 2, 0, None) == 1
+    assert "n_tensors" in _cabi.last_error()
+    assert lib.tgt_a2a_pack_heads(x.data_ptr(), None, None, 1, x.data_ptr(), 1, 4, 4, 2, 7, None) == 1
+    assert lib.tgt_a2a_pack_heads(x.data_ptr() + 4, None, None, 1, x.data_ptr(), 1, 4, 4, 2, 0, None) == 1
+    assert "aligned" in _cabi.last_error()
