@@ -197,14 +197,14 @@ class OpBuffers:
         self.dbias = torch.empty_like(bias) if with_bias else None
         lib = _cabi.load()
         nb = ctypes.c_size_t()
+        self.code = _cabi.TGT_F32 if dtype == torch.float32 else _cabi.TGT_BF16
         _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), graph.by_src.byref(), HEADS, HEAD_DIM,
-                                                      1, ctypes.byref(nb)))
+                                                      self.code, 1, ctypes.byref(nb)))
         nf = ctypes.c_size_t()
-        _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), None, HEADS, HEAD_DIM, 0,
+        _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), None, HEADS, HEAD_DIM, self.code, 0,
                                                       ctypes.byref(nf)))
         self.scratch_f = torch.empty(max(nf.value, 16), dtype=torch.uint8, device=dev)
         self.scratch_b = torch.empty(max(nb.value, 16), dtype=torch.uint8, device=dev)
-        self.code = _cabi.TGT_F32 if dtype == torch.float32 else _cabi.TGT_BF16
         self.graph = graph
 
     def fwd(self, stream):
@@ -240,8 +240,8 @@ def capture(fn):
 
 
 def kernels_per_step(graph):
-    per = lambda lay: 1 + (2 if lay.n_chunks > 0 else 0)
-    return 2 * per(graph.by_dst) + per(graph.by_src)
+    # forward, dQ pass, dK/dV pass: one walk + one stitch kernel each; plus the row-statistics kernel
+    return 3 * 2 + 1
 
 
 def run_single_gpu(args, dtype):
@@ -254,9 +254,19 @@ def run_single_gpu(args, dtype):
     graph = SparseGraph(edge_index.to(dev), n_rows)
     graph.by_src  # build both layouts before timing
     sets = [OpBuffers(graph, dtype, 1234 + i) for i in range(ROTATING_SETS)]
-    step_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 3))) for b in sets]
-    phase_graphs = [[capture(lambda s, b=b: b.fwd(s)), capture(lambda s, b=b: b.bwd(s, 1)),
-                     capture(lambda s, b=b: b.bwd(s, 2))] for b in sets]
+    if args.profile:
+        # plain launches of a few steps for ncu (no CUDA graph, no end-to-end or CPU legs)
+        stream = torch.cuda.current_stream().cuda_stream
+        for i in range(args.warmup + args.steps):
+            sets[i % ROTATING_SETS].fwd(stream)
+            sets[i % ROTATING_SETS].bwd(stream, 7)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_run": True, "steps": args.steps, "warmup": args.warmup,
+                          "kernels_per_step": kernels_per_step(graph)}), flush=True)
+        return
+    step_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 7))) for b in sets]
+    phase_graphs = [[capture(lambda s, b=b: b.fwd(s)), capture(lambda s, b=b: b.bwd(s, 3)),
+                     capture(lambda s, b=b: b.bwd(s, 4))] for b in sets]
     torch.cuda.synchronize()
 
     sampler = ClockSampler(0)
@@ -469,6 +479,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--dtype", choices=["fp32", "bf16"], default="fp32")
+    ap.add_argument("--profile", action="store_true",
+                    help="N=1 only: launch warmup+steps plain forward+backward steps and exit (for ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

@@ -46,17 +46,14 @@ extern "C" {
 /* heads  -> bias[E, H]  one value per edge and head                                              */
 
 /*
- * Edges grouped by one endpoint ("segment layout").  Built by tgt_edge_layout_build.
- *   group_by = 1 : grouped by destination (edge_index row 1) — CSR used by forward and by the
- *                  dQ pass; `other` holds the source of every edge.
- *   group_by = 0 : grouped by source (edge_index row 0) — CSC used by the dK/dV pass; `other`
- *                  holds the destination.
+ * Edges sorted by one endpoint ("segment layout").  Built by tgt_edge_layout_build.
+ *   group_by = 1 : sorted by destination (edge_index row 1) — used by forward and by the dQ pass;
+ *                  `other` holds the source of every edge.
+ *   group_by = 0 : sorted by source (edge_index row 0) — used by the dK/dV pass; `other` holds the
+ *                  destination.
  * Definition (bit-exact contract): perm = stable argsort of the grouping endpoint,
- * other = other_endpoint[perm], ptr = exclusive prefix sum of bincount(grouping endpoint, n_rows).
- * Rows with more than `chunk_edges` edges ("hub rows", e.g. Graphormer's global token) are listed
- * in hub_row[n_hubs] in ascending row order and cut into chunks of chunk_edges consecutive edges:
- * chunks hub_chunk_ptr[i] .. hub_chunk_ptr[i+1]-1 belong to hub_row[i]; chunk c covers edges
- * chunk_begin[c] .. min(chunk_begin[c]+chunk_edges, ptr[chunk_row[c]+1]) - 1.
+ * seg = grouping endpoint[perm], other = other endpoint[perm],
+ * ptr = exclusive prefix sum of bincount(grouping endpoint, n_rows).
  */
 typedef struct tgt_layout {
   int64_t n_rows;
@@ -64,14 +61,7 @@ typedef struct tgt_layout {
   const int32_t* ptr;   /* device [n_rows + 1] */
   const int32_t* other; /* device [n_edges]    */
   const int32_t* perm;  /* device [n_edges]    */
-  int32_t chunk_edges;
-  int32_t n_chunks;
-  int32_t n_hubs;
-  int32_t reserved;
-  const int32_t* chunk_row;     /* device [n_chunks]   */
-  const int32_t* chunk_begin;   /* device [n_chunks]   */
-  const int32_t* hub_row;       /* device [n_hubs]     */
-  const int32_t* hub_chunk_ptr; /* device [n_hubs + 1] */
+  const int32_t* seg;   /* device [n_edges]    */
 } tgt_layout;
 
 /* Library version (major * 100 + minor). */
@@ -81,12 +71,18 @@ TGT_API int tgt_version(void);
 TGT_API const char* tgt_last_error(void);
 
 /*
- * Capacity query for tgt_edge_layout_build: upper bounds on the number of chunks and hub rows for
- * any graph with n_edges edges, and the bytes of device workspace the build needs.
+ * Tuning / test knob with no counterpart in the reference: the attention kernels cut the sorted edge
+ * list into tiles of (128 / lanes-per-row) * edges_per_lane_group edges.  0 (the default) lets the
+ * library choose so that one wave of thread blocks covers the graph; a small value forces many
+ * tiles, which the tests use to exercise the cross-tile paths on small graphs.  Process-wide.
+ */
+TGT_API int tgt_debug_set_tile_edges(int edges_per_lane_group);
+
+/*
+ * Bytes of device workspace tgt_edge_layout_build needs.
  * Replaces nothing in the reference (the reference keeps edges as an unsorted COO list).
  */
-TGT_API int tgt_edge_layout_sizes(int64_t n_rows, int64_t n_edges, int32_t chunk_edges,
-                          int64_t* max_chunks, int64_t* max_hubs, size_t* workspace_bytes);
+TGT_API int tgt_edge_layout_sizes(int64_t n_rows, int64_t n_edges, size_t* workspace_bytes);
 
 /*
  * Build one segment layout from the COO edge list the reference's batch packing produces
@@ -94,24 +90,23 @@ TGT_API int tgt_edge_layout_sizes(int64_t n_rows, int64_t n_edges, int32_t chunk
  * get_batch_reorder_blockize, data/collator_sp_sparse.py:126-133 flatten_edge_index_nopad):
  * edge_index is a device int64 [2, n_edges] array, row 0 = source (K/V row), row 1 = destination
  * (Q / output row), exactly as consumed by CoreAttention.sparse_attention (attn_module.py:146-147).
- * Output arrays are device buffers sized by tgt_edge_layout_sizes (ptr: n_rows+1, other/perm:
- * n_edges, chunk_row/chunk_begin: max_chunks, hub_row: max_hubs, hub_chunk_ptr: max_hubs+1).
- * counts_host[0] = n_chunks, counts_host[1] = n_hubs on return.
+ * ptr [n_rows + 1], other, perm, seg [n_edges] are device output buffers.
  * This call SYNCHRONISES the stream once (it is made once per batch, not per layer) and returns
  * TGT_ERR_INDEX_RANGE if any node id is outside [0, n_rows).
  */
-TGT_API int tgt_edge_layout_build(const int64_t* edge_index, int64_t n_edges, int64_t n_rows, int group_by,
-                          int32_t chunk_edges, int32_t* ptr, int32_t* other, int32_t* perm,
-                          int32_t* chunk_row, int32_t* chunk_begin, int32_t* hub_row,
-                          int32_t* hub_chunk_ptr, int64_t* counts_host, void* workspace,
-                          size_t workspace_bytes, void* stream);
+TGT_API int tgt_edge_layout_build(const int64_t* edge_index, int64_t n_edges, int64_t n_rows,
+                                  int group_by, int32_t* ptr, int32_t* other, int32_t* perm,
+                                  int32_t* seg, void* workspace, size_t workspace_bytes,
+                                  void* stream);
 
 /*
  * Bytes of scratch tgt_sparse_attn_fwd (phase 0) / tgt_sparse_attn_bwd (phase 1) need for these
- * layouts.  by_src may be NULL for phase 0.
+ * layouts (partial sums of rows that cross a tile boundary; row statistics of the backward).
+ * by_src may be NULL for phase 0.
  */
-TGT_API int tgt_sparse_attn_scratch_bytes(const tgt_layout* by_dst, const tgt_layout* by_src, int heads,
-                                  int head_dim, int phase, size_t* bytes);
+TGT_API int tgt_sparse_attn_scratch_bytes(const tgt_layout* by_dst, const tgt_layout* by_src,
+                                          int heads, int head_dim, int dtype, int phase,
+                                          size_t* bytes);
 
 /*
  * Forward of the topology-aware sparse attention: for every edge e = (s -> d) and head h
@@ -135,8 +130,8 @@ TGT_API int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, con
  * elementwise chain).  With G = dout, inv = 1/(Z+1e-6):
  *   dw = (G_d . V_s - G_d . O_d) * inv_d;  dV_s += w * inv_d * G_d;  dt = dw * w  (= dbias)
  *   da = dt * [-5 <= raw <= 5];  dQ_d += da * K_s / sqrt(D);  dK_s += da * Q_d / sqrt(D)
- * Pass A walks by_dst (dQ, dbias, per-row statistics), pass B walks by_src (dK, dV); scores are
- * recomputed, nothing per-edge is read from forward.  dbias is device fp32 in ORIGINAL edge order
+ * A streaming pre-pass computes the per-row statistics, pass A walks by_dst (dQ, dbias), pass B
+ * walks by_src (dK, dV); scores are recomputed, nothing per-edge is read from forward.  dbias is device fp32 in ORIGINAL edge order
  * with the shape bias has, or NULL when not wanted.  Deterministic (no atomics).
  */
 TGT_API int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
@@ -146,10 +141,11 @@ TGT_API int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* k, 
                         size_t scratch_bytes, void* stream);
 
 /*
- * The same backward with the two passes selectable: passes = 1 runs pass A only (dQ, dbias, row
- * statistics into `scratch`), 2 runs pass B only (dK, dV; needs the statistics a pass A left in the
- * same scratch for the same inputs), 3 runs both (= tgt_sparse_attn_bwd).  Lets a caller time or
- * overlap the passes separately; replaces the same reference code as tgt_sparse_attn_bwd.
+ * The same backward with its stages selectable by bit mask: 1 = row statistics
+ * (1/(Z+1e-6) and dO.O per row and head, into `scratch`), 2 = pass A (dQ, dbias), 4 = pass B
+ * (dK, dV).  Passes A and B need the statistics a stage-1 call left in the same scratch for the same
+ * inputs.  7 = tgt_sparse_attn_bwd.  Lets a caller time or overlap the stages separately; replaces
+ * the same reference code as tgt_sparse_attn_bwd.
  */
 TGT_API int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const void* k, const void* v,
                                        const float* bias, int bias_heads, const void* out,

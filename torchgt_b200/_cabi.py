@@ -5,7 +5,7 @@ There is no CPU fallback: if the library is missing or a call fails this module 
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtorchgt_b200.so"
@@ -40,14 +40,7 @@ class TgtLayout(ctypes.Structure):
         ("ptr", c_void_p),
         ("other", c_void_p),
         ("perm", c_void_p),
-        ("chunk_edges", c_int32),
-        ("n_chunks", c_int32),
-        ("n_hubs", c_int32),
-        ("reserved", c_int32),
-        ("chunk_row", c_void_p),
-        ("chunk_begin", c_void_p),
-        ("hub_row", c_void_p),
-        ("hub_chunk_ptr", c_void_p),
+        ("seg", c_void_p),
     ]
 
 
@@ -57,12 +50,11 @@ _PL = POINTER(TgtLayout)
 SIGNATURES = {
     "tgt_version": (c_int, []),
     "tgt_last_error": (c_char_p, []),
-    "tgt_edge_layout_sizes": (c_int, [c_int64, c_int64, c_int32, POINTER(c_int64), POINTER(c_int64),
-                                      POINTER(c_size_t)]),
-    "tgt_edge_layout_build": (c_int, [c_void_p, c_int64, c_int64, c_int, c_int32, c_void_p, c_void_p,
-                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                      POINTER(c_int64), c_void_p, c_size_t, c_void_p]),
-    "tgt_sparse_attn_scratch_bytes": (c_int, [_PL, _PL, c_int, c_int, c_int, POINTER(c_size_t)]),
+    "tgt_debug_set_tile_edges": (c_int, [c_int]),
+    "tgt_edge_layout_sizes": (c_int, [c_int64, c_int64, POINTER(c_size_t)]),
+    "tgt_edge_layout_build": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_size_t, c_void_p]),
+    "tgt_sparse_attn_scratch_bytes": (c_int, [_PL, _PL, c_int, c_int, c_int, c_int, POINTER(c_size_t)]),
     "tgt_sparse_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, _PL, c_void_p,
                                     c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "tgt_sparse_attn_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,

@@ -1,100 +1,75 @@
-// Lane mapping and work assignment shared by the sparse-attention kernels.
+// Edge-balanced segmented reduction shared by the three sparse-attention kernels.
 //
-// A row of Q/K/V/O is heads*head_dim values.  Lanes move 16 bytes each (VEC values), so
-//   LPH = head_dim / VEC        lanes cover one head,
-//   G   = LPH * heads_per_group lanes cover one "head group" of a row (G <= 32),
-// and heads that do not fit one group are walked by blockIdx.y.  Within a warp, LPR >= G lanes
-// work on one row (LPR is a run-time power of two), so LPR/G edges of that row are in flight per
-// step ("slots") and 32/LPR rows share the warp.
+// Lanes move 16 bytes of a row each (VEC values): LPH = head_dim / VEC lanes cover one head and
+// G = LPH * heads_per_group lanes ("lane group") cover the heads one CTA column handles; heads that
+// do not fit 32 lanes are walked by blockIdx.y.
 //
-// Rows with more than chunk_edges edges are not walked in row mode; their chunks are walked in
-// chunk mode (one warp per chunk, LPR = 32) into fp32 partials which a small reduce kernel sums in
-// chunk order.  No atomics anywhere, so results are bitwise reproducible.
+// The edges, sorted by the grouping endpoint ("row"), are cut into tiles of NG * ge consecutive
+// edges, one CTA per tile, NG = 128 / G lane groups per CTA.  Lane group g walks ge consecutive
+// edges, kUnroll at a time: all gathers of a batch are issued before any arithmetic.  Edge
+// positions, not rows, are what is divided, so a row with 100,000 edges and a row with one edge
+// cost the same per edge and every lane group does the same amount of work.
+//
+// A row whose edges lie inside one lane group's range is finished by that group and written once.
+// A row that crosses a range boundary leaves partial sums in shared memory ("head" = the range
+// starts inside the row, "tail" = the row starts here and runs past the range); after a barrier
+// the group that holds the tail adds the heads of the following groups in order.  If the row
+// also crosses the tile boundary the CTA writes its sum to a per-tile carry in global memory and a
+// small second kernel adds those in tile order.  Every sum has a fixed order: no atomics, bitwise
+// reproducible results.  Rows without edges are zero-filled by the group that walks the gap.
 #pragma once
 
 #include "tgt_common.cuh"
 
 namespace tgt {
 
-constexpr int kWarpsPerBlock = 4;
-constexpr int kBlockThreads = kWarpsPerBlock * 32;
+constexpr int kBlockThreads = 128;
 constexpr int kUnroll = 4;
 
-struct Walk {
-  int row;        // row this lane works on (-1: none)
-  int begin;      // first edge position of this lane (already offset by its slot)
-  int end;        // one past the last edge position of the row/chunk
-  int iters;      // warp-uniform number of steps
-  int nslots;     // edges in flight per row per step
-  int slot;       // this lane's slot
-  int c;          // this lane's 16-byte column inside the head group
-  int chunk;      // chunk id in chunk mode, else -1
-  bool is_hub;    // row mode: the row is a hub and is handled by chunk mode
+template <int G>
+struct TileGeom {
+  static constexpr int NG = kBlockThreads / G;  // lane groups per CTA
+  static constexpr int GE_MAX = (2048 / NG) > 128 ? 128 : ((2048 / NG) < 8 ? 8 : (2048 / NG));
+  static constexpr int TE_MAX = NG * GE_MAX;    // most edges a tile can hold
 };
 
-// Work assignment for one lane.  `lpr_log2` is log2(lanes per row) in row mode.
-template <int G>
-__device__ __forceinline__ Walk make_walk(const tgt_layout& L, bool chunk_mode, int lpr_log2) {
-  Walk w;
-  const int lane = threadIdx.x & 31;
-  const int warp_global = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  w.chunk = -1;
-  w.is_hub = false;
-  int deg = 0;
-  if (chunk_mode) {
-    w.nslots = 32 / G;
-    w.slot = lane / G;
-    w.c = lane % G;
-    if (warp_global < L.n_chunks) {
-      w.chunk = warp_global;
-      w.row = __ldg(L.chunk_row + warp_global);
-      const int b = __ldg(L.chunk_begin + warp_global);
-      const int row_end = __ldg(L.ptr + w.row + 1);
-      w.end = min(b + L.chunk_edges, row_end);
-      w.begin = b + w.slot;
-      deg = w.end - b;
-    } else {
-      w.row = -1;
-      w.begin = w.end = 0;
-    }
-  } else {
-    const int lpr = 1 << lpr_log2;
-    const int rpw = 32 >> lpr_log2;
-    const int in_row = lane & (lpr - 1);
-    w.nslots = lpr / G;
-    w.slot = in_row / G;
-    w.c = in_row % G;
-    const int64_t row = int64_t(warp_global) * rpw + (lane >> lpr_log2);
-    if (row < L.n_rows) {
-      w.row = int(row);
-      const int b = __ldg(L.ptr + row);
-      w.end = __ldg(L.ptr + row + 1);
-      deg = w.end - b;
-      if (deg > L.chunk_edges) {
-        w.is_hub = true;
-        deg = 0;
-        w.end = b;
-      }
-      w.begin = b + w.slot;
-    } else {
-      w.row = -1;
-      w.begin = w.end = 0;
-    }
-  }
-  const int steps = (deg + w.nslots - 1) / w.nslots;
-  w.iters = __reduce_max_sync(0xffffffffu, steps);
-  return w;
+// What every kernel needs to walk the edges.
+struct SegWalk {
+  const int32_t* ptr;
+  const int32_t* other;
+  const int32_t* perm;
+  const int32_t* seg;
+  int n_rows;
+  int n_edges;
+  int ge;          // edges per lane group per tile (multiple of kUnroll, <= GE_MAX)
+  int n_tiles;
+  float* gcarry;   // [n_tiles][2][gridDim.y * G * NACC] cross-tile partial sums
+  bool need_perm;  // stage perm[] (bias or dbias in original edge order)
+};
+
+inline int host_ge_max(int g) {
+  const int ng = kBlockThreads / g;
+  int m = 2048 / ng;
+  return m > 128 ? 128 : (m < 8 ? 8 : m);
 }
 
-// Sum over the slots of one row (lanes that hold the same column c); LPR lanes per row.
-template <int G>
-__device__ __forceinline__ float slot_sum(float x, int lpr) {
-#pragma unroll
-  for (int off = G; off < 32; off <<= 1) {
-    const float t = __shfl_xor_sync(0xffffffffu, x, off);
-    if (off < lpr) x += t;
+// Edges per lane group: one balanced wave over the GPU when the graph is small enough, else the
+// largest tile.  `ctas_per_sm` is the occupancy the caller expects.
+int forced_ge();  // 0 unless tgt_debug_set_tile_edges() overrides the choice
+
+inline int choose_ge(int64_t n_edges, int g, int ctas_per_sm) {
+  const int ng = kBlockThreads / g;
+  if (forced_ge() > 0) {
+    int f = (forced_ge() + kUnroll - 1) / kUnroll * kUnroll;
+    return f > host_ge_max(g) ? host_ge_max(g) : f;
   }
-  return x;
+  const int64_t groups = int64_t(kSmCount) * ctas_per_sm * ng;
+  int64_t ge = (n_edges + groups - 1) / groups;
+  ge = (ge + kUnroll - 1) / kUnroll * kUnroll;
+  const int lo = 4 * kUnroll > host_ge_max(g) ? host_ge_max(g) : 4 * kUnroll;
+  if (ge < lo) ge = lo;
+  if (ge > host_ge_max(g)) ge = host_ge_max(g);
+  return int(ge);
 }
 
 template <int VEC>
@@ -113,20 +88,212 @@ __device__ __forceinline__ bool clamp_passes_grad(float raw) {
   return raw >= kClampLo && raw <= kClampHi;
 }
 
-// Host-side choice of lanes per row: enough slots for about half the average degree.
-inline int choose_lpr_log2(int G, double avg_degree) {
-  int lpr = G;
-  while (lpr < 32 && double(lpr / G) * 2.0 < avg_degree) lpr <<= 1;
-  int l2 = 0;
-  while ((1 << l2) < lpr) ++l2;
-  return l2;
+// exp(x) for |x| < 80: ex2.approx on the rounded product x*log2(e), corrected for the rounding
+// error of that product with one fma (relative error about 2^-22, like expf, in 6 instructions).
+__device__ __forceinline__ float fast_exp(float x) {
+  constexpr float kLog2eHi = 1.4426950216293335f;   // log2(e) rounded to fp32
+  constexpr float kLog2eLo = 1.9259629911e-8f;      // log2(e) - kLog2eHi
+  constexpr float kLn2 = 0.6931471805599453f;
+  const float t = x * kLog2eHi;
+  const float r = fmaf(x, kLog2eHi, -t) + x * kLog2eLo;  // what the product lost
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+  return fmaf(e, r * kLn2, e);
+}
+
+// The walk.  Policy supplies:
+//   static constexpr int NACC;                     accumulators per lane
+//   struct Operands;                               what one edge loads
+//   void load(Operands&, int row, int other, int perm_e) const;      issue the gathers of one edge
+//   void clear(Operands&) const;                                     operands of a padding slot
+//   Scalars prep(const Operands&, bool valid, int perm_e) const;     warp-uniform part (shuffles)
+//   void accumulate(float (&acc)[NACC], const Operands&, const Scalars&) const;
+//   void finalize(int row, const float (&acc)[NACC]) const;          write the finished row
+//   void zero_row(int row) const;                                    row without edges
+template <int G, class Policy>
+__device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, int32_t* s_other,
+                                          int32_t* s_seg, int32_t* s_perm, float* s_carry,
+                                          int32_t* s_carry_row) {
+  constexpr int NG = TileGeom<G>::NG;
+  constexpr int NACC = Policy::NACC;
+  const int tid = threadIdx.x;
+  const int g = tid / G;        // lane group inside the CTA
+  const int c = tid % G;        // 16-byte column inside the group
+  const int te = NG * w.ge;
+  const int64_t t0 = int64_t(blockIdx.x) * te;
+  const int n = int(min(int64_t(te), int64_t(w.n_edges) - t0));  // edges in this tile (>= 1)
+
+  // ---- stage the tile's indices: s_seg[i + 1] = row of tile edge i, with one edge of halo each side
+  for (int i = tid; i < n + 2; i += kBlockThreads) {
+    const int64_t e = t0 - 1 + i;
+    s_seg[i] = e < 0 ? -1 : (e >= w.n_edges ? -2 : __ldg(w.seg + e));
+  }
+  for (int i = tid; i < n; i += kBlockThreads) {
+    s_other[i] = __ldg(w.other + t0 + i);
+    if (w.need_perm) s_perm[i] = __ldg(w.perm + t0 + i);
+  }
+  for (int i = tid; i < 2 * NG; i += kBlockThreads) s_carry_row[i] = -3;  // [g][0] head row, [g][1] tail row
+  __syncthreads();
+
+  // ---- walk this group's range [gb, ge) of the tile
+  const int gb = min(g * w.ge, n);
+  const int gend = min(gb + w.ge, n);
+  float acc[NACC];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
+  int cur = s_seg[gb];                         // row of the edge just before the range
+  bool own = gb < gend && s_seg[gb + 1] == cur;  // the range starts inside row `cur`
+  bool head_pending = own;
+  float* my_head = s_carry + (g * 2 + 0) * (G * NACC) + c * NACC;
+  float* my_tail = s_carry + (g * 2 + 1) * (G * NACC) + c * NACC;
+
+  // all groups of a warp run the same number of batches (the shuffles inside need the full warp)
+  const int warp_first_group = (tid / 32) * (32 / G);
+  const int warp_gb = min(warp_first_group * w.ge, n);
+  const int batches = (min(w.ge, n - warp_gb) + kUnroll - 1) / kUnroll;
+  for (int b = 0; b < batches; ++b) {
+    typename Policy::Operands ops[kUnroll];
+    int row[kUnroll], pe[kUnroll];
+    bool valid[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = gb + b * kUnroll + u;
+      valid[u] = i < gend;
+      const int ii = valid[u] ? i : 0;
+      row[u] = s_seg[ii + 1];
+      pe[u] = w.need_perm ? s_perm[ii] : 0;
+      if (valid[u]) pol.load(ops[u], row[u], s_other[ii], pe[u]);
+      else pol.clear(ops[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const typename Policy::Scalars sc = pol.prep(ops[u], valid[u], pe[u]);
+      if (valid[u]) {
+        if (row[u] != cur) {
+          if (own) {
+            if (head_pending) {
+#pragma unroll
+              for (int a = 0; a < NACC; ++a) my_head[a] = acc[a];
+              if (c == 0) s_carry_row[g * 2 + 0] = cur;
+            } else {
+              pol.finalize(cur, acc);
+            }
+          }
+          head_pending = false;
+          for (int r = cur + 1; r < row[u]; ++r) pol.zero_row(r);
+          cur = row[u];
+          own = true;
+#pragma unroll
+          for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
+        }
+        pol.accumulate(acc, ops[u], sc);
+      }
+    }
+  }
+  if (gb < gend) {  // close the last row of the range
+    const bool cont_out = s_seg[gend + 1] == cur;
+    if (head_pending) {
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) my_head[a] = acc[a];
+      if (c == 0) s_carry_row[g * 2 + 0] = cur;
+    } else if (cont_out) {
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) my_tail[a] = acc[a];
+      if (c == 0) s_carry_row[g * 2 + 1] = cur;
+    } else {
+      pol.finalize(cur, acc);
+    }
+    if (t0 + gend == w.n_edges)  // this group owns the last edge: rows after it have no edges
+      for (int r = cur + 1; r < w.n_rows; ++r) pol.zero_row(r);
+  }
+  __syncthreads();
+
+  // ---- stitch rows that cross group boundaries, in group order
+  const int last_row = s_seg[n];            // row of the tile's last edge
+  const bool tile_cont_out = s_seg[n + 1] == last_row;
+  const int lanes_all = gridDim.y * G;
+  float* tile_carry = w.gcarry + (int64_t(blockIdx.x) * 2) * (int64_t(lanes_all) * NACC) +
+                      int64_t(blockIdx.y * G + c) * NACC;
+  if (g == 0 && s_seg[0] == s_seg[1]) {
+    // the tile starts inside a row that began in an earlier tile: sum its heads into the tile's
+    // head carry
+    const int r = s_seg[1];
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
+    for (int j = 0; j < NG && s_carry_row[j * 2] == r; ++j) {
+      const float* h = s_carry + (j * 2) * (G * NACC) + c * NACC;
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) acc[a] += h[a];
+    }
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) tile_carry[a] = acc[a];
+  }
+  const int r = s_carry_row[g * 2 + 1];
+  if (r >= 0) {
+    // this group holds the start of row r: add the heads of the groups the row runs through
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) acc[a] = my_tail[a];
+    for (int j = g + 1; j < NG && s_carry_row[j * 2] == r; ++j) {
+      const float* h = s_carry + (j * 2) * (G * NACC) + c * NACC;
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) acc[a] += h[a];
+    }
+    if (r == last_row && tile_cont_out) {
+      float* t = tile_carry + int64_t(lanes_all) * NACC;  // the tile's tail carry
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) t[a] = acc[a];
+    } else {
+      pol.finalize(r, acc);
+    }
+  }
+}
+
+// Second kernel: rows that cross tile boundaries.  One warp per tile; the warp of the tile in
+// which such a row STARTS adds that tile's tail carry and the head carries of the following tiles
+// in tile order and finishes the row.
+template <int G, class Policy>
+__device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol) {
+  constexpr int NG = TileGeom<G>::NG;
+  constexpr int NACC = Policy::NACC;
+  const int tile = blockIdx.x * (kBlockThreads / 32) + (threadIdx.x >> 5);
+  if (tile >= w.n_tiles) return;
+  const int lane = threadIdx.x & 31;
+  const int te = NG * w.ge;
+  const int64_t t1 = int64_t(tile + 1) * te;
+  if (t1 >= w.n_edges) return;                       // last tile: nothing runs past it
+  const int r = __ldg(w.seg + t1 - 1);
+  if (__ldg(w.seg + t1) != r) return;                // the tile ends on a row boundary
+  const int row_begin = __ldg(w.ptr + r);
+  if (row_begin < t1 - te) return;                   // the row started in an earlier tile
+  const int last_tile = (__ldg(w.ptr + r + 1) - 1) / te;
+  constexpr int NSLOT = 32 / G;
+  const int slot = lane / G, c = lane % G;
+  const int lanes_all = gridDim.y * G;
+  const int64_t stride = int64_t(lanes_all) * NACC;
+  const float* base = w.gcarry + int64_t(blockIdx.y * G + c) * NACC;
+  float acc[NACC];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
+  // partial 0 = tail carry of `tile`, partial i > 0 = head carry of tile + i
+  const int n_part = last_tile - tile + 1;
+  for (int i = slot; i < n_part; i += NSLOT) {
+    const float* p = base + (int64_t(tile + i) * 2 + (i == 0 ? 1 : 0)) * stride;
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) acc[a] += p[a];
+  }
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) {
+#pragma unroll
+    for (int off = G; off < 32; off <<= 1) acc[a] += __shfl_xor_sync(0xffffffffu, acc[a], off);
+  }
+  if (slot == 0) pol.finalize(r, acc);
 }
 
 struct HeadSplit {
-  int lph;         // lanes per head
-  int hpg;         // heads per group
-  int g;           // lanes per group
-  int groups;      // number of head groups (gridDim.y)
+  int lph;     // lanes per head
+  int hpg;     // heads per lane group
+  int g;       // lanes per group
+  int groups;  // number of head groups (gridDim.y)
 };
 
 // Returns false when (heads, head_dim, dtype) cannot be mapped onto 16-byte lanes.
@@ -145,37 +312,57 @@ inline bool split_heads(int heads, int head_dim, int dtype, HeadSplit* hs) {
 }
 
 // Expands to `CALL(T, LPH, G)` for the run-time (dtype, lph, g) triple.
-#define TGT_DISPATCH_G(T, LPH, g, CALL)                     \
-  switch (g) {                                              \
-    case 1: if constexpr (LPH <= 1) { CALL(T, LPH, 1); } break;   \
-    case 2: if constexpr (LPH <= 2) { CALL(T, LPH, 2); } break;   \
-    case 4: if constexpr (LPH <= 4) { CALL(T, LPH, 4); } break;   \
-    case 8: if constexpr (LPH <= 8) { CALL(T, LPH, 8); } break;   \
+#define TGT_DISPATCH_G(T, LPH, g, CALL)                            \
+  switch (g) {                                                     \
+    case 1: if constexpr (LPH <= 1) { CALL(T, LPH, 1); } break;    \
+    case 2: if constexpr (LPH <= 2) { CALL(T, LPH, 2); } break;    \
+    case 4: if constexpr (LPH <= 4) { CALL(T, LPH, 4); } break;    \
+    case 8: if constexpr (LPH <= 8) { CALL(T, LPH, 8); } break;    \
     case 16: if constexpr (LPH <= 16) { CALL(T, LPH, 16); } break; \
     case 32: if constexpr (LPH <= 32) { CALL(T, LPH, 32); } break; \
-    default: break;                                         \
+    default: break;                                                \
   }
 
-#define TGT_DISPATCH_LPH(T, lph, g, CALL)              \
-  switch (lph) {                                       \
-    case 1: TGT_DISPATCH_G(T, 1, g, CALL) break;       \
-    case 2: TGT_DISPATCH_G(T, 2, g, CALL) break;       \
-    case 4: TGT_DISPATCH_G(T, 4, g, CALL) break;       \
-    case 8: TGT_DISPATCH_G(T, 8, g, CALL) break;       \
-    case 16: TGT_DISPATCH_G(T, 16, g, CALL) break;     \
-    case 32: TGT_DISPATCH_G(T, 32, g, CALL) break;     \
-    default: break;                                    \
+#define TGT_DISPATCH_LPH(T, lph, g, CALL)          \
+  switch (lph) {                                   \
+    case 1: TGT_DISPATCH_G(T, 1, g, CALL) break;   \
+    case 2: TGT_DISPATCH_G(T, 2, g, CALL) break;   \
+    case 4: TGT_DISPATCH_G(T, 4, g, CALL) break;   \
+    case 8: TGT_DISPATCH_G(T, 8, g, CALL) break;   \
+    case 16: TGT_DISPATCH_G(T, 16, g, CALL) break; \
+    case 32: TGT_DISPATCH_G(T, 32, g, CALL) break; \
+    default: break;                                \
   }
 
-#define TGT_DISPATCH(dtype, lph, g, CALL)                       \
-  do {                                                          \
-    if ((dtype) == TGT_F32) {                                   \
-      TGT_DISPATCH_LPH(float, lph, g, CALL)                     \
-    } else {                                                    \
-      TGT_DISPATCH_LPH(__nv_bfloat16, lph, g, CALL)             \
-    }                                                           \
+#define TGT_DISPATCH(dtype, lph, g, CALL)           \
+  do {                                              \
+    if ((dtype) == TGT_F32) {                       \
+      TGT_DISPATCH_LPH(float, lph, g, CALL)         \
+    } else {                                        \
+      TGT_DISPATCH_LPH(__nv_bfloat16, lph, g, CALL) \
+    }                                               \
   } while (0)
 
 int check_layout(const tgt_layout* L, const char* name);
+
+// Tiling of one pass: edges per lane group, number of tiles, bytes of cross-tile carry.
+struct TilePlan {
+  int ge;
+  int n_tiles;
+  size_t carry_bytes;
+};
+TilePlan plan_tiles(int64_t n_edges, const HeadSplit& hs, int nacc, int ctas_per_sm);
+
+// Shared-memory bytes walk_tile needs (indices + carries), as the kernels declare them.
+template <int G, int NACC>
+struct TileSmem {
+  static constexpr int TE = TileGeom<G>::TE_MAX;
+  static constexpr int NG = TileGeom<G>::NG;
+  int32_t other[TE];
+  int32_t seg[TE + 4];
+  int32_t perm[TE];
+  float carry[NG * 2 * G * NACC];
+  int32_t carry_row[NG * 2];
+};
 
 }  // namespace tgt

@@ -1,4 +1,5 @@
 // Error reporting, version and layout validation shared by every entry point of the C ABI.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -8,7 +9,8 @@ namespace tgt {
 
 namespace {
 thread_local char g_error[512] = "";
-}
+std::atomic<int> g_forced_ge{0};
+}  // namespace
 
 int set_error(int code, const char* fmt, ...) {
   va_list ap;
@@ -18,25 +20,29 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 
+int forced_ge() { return g_forced_ge.load(std::memory_order_relaxed); }
+
 int check_layout(const tgt_layout* L, const char* name) {
   if (L == nullptr) return set_error(TGT_ERR_INVALID, "%s is null", name);
   if (L->n_rows < 0 || L->n_edges < 0 || L->n_rows >= (int64_t(1) << 31) - 1 ||
       L->n_edges >= (int64_t(1) << 31) - 1)
     return set_error(TGT_ERR_INVALID, "%s: n_rows/n_edges out of range", name);
-  if (L->chunk_edges < 1) return set_error(TGT_ERR_INVALID, "%s: chunk_edges must be >= 1", name);
-  if (L->n_chunks < 0 || L->n_hubs < 0 || L->n_hubs > L->n_chunks)
-    return set_error(TGT_ERR_INVALID, "%s: inconsistent hub counts", name);
+  if (L->n_edges > 0 && L->n_rows == 0)
+    return set_error(TGT_ERR_INVALID, "%s: edges without rows", name);
   if (L->n_rows > 0 && L->ptr == nullptr) return set_error(TGT_ERR_INVALID, "%s: ptr is null", name);
-  if (L->n_edges > 0 && (L->other == nullptr || L->perm == nullptr))
-    return set_error(TGT_ERR_INVALID, "%s: other/perm is null", name);
-  if (L->n_chunks > 0 && (L->chunk_row == nullptr || L->chunk_begin == nullptr ||
-                          L->hub_row == nullptr || L->hub_chunk_ptr == nullptr))
-    return set_error(TGT_ERR_INVALID, "%s: hub arrays are null", name);
+  if (L->n_edges > 0 && (L->other == nullptr || L->perm == nullptr || L->seg == nullptr))
+    return set_error(TGT_ERR_INVALID, "%s: other/perm/seg is null", name);
   return TGT_OK;
 }
 
 }  // namespace tgt
 
-extern "C" int tgt_version(void) { return 100; }
+extern "C" int tgt_version(void) { return 101; }
 
 extern "C" const char* tgt_last_error(void) { return tgt::g_error; }
+
+extern "C" int tgt_debug_set_tile_edges(int edges_per_lane_group) {
+  TGT_CHECK_ARG(edges_per_lane_group >= 0, "edges_per_lane_group must be >= 0");
+  tgt::g_forced_ge.store(edges_per_lane_group, std::memory_order_relaxed);
+  return TGT_OK;
+}

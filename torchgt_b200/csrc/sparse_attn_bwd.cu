@@ -1,13 +1,15 @@
-// Backward of the sparse graph attention in two atomics-free passes that recompute the scores:
-//   pass A walks edges grouped by destination: dQ, dbias and the per-row statistics
-//          stats[d,h] = { 1/(Z+1e-6), dO_d . O_d };
-//   pass B walks edges grouped by source: dK and dV (reads the statistics of each destination).
+// Backward of the sparse graph attention: a row-statistics pre-pass and two atomics-free passes that
+// recompute the scores.
+//   stats : stats[d,h] = { 1/(Z+1e-6), dO_d . O_d }                       (streams dO and O once)
+//   pass A: edges sorted by destination -> dQ and dbias
+//   pass B: edges sorted by source      -> dK and dV
 // With G = dO, inv = 1/(Z+1e-6), w = exp(clamp(raw)+bias):
 //   dw = (G_d.V_s - G_d.O_d) * inv_d      dV_s += w * inv_d * G_d      dt = dw * w  (= dbias)
 //   da = dt * [-5 <= raw <= 5]            dQ_d += da * K_s / sqrt(D)   dK_s += da * Q_d / sqrt(D)
 #include "attn_common.cuh"
 
 namespace tgt {
+
 namespace {
 
 struct BwdParams {
@@ -24,290 +26,334 @@ struct BwdParams {
   void* dv;
   float* dbias;
   float2* stats;  // [n_rows, heads]
-  float* part;    // chunk partials of the running pass
-  tgt_layout L;   // by_dst in pass A, by_src in pass B
-  int heads;
-  int row_elems;
+  int heads, row_elems;
+  int64_t n_rows;
   float inv_scale;
-  int chunk_mode;
-  int lpr_log2;
+  SegWalk walk;
 };
 
-template <int VEC>
-__device__ __forceinline__ void zero(float (&a)[VEC]) {
+// ---- row statistics ---------------------------------------------------------------------------
+// One lane per 16-byte chunk of a row; the LPH lanes of a head are adjacent.
+template <typename T, int LPH>
+__global__ void __launch_bounds__(256) bwd_stats_kernel(const BwdParams p) {
+  constexpr int VEC = Vec16<T>::kElems;
+  const int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  const int chunks = p.row_elems / VEC;
+  const int64_t total = p.n_rows * chunks;
+  const bool live = idx < total;
+  float g[VEC], o[VEC];
 #pragma unroll
-  for (int j = 0; j < VEC; ++j) a[j] = 0.f;
+  for (int j = 0; j < VEC; ++j) g[j] = o[j] = 0.f;
+  if (live) {
+    Vec16<T>::load(static_cast<const T*>(p.dout) + idx * VEC, g);
+    Vec16<T>::load(static_cast<const T*>(p.out) + idx * VEC, o);
+  }
+  const float delta = group_sum<LPH>(dot<VEC>(g, o));
+  if (live && (idx % LPH) == 0) {
+    const int64_t row = idx / chunks;
+    const int head = int(idx % chunks) / LPH;
+    const float zr = __ldg(p.z + row * p.heads + head);
+    p.stats[row * p.heads + head] = make_float2(1.0f / (zr + kZEps), delta);
+  }
 }
 
-template <int VEC>
-__device__ __forceinline__ void store_partial(float* dst, const float (&a)[VEC]) {
+// ---- pass A: dQ and dbias -----------------------------------------------------------------------
+template <typename T, int LPH, int G>
+struct DqPolicy {
+  static constexpr int VEC = Vec16<T>::kElems;
+  static constexpr int NACC = VEC;
+
+  const T* __restrict__ q;
+  const T* __restrict__ k;
+  const T* __restrict__ v;
+  const T* __restrict__ dout;
+  const float2* __restrict__ stats;
+  const float* __restrict__ bias;
+  float* __restrict__ dbias;
+  T* __restrict__ dq;
+  int bias_stride, bias_off;
+  int row_elems, heads, col0, head;
+  bool head_leader, group_leader;
+  float inv_scale;
+
+  struct Operands {
+    float k[VEC], v[VEC], q[VEC], g[VEC];
+    float2 st;
+    float b;
+  };
+  struct Scalars {
+    float da;
+  };
+
+  __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
+    const int64_t so = int64_t(src) * row_elems + col0;
+    const int64_t ro = int64_t(row) * row_elems + col0;
+    Vec16<T>::load(k + so, o.k);
+    Vec16<T>::load(v + so, o.v);
+    Vec16<T>::load(q + ro, o.q);
+    Vec16<T>::load(dout + ro, o.g);
+    o.st = __ldg(stats + int64_t(row) * heads + head);
+    o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
+  }
+  __device__ __forceinline__ void clear(Operands& o) const {
 #pragma unroll
-  for (int j = 0; j < VEC; j += 4)
-    *reinterpret_cast<float4*>(dst + j) = make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]);
+    for (int j = 0; j < VEC; ++j) o.k[j] = o.v[j] = o.q[j] = o.g[j] = 0.f;
+    o.st = make_float2(0.f, 0.f);
+    o.b = 0.f;
+  }
+  __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int pe) const {
+    const float raw = group_sum<LPH>(dot<VEC>(o.q, o.k)) * inv_scale;
+    const float gv = group_sum<LPH>(dot<VEC>(o.g, o.v));
+    const float wgt = fast_exp(clamp_score(raw) + o.b);
+    const float dt = valid ? (gv - o.st.y) * o.st.x * wgt : 0.f;
+    if (dbias != nullptr) {
+      if (bias_stride == 1) {
+        // every head's dt sits on LPH lanes, so the group sum counts it LPH times
+        const float s = group_sum<G>(dt) * (1.0f / LPH);
+        if (valid && group_leader) dbias[pe] = s;
+      } else if (valid && head_leader) {
+        dbias[int64_t(pe) * bias_stride + head] = dt;
+      }
+    }
+    Scalars s;
+    s.da = clamp_passes_grad(raw) ? dt : 0.f;
+    return s;
+  }
+  __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
+                                             const Scalars& s) const {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = fmaf(s.da, o.k[j], acc[j]);
+  }
+  __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {
+    float o[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o[j] = acc[j] * inv_scale;
+    Vec16<T>::store(dq + int64_t(row) * row_elems + col0, o);
+  }
+  __device__ __forceinline__ void zero_row(int row) const {
+    float o[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o[j] = 0.f;
+    Vec16<T>::store(dq + int64_t(row) * row_elems + col0, o);
+  }
+};
+
+// ---- pass B: dK and dV --------------------------------------------------------------------------
+template <typename T, int LPH, int G>
+struct DkvPolicy {
+  static constexpr int VEC = Vec16<T>::kElems;
+  static constexpr int NACC = 2 * VEC;  // dK then dV
+
+  const T* __restrict__ q;
+  const T* __restrict__ k;
+  const T* __restrict__ v;
+  const T* __restrict__ dout;
+  const float2* __restrict__ stats;
+  const float* __restrict__ bias;
+  T* __restrict__ dk;
+  T* __restrict__ dv;
+  int bias_stride, bias_off;
+  int row_elems, heads, col0, head;
+  float inv_scale;
+
+  struct Operands {
+    float q[VEC], g[VEC], k[VEC], v[VEC];
+    float2 st;
+    float b;
+  };
+  struct Scalars {
+    float da, wi;
+  };
+
+  // `row` is the source (K/V row), `dst` the destination whose Q, dO and statistics are gathered
+  __device__ __forceinline__ void load(Operands& o, int row, int dst, int pe) const {
+    const int64_t d = int64_t(dst) * row_elems + col0;
+    const int64_t ro = int64_t(row) * row_elems + col0;
+    Vec16<T>::load(q + d, o.q);
+    Vec16<T>::load(dout + d, o.g);
+    Vec16<T>::load(k + ro, o.k);
+    Vec16<T>::load(v + ro, o.v);
+    o.st = __ldg(stats + int64_t(dst) * heads + head);
+    o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
+  }
+  __device__ __forceinline__ void clear(Operands& o) const {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o.k[j] = o.v[j] = o.q[j] = o.g[j] = 0.f;
+    o.st = make_float2(0.f, 0.f);
+    o.b = 0.f;
+  }
+  __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
+    const float raw = group_sum<LPH>(dot<VEC>(o.q, o.k)) * inv_scale;
+    const float gv = group_sum<LPH>(dot<VEC>(o.g, o.v));
+    const float wgt = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
+    const float dt = (gv - o.st.y) * o.st.x * wgt;
+    Scalars s;
+    s.da = clamp_passes_grad(raw) ? dt : 0.f;
+    s.wi = wgt * o.st.x;
+    return s;
+  }
+  __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
+                                             const Scalars& s) const {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      acc[j] = fmaf(s.da, o.q[j], acc[j]);
+      acc[VEC + j] = fmaf(s.wi, o.g[j], acc[VEC + j]);
+    }
+  }
+  __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {
+    float a[VEC], b[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      a[j] = acc[j] * inv_scale;
+      b[j] = acc[VEC + j];
+    }
+    const int64_t off = int64_t(row) * row_elems + col0;
+    Vec16<T>::store(dk + off, a);
+    Vec16<T>::store(dv + off, b);
+  }
+  __device__ __forceinline__ void zero_row(int row) const {
+    float o[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o[j] = 0.f;
+    const int64_t off = int64_t(row) * row_elems + col0;
+    Vec16<T>::store(dk + off, o);
+    Vec16<T>::store(dv + off, o);
+  }
+};
+
+template <typename T, int LPH, int G>
+__device__ __forceinline__ DqPolicy<T, LPH, G> make_dq_policy(const BwdParams& p) {
+  constexpr int VEC = Vec16<T>::kElems;
+  const int c = threadIdx.x % G;
+  DqPolicy<T, LPH, G> pol;
+  pol.q = static_cast<const T*>(p.q);
+  pol.k = static_cast<const T*>(p.k);
+  pol.v = static_cast<const T*>(p.v);
+  pol.dout = static_cast<const T*>(p.dout);
+  pol.stats = p.stats;
+  pol.bias = p.bias;
+  pol.dbias = p.dbias;
+  pol.dq = static_cast<T*>(p.dq);
+  pol.head = blockIdx.y * (G / LPH) + c / LPH;
+  pol.bias_stride = p.bias_heads;
+  pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
+  pol.row_elems = p.row_elems;
+  pol.heads = p.heads;
+  pol.col0 = (blockIdx.y * G + c) * VEC;
+  pol.head_leader = c % LPH == 0;
+  pol.group_leader = c == 0;
+  pol.inv_scale = p.inv_scale;
+  return pol;
 }
 
-// ---- pass A: dQ, dbias, row statistics -----------------------------------------------------
+template <typename T, int LPH, int G>
+__device__ __forceinline__ DkvPolicy<T, LPH, G> make_dkv_policy(const BwdParams& p) {
+  constexpr int VEC = Vec16<T>::kElems;
+  const int c = threadIdx.x % G;
+  DkvPolicy<T, LPH, G> pol;
+  pol.q = static_cast<const T*>(p.q);
+  pol.k = static_cast<const T*>(p.k);
+  pol.v = static_cast<const T*>(p.v);
+  pol.dout = static_cast<const T*>(p.dout);
+  pol.stats = p.stats;
+  pol.bias = p.bias;
+  pol.dk = static_cast<T*>(p.dk);
+  pol.dv = static_cast<T*>(p.dv);
+  pol.head = blockIdx.y * (G / LPH) + c / LPH;
+  pol.bias_stride = p.bias_heads;
+  pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
+  pol.row_elems = p.row_elems;
+  pol.heads = p.heads;
+  pol.col0 = (blockIdx.y * G + c) * VEC;
+  pol.inv_scale = p.inv_scale;
+  return pol;
+}
+
 template <typename T, int LPH, int G>
 __global__ void __launch_bounds__(kBlockThreads) bwd_dq_kernel(const BwdParams p) {
-  constexpr int VEC = Vec16<T>::kElems;
-  const Walk w = make_walk<G>(p.L, p.chunk_mode != 0, p.lpr_log2);
-  const int col0 = (blockIdx.y * G + w.c) * VEC;
-  const int head = blockIdx.y * (G / LPH) + w.c / LPH;
-  const T* __restrict__ K = static_cast<const T*>(p.k);
-  const T* __restrict__ V = static_cast<const T*>(p.v);
-
-  float q[VEC], g[VEC], o[VEC];
-  zero<VEC>(q); zero<VEC>(g); zero<VEC>(o);
-  float zrow = 0.f;
-  if (w.row >= 0) {
-    const int64_t off = int64_t(w.row) * p.row_elems + col0;
-    Vec16<T>::load(static_cast<const T*>(p.q) + off, q);
-    Vec16<T>::load(static_cast<const T*>(p.dout) + off, g);
-    Vec16<T>::load(static_cast<const T*>(p.out) + off, o);
-    zrow = __ldg(p.z + int64_t(w.row) * p.heads + head);
-  }
-  const float inv = 1.0f / (zrow + kZEps);
-  const float delta = group_sum<LPH>(dot<VEC>(g, o));
-  if (!p.chunk_mode && w.row >= 0 && w.slot == 0 && w.c % LPH == 0)
-    p.stats[int64_t(w.row) * p.heads + head] = make_float2(inv, delta);
-
-  float dq[VEC];
-  zero<VEC>(dq);
-  const int32_t* __restrict__ other = p.L.other;
-  const int32_t* __restrict__ perm = p.L.perm;
-  const bool need_perm = p.bias != nullptr || p.dbias != nullptr;
-  const int bias_stride = p.bias_heads;
-  const int bias_off = p.bias_heads > 1 ? head : 0;
-
-  int e = w.begin;
-  for (int it = 0; it < w.iters; it += kUnroll) {
-    int src[kUnroll], pe[kUnroll];
-    float b[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int ee = e + u * w.nslots;
-      src[u] = (ee < w.end) ? __ldg(other + ee) : -1;
-      pe[u] = (need_perm && ee < w.end) ? __ldg(perm + ee) : 0;
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      b[u] = 0.f;
-      if (p.bias != nullptr && src[u] >= 0)
-        b[u] = __ldg(p.bias + int64_t(pe[u]) * bias_stride + bias_off);
-    }
-    float kk[kUnroll][VEC], vv[kUnroll][VEC];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      if (src[u] >= 0) {
-        const int64_t off = int64_t(src[u]) * p.row_elems + col0;
-        Vec16<T>::load(K + off, kk[u]);
-        Vec16<T>::load(V + off, vv[u]);
-      } else {
-        zero<VEC>(kk[u]);
-        zero<VEC>(vv[u]);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const float raw = group_sum<LPH>(dot<VEC>(q, kk[u])) * p.inv_scale;
-      const float gv = group_sum<LPH>(dot<VEC>(g, vv[u]));
-      const float wgt = expf(clamp_score(raw) + b[u]);
-      float dt = (gv - delta) * inv * wgt;
-      if (src[u] < 0) dt = 0.f;
-      const float da = clamp_passes_grad(raw) ? dt : 0.f;
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) dq[j] = fmaf(da, kk[u][j], dq[j]);
-      if (p.dbias != nullptr) {
-        if (p.bias_heads == 1) {
-          // every head's dt sits on LPH lanes; the group sum counts it LPH times
-          const float s = group_sum<G>(dt) * (1.0f / LPH);
-          if (src[u] >= 0 && w.c == 0) p.dbias[pe[u]] = s;
-        } else if (src[u] >= 0 && w.c % LPH == 0) {
-          p.dbias[int64_t(pe[u]) * bias_stride + head] = dt;
-        }
-      }
-    }
-    e += kUnroll * w.nslots;
-  }
-
-  const int lpr = p.chunk_mode ? 32 : (1 << p.lpr_log2);
-#pragma unroll
-  for (int j = 0; j < VEC; ++j) dq[j] = slot_sum<G>(dq[j], lpr);
-  if (w.row < 0 || w.is_hub || w.slot != 0) return;
-  if (p.chunk_mode) {
-    store_partial<VEC>(p.part + int64_t(w.chunk) * p.row_elems + col0, dq);
-  } else {
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) dq[j] *= p.inv_scale;
-    Vec16<T>::store(static_cast<T*>(p.dq) + int64_t(w.row) * p.row_elems + col0, dq);
-  }
+  using Policy = DqPolicy<T, LPH, G>;
+  __shared__ TileSmem<G, Policy::NACC> sm;
+  const Policy pol = make_dq_policy<T, LPH, G>(p);
+  walk_tile<G, Policy>(p.walk, pol, sm.other, sm.seg, sm.perm, sm.carry, sm.carry_row);
 }
 
-// ---- pass B: dK, dV --------------------------------------------------------------------------
+template <typename T, int LPH, int G>
+__global__ void __launch_bounds__(kBlockThreads) bwd_dq_stitch_kernel(const BwdParams p) {
+  using Policy = DqPolicy<T, LPH, G>;
+  const Policy pol = make_dq_policy<T, LPH, G>(p);
+  stitch_tiles<G, Policy>(p.walk, pol);
+}
+
 template <typename T, int LPH, int G>
 __global__ void __launch_bounds__(kBlockThreads) bwd_dkv_kernel(const BwdParams p) {
-  constexpr int VEC = Vec16<T>::kElems;
-  const Walk w = make_walk<G>(p.L, p.chunk_mode != 0, p.lpr_log2);
-  const int col0 = (blockIdx.y * G + w.c) * VEC;
-  const int head = blockIdx.y * (G / LPH) + w.c / LPH;
-  const T* __restrict__ Q = static_cast<const T*>(p.q);
-  const T* __restrict__ DO = static_cast<const T*>(p.dout);
-
-  float k[VEC], v[VEC];
-  zero<VEC>(k); zero<VEC>(v);
-  if (w.row >= 0 && !w.is_hub) {
-    const int64_t off = int64_t(w.row) * p.row_elems + col0;
-    Vec16<T>::load(static_cast<const T*>(p.k) + off, k);
-    Vec16<T>::load(static_cast<const T*>(p.v) + off, v);
-  }
-
-  float dk[VEC], dv[VEC];
-  zero<VEC>(dk); zero<VEC>(dv);
-  const int32_t* __restrict__ other = p.L.other;
-  const int32_t* __restrict__ perm = p.L.perm;
-  const int bias_stride = p.bias_heads;
-  const int bias_off = p.bias_heads > 1 ? head : 0;
-
-  int e = w.begin;
-  for (int it = 0; it < w.iters; it += kUnroll) {
-    int dst[kUnroll];
-    float b[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int ee = e + u * w.nslots;
-      dst[u] = (ee < w.end) ? __ldg(other + ee) : -1;
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int ee = e + u * w.nslots;
-      b[u] = 0.f;
-      if (p.bias != nullptr && dst[u] >= 0)
-        b[u] = __ldg(p.bias + int64_t(__ldg(perm + ee)) * bias_stride + bias_off);
-    }
-    float qq[kUnroll][VEC], gg[kUnroll][VEC];
-    float2 st[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      if (dst[u] >= 0) {
-        const int64_t off = int64_t(dst[u]) * p.row_elems + col0;
-        Vec16<T>::load(Q + off, qq[u]);
-        Vec16<T>::load(DO + off, gg[u]);
-        st[u] = __ldg(p.stats + int64_t(dst[u]) * p.heads + head);
-      } else {
-        zero<VEC>(qq[u]);
-        zero<VEC>(gg[u]);
-        st[u] = make_float2(0.f, 0.f);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const float raw = group_sum<LPH>(dot<VEC>(qq[u], k)) * p.inv_scale;
-      const float gv = group_sum<LPH>(dot<VEC>(gg[u], v));
-      float wgt = expf(clamp_score(raw) + b[u]);
-      if (dst[u] < 0) wgt = 0.f;
-      const float dt = (gv - st[u].y) * st[u].x * wgt;
-      const float da = clamp_passes_grad(raw) ? dt : 0.f;
-      const float wi = wgt * st[u].x;
-#pragma unroll
-      for (int j = 0; j < VEC; ++j) {
-        dv[j] = fmaf(wi, gg[u][j], dv[j]);
-        dk[j] = fmaf(da, qq[u][j], dk[j]);
-      }
-    }
-    e += kUnroll * w.nslots;
-  }
-
-  const int lpr = p.chunk_mode ? 32 : (1 << p.lpr_log2);
-#pragma unroll
-  for (int j = 0; j < VEC; ++j) {
-    dk[j] = slot_sum<G>(dk[j], lpr);
-    dv[j] = slot_sum<G>(dv[j], lpr);
-  }
-  if (w.row < 0 || w.is_hub || w.slot != 0) return;
-  if (p.chunk_mode) {
-    float* base = p.part + int64_t(w.chunk) * 2 * p.row_elems + col0;
-    store_partial<VEC>(base, dk);
-    store_partial<VEC>(base + p.row_elems, dv);
-  } else {
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) dk[j] *= p.inv_scale;
-    const int64_t off = int64_t(w.row) * p.row_elems + col0;
-    Vec16<T>::store(static_cast<T*>(p.dk) + off, dk);
-    Vec16<T>::store(static_cast<T*>(p.dv) + off, dv);
-  }
+  using Policy = DkvPolicy<T, LPH, G>;
+  __shared__ TileSmem<G, Policy::NACC> sm;
+  const Policy pol = make_dkv_policy<T, LPH, G>(p);
+  walk_tile<G, Policy>(p.walk, pol, sm.other, sm.seg, sm.perm, sm.carry, sm.carry_row);
 }
 
-// Sum chunk partials of each hub row in chunk order; n_out tensors are interleaved per chunk.
-template <typename T>
-__global__ void __launch_bounds__(kBlockThreads)
-bwd_hub_reduce_kernel(const tgt_layout L, const float* __restrict__ part, int n_out, void* out0,
-                      void* out1, float scale0, float scale1, int row_elems) {
-  const int hub = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (hub >= L.n_hubs) return;
-  const int lane = threadIdx.x & 31;
-  const int col = (blockIdx.y * 32 + lane) * 4;
-  if (col >= row_elems) return;
-  const int row = __ldg(L.hub_row + hub);
-  const int c0 = __ldg(L.hub_chunk_ptr + hub), c1 = __ldg(L.hub_chunk_ptr + hub + 1);
-  for (int t = 0; t < n_out; ++t) {
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c = c0; c < c1; ++c) {
-      const float4 x = *reinterpret_cast<const float4*>(
-          part + (int64_t(c) * n_out + t) * row_elems + col);
-      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
-    }
-    const float s = t == 0 ? scale0 : scale1;
-    T* o = static_cast<T*>(t == 0 ? out0 : out1) + int64_t(row) * row_elems + col;
-    if constexpr (sizeof(T) == 4) {
-      *reinterpret_cast<float4*>(o) = make_float4(a.x * s, a.y * s, a.z * s, a.w * s);
-    } else {
-      const __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * s, a.y * s);
-      const __nv_bfloat162 hi = __floats2bfloat162_rn(a.z * s, a.w * s);
-      uint2 pk;
-      pk.x = *reinterpret_cast<const uint32_t*>(&lo);
-      pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-      *reinterpret_cast<uint2*>(o) = pk;
-    }
-  }
+template <typename T, int LPH, int G>
+__global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const BwdParams p) {
+  using Policy = DkvPolicy<T, LPH, G>;
+  const Policy pol = make_dkv_policy<T, LPH, G>(p);
+  stitch_tiles<G, Policy>(p.walk, pol);
 }
+
+constexpr int kDqCtasPerSm = 4;
+constexpr int kDkvCtasPerSm = 4;
 
 struct BwdScratch {
-  size_t stats, part_a, part_b, total;
+  size_t stats, carry_a, carry_b, total;
+  TilePlan plan_a, plan_b;
 };
 
-BwdScratch plan_bwd_scratch(const tgt_layout* by_dst, const tgt_layout* by_src, int heads,
-                            int head_dim) {
+BwdScratch plan_bwd_scratch(const tgt_layout* by_dst, const HeadSplit& hs, int heads, int dtype) {
   BwdScratch s;
-  const size_t row = size_t(heads) * head_dim * 4;
+  const int vec = dtype == TGT_F32 ? 4 : 8;
+  s.plan_a = plan_tiles(by_dst->n_edges, hs, vec, kDqCtasPerSm);
+  s.plan_b = plan_tiles(by_dst->n_edges, hs, 2 * vec, kDkvCtasPerSm);
   size_t off = 0;
   s.stats = off; off += round_up(size_t(by_dst->n_rows) * heads * 8, 256);
-  s.part_a = off; off += round_up(size_t(by_dst->n_chunks) * row, 256);
-  s.part_b = off; off += round_up(size_t(by_src->n_chunks) * 2 * row, 256);
+  s.carry_a = off; off += s.plan_a.carry_bytes;
+  s.carry_b = off; off += s.plan_b.carry_bytes;
   s.total = off;
   return s;
 }
 
+void fill_walk(SegWalk* w, const tgt_layout& L, const TilePlan& tp, float* carry, bool need_perm) {
+  w->ptr = L.ptr; w->other = L.other; w->perm = L.perm; w->seg = L.seg;
+  w->n_rows = int(L.n_rows); w->n_edges = int(L.n_edges);
+  w->ge = tp.ge; w->n_tiles = tp.n_tiles;
+  w->gcarry = carry;
+  w->need_perm = need_perm;
+}
+
 }  // namespace
 
-size_t fwd_scratch_bytes(const tgt_layout* L, int heads, int head_dim);
+size_t fwd_scratch_bytes(const tgt_layout* L, int heads, int head_dim, int dtype);
 
 }  // namespace tgt
 
 extern "C" int tgt_sparse_attn_scratch_bytes(const tgt_layout* by_dst, const tgt_layout* by_src,
-                                             int heads, int head_dim, int phase, size_t* bytes) {
+                                             int heads, int head_dim, int dtype, int phase,
+                                             size_t* bytes) {
   using namespace tgt;
   TGT_CHECK_ARG(bytes != nullptr, "bytes is null");
-  TGT_CHECK_ARG(heads >= 1 && head_dim >= 1, "heads and head_dim must be >= 1");
   TGT_CHECK_ARG(phase == 0 || phase == 1, "phase must be 0 (forward) or 1 (backward)");
+  TGT_CHECK_ARG(dtype == TGT_F32 || dtype == TGT_BF16, "dtype must be TGT_F32 or TGT_BF16");
   int rc = check_layout(by_dst, "by_dst");
   if (rc != TGT_OK) return rc;
+  HeadSplit hs;
+  if (!split_heads(heads, head_dim, dtype, &hs))
+    return set_error(TGT_ERR_UNSUPPORTED, "heads=%d head_dim=%d dtype=%d is not supported", heads,
+                     head_dim, dtype);
   if (phase == 0) {
-    *bytes = by_dst->n_chunks > 0 ? fwd_scratch_bytes(by_dst, heads, head_dim) : 0;
+    *bytes = fwd_scratch_bytes(by_dst, heads, head_dim, dtype);
     return TGT_OK;
   }
   rc = check_layout(by_src, "by_src");
   if (rc != TGT_OK) return rc;
-  *bytes = plan_bwd_scratch(by_dst, by_src, heads, head_dim).total;
+  *bytes = plan_bwd_scratch(by_dst, hs, heads, dtype).total;
   return TGT_OK;
 }
 
@@ -319,7 +365,7 @@ extern "C" int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* 
                                    size_t scratch_bytes, void* stream) {
   return tgt_sparse_attn_bwd_passes(dout, q, k, v, bias, bias_heads, out, z, by_dst, by_src, dq, dk,
                                     dv, dbias, heads, head_dim, dtype, scratch, scratch_bytes, stream,
-                                    3);
+                                    7);
 }
 
 extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const void* k,
@@ -330,8 +376,9 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
                                           void* scratch, size_t scratch_bytes, void* stream_,
                                           int passes) {
   using namespace tgt;
-  TGT_CHECK_ARG(passes >= 1 && passes <= 3, "passes must be 1 (dQ), 2 (dK/dV) or 3 (both)");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  TGT_CHECK_ARG(passes >= 1 && passes <= 7,
+                "passes is a bit mask: 1 = row statistics, 2 = dQ/dbias, 4 = dK/dV");
   TGT_CHECK_ARG(dtype == TGT_F32 || dtype == TGT_BF16, "dtype must be TGT_F32 or TGT_BF16");
   int rc = check_layout(by_dst, "by_dst");
   if (rc != TGT_OK) return rc;
@@ -353,13 +400,24 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
     return set_error(TGT_ERR_UNSUPPORTED,
                      "a per-edge scalar dbias needs all heads in one lane group (heads*head_dim "
                      "<= 512 bytes, heads a power of two); pass a per-head bias instead");
-  if (by_dst->n_rows == 0) return TGT_OK;
+  const int64_t n_rows = by_dst->n_rows, n_edges = by_dst->n_edges;
+  if (n_rows == 0) return TGT_OK;
   TGT_CHECK_ARG(dout && q && k && v && out && z && dq && dk && dv, "tensor pointers must not be null");
   TGT_CHECK_ARG(aligned16(dout) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
                     aligned16(z) && aligned16(dq) && aligned16(dk) && aligned16(dv) &&
                     aligned16(bias) && aligned16(dbias) && aligned16(scratch),
                 "device pointers must be 16-byte aligned");
-  const BwdScratch sc = plan_bwd_scratch(by_dst, by_src, heads, head_dim);
+  const size_t elem = dtype == TGT_F32 ? 4 : 2;
+  const size_t tensor_bytes = size_t(n_rows) * heads * head_dim * elem;
+  if (n_edges == 0) {  // no edges: all gradients vanish
+    if (passes & 2) TGT_CHECK_CUDA(cudaMemsetAsync(dq, 0, tensor_bytes, stream));
+    if (passes & 4) {
+      TGT_CHECK_CUDA(cudaMemsetAsync(dk, 0, tensor_bytes, stream));
+      TGT_CHECK_CUDA(cudaMemsetAsync(dv, 0, tensor_bytes, stream));
+    }
+    return TGT_OK;
+  }
+  const BwdScratch sc = plan_bwd_scratch(by_dst, hs, heads, dtype);
   if (scratch == nullptr || scratch_bytes < sc.total)
     return set_error(TGT_ERR_WORKSPACE, "scratch holds %zu bytes, %zu needed", scratch_bytes,
                      sc.total);
@@ -372,64 +430,44 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
   p.stats = reinterpret_cast<float2*>(base + sc.stats);
   p.heads = heads;
   p.row_elems = heads * head_dim;
+  p.n_rows = n_rows;
   p.inv_scale = 1.0f / sqrtf(float(head_dim));
-  const dim3 reduce_y((p.row_elems + 127) / 128);
 
-#define TGT_LAUNCH_DQ(T, LPH, G) bwd_dq_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
-#define TGT_LAUNCH_DKV(T, LPH, G) bwd_dkv_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
-
-  // ---- pass A over destinations
   if (passes & 1) {
-    const tgt_layout& L = *by_dst;
-    p.L = L;
-    p.part = reinterpret_cast<float*>(base + sc.part_a);
-    p.lpr_log2 = choose_lpr_log2(hs.g, double(L.n_edges) / double(L.n_rows));
-    if (L.n_chunks > 0) {
-      p.chunk_mode = 1;
-      dim3 grid((L.n_chunks + kWarpsPerBlock - 1) / kWarpsPerBlock, hs.groups);
-      TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQ);
-    }
-    p.chunk_mode = 0;
-    const int64_t rows_per_block = int64_t(kWarpsPerBlock) * (32 >> p.lpr_log2);
-    dim3 grid(unsigned((L.n_rows + rows_per_block - 1) / rows_per_block), hs.groups);
-    TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQ);
-    if (L.n_hubs > 0) {
-      dim3 rgrid((L.n_hubs + kWarpsPerBlock - 1) / kWarpsPerBlock, reduce_y.x);
-      if (dtype == TGT_F32)
-        bwd_hub_reduce_kernel<float><<<rgrid, kBlockThreads, 0, stream>>>(
-            L, p.part, 1, dq, nullptr, p.inv_scale, 0.f, p.row_elems);
-      else
-        bwd_hub_reduce_kernel<__nv_bfloat16><<<rgrid, kBlockThreads, 0, stream>>>(
-            L, p.part, 1, dq, nullptr, p.inv_scale, 0.f, p.row_elems);
-    }
+    const int64_t lanes = n_rows * (p.row_elems / (dtype == TGT_F32 ? 4 : 8));
+    const unsigned blocks = unsigned((lanes + 255) / 256);
+#define TGT_LAUNCH_STATS(T, LPH, G) bwd_stats_kernel<T, LPH><<<blocks, 256, 0, stream>>>(p)
+    TGT_DISPATCH(dtype, hs.lph, hs.lph, TGT_LAUNCH_STATS);
+#undef TGT_LAUNCH_STATS
   }
-  // ---- pass B over sources
   if (passes & 2) {
-    const tgt_layout& L = *by_src;
-    p.L = L;
-    p.part = reinterpret_cast<float*>(base + sc.part_b);
-    p.lpr_log2 = choose_lpr_log2(hs.g, double(L.n_edges) / double(L.n_rows));
-    if (L.n_chunks > 0) {
-      p.chunk_mode = 1;
-      dim3 grid((L.n_chunks + kWarpsPerBlock - 1) / kWarpsPerBlock, hs.groups);
-      TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DKV);
-    }
-    p.chunk_mode = 0;
-    const int64_t rows_per_block = int64_t(kWarpsPerBlock) * (32 >> p.lpr_log2);
-    dim3 grid(unsigned((L.n_rows + rows_per_block - 1) / rows_per_block), hs.groups);
-    TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DKV);
-    if (L.n_hubs > 0) {
-      dim3 rgrid((L.n_hubs + kWarpsPerBlock - 1) / kWarpsPerBlock, reduce_y.x);
-      if (dtype == TGT_F32)
-        bwd_hub_reduce_kernel<float><<<rgrid, kBlockThreads, 0, stream>>>(
-            L, p.part, 2, dk, dv, p.inv_scale, 1.0f, p.row_elems);
-      else
-        bwd_hub_reduce_kernel<__nv_bfloat16><<<rgrid, kBlockThreads, 0, stream>>>(
-            L, p.part, 2, dk, dv, p.inv_scale, 1.0f, p.row_elems);
-    }
-  }
+    fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a),
+              bias != nullptr || dbias != nullptr);
+    const dim3 grid(sc.plan_a.n_tiles, hs.groups);
+    const dim3 sgrid((sc.plan_a.n_tiles + kBlockThreads / 32 - 1) / (kBlockThreads / 32), hs.groups);
+#define TGT_LAUNCH_DQ(T, LPH, G)                                               \
+  do {                                                                         \
+    bwd_dq_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);           \
+    if (sc.plan_a.n_tiles > 1)                                                 \
+      bwd_dq_stitch_kernel<T, LPH, G><<<sgrid, kBlockThreads, 0, stream>>>(p); \
+  } while (0)
+    TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQ);
 #undef TGT_LAUNCH_DQ
+  }
+  if (passes & 4) {
+    fill_walk(&p.walk, *by_src, sc.plan_b, reinterpret_cast<float*>(base + sc.carry_b),
+              bias != nullptr);
+    const dim3 grid(sc.plan_b.n_tiles, hs.groups);
+    const dim3 sgrid((sc.plan_b.n_tiles + kBlockThreads / 32 - 1) / (kBlockThreads / 32), hs.groups);
+#define TGT_LAUNCH_DKV(T, LPH, G)                                               \
+  do {                                                                          \
+    bwd_dkv_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);           \
+    if (sc.plan_b.n_tiles > 1)                                                  \
+      bwd_dkv_stitch_kernel<T, LPH, G><<<sgrid, kBlockThreads, 0, stream>>>(p); \
+  } while (0)
+    TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DKV);
 #undef TGT_LAUNCH_DKV
+  }
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }

@@ -14,53 +14,32 @@ import torch
 
 from . import _cabi
 
-DEFAULT_CHUNK_EDGES = 128
-
-
 class EdgeLayout:
-    """One orientation of the graph: edges grouped by destination (``group_by=1``) or source."""
+    """One orientation of the graph: edges sorted by destination (``group_by=1``) or source (0).
 
-    def __init__(self, edge_index: torch.Tensor, n_rows: int, group_by: int, chunk_edges: int):
+    ``perm`` is the stable argsort of the grouping endpoint, ``seg`` that endpoint in sorted order,
+    ``other`` the opposite endpoint in sorted order, ``ptr`` the row pointers (all int32, on the GPU)."""
+
+    def __init__(self, edge_index: torch.Tensor, n_rows: int, group_by: int):
         lib = _cabi.load()
         dev = edge_index.device
         n_edges = int(edge_index.shape[1])
-        max_chunks, max_hubs, ws = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_size_t()
-        _cabi.check(lib.tgt_edge_layout_sizes(n_rows, n_edges, chunk_edges, ctypes.byref(max_chunks),
-                                              ctypes.byref(max_hubs), ctypes.byref(ws)))
+        ws = ctypes.c_size_t()
+        _cabi.check(lib.tgt_edge_layout_sizes(n_rows, n_edges, ctypes.byref(ws)))
         i32 = dict(dtype=torch.int32, device=dev)
         self.ptr = torch.empty(n_rows + 1, **i32)
-        self.other = torch.empty(max(n_edges, 1), **i32)
-        self.perm = torch.empty(max(n_edges, 1), **i32)
-        chunk_row = torch.empty(max_chunks.value, **i32)
-        chunk_begin = torch.empty(max_chunks.value, **i32)
-        hub_row = torch.empty(max_hubs.value, **i32)
-        hub_chunk_ptr = torch.empty(max_hubs.value + 1, **i32)
+        self.other = torch.empty(n_edges, **i32)
+        self.perm = torch.empty(n_edges, **i32)
+        self.seg = torch.empty(n_edges, **i32)
         workspace = torch.empty(max(ws.value, 16), dtype=torch.uint8, device=dev)
-        counts = (ctypes.c_int64 * 2)()
         stream = torch.cuda.current_stream(dev).cuda_stream
+        nz = lambda t: t.data_ptr() if t.numel() else None
         _cabi.check(lib.tgt_edge_layout_build(
-            edge_index.data_ptr(), n_edges, n_rows, group_by, chunk_edges, self.ptr.data_ptr(),
-            self.other.data_ptr(), self.perm.data_ptr(), chunk_row.data_ptr(), chunk_begin.data_ptr(),
-            hub_row.data_ptr(), hub_chunk_ptr.data_ptr(), counts, workspace.data_ptr(), ws.value,
-            stream))
-        self.n_rows, self.n_edges, self.group_by, self.chunk_edges = n_rows, n_edges, group_by, chunk_edges
-        self.n_chunks, self.n_hubs = int(counts[0]), int(counts[1])
-        # keep only what the graph needs (the capacity bound is ~2E/chunk_edges entries)
-        self.other = self.other[:n_edges]
-        self.perm = self.perm[:n_edges]
-        self.chunk_row = chunk_row[: self.n_chunks].clone()
-        self.chunk_begin = chunk_begin[: self.n_chunks].clone()
-        self.hub_row = hub_row[: self.n_hubs].clone()
-        self.hub_chunk_ptr = hub_chunk_ptr[: self.n_hubs + 1].clone()
-        self.c = _cabi.TgtLayout(
-            n_rows=n_rows, n_edges=n_edges, ptr=self.ptr.data_ptr(),
-            other=self.other.data_ptr() if n_edges else None,
-            perm=self.perm.data_ptr() if n_edges else None,
-            chunk_edges=chunk_edges, n_chunks=self.n_chunks, n_hubs=self.n_hubs, reserved=0,
-            chunk_row=self.chunk_row.data_ptr() if self.n_chunks else None,
-            chunk_begin=self.chunk_begin.data_ptr() if self.n_chunks else None,
-            hub_row=self.hub_row.data_ptr() if self.n_hubs else None,
-            hub_chunk_ptr=self.hub_chunk_ptr.data_ptr() if self.n_chunks else None)
+            nz(edge_index), n_edges, n_rows, group_by, self.ptr.data_ptr(), nz(self.other), nz(self.perm),
+            nz(self.seg), workspace.data_ptr(), workspace.numel(), stream))
+        self.n_rows, self.n_edges, self.group_by = n_rows, n_edges, group_by
+        self.c = _cabi.TgtLayout(n_rows=n_rows, n_edges=n_edges, ptr=self.ptr.data_ptr(), other=nz(self.other),
+                                 perm=nz(self.perm), seg=nz(self.seg))
 
     def byref(self):
         return ctypes.byref(self.c)
@@ -69,7 +48,7 @@ class EdgeLayout:
 class SparseGraph:
     """Handle holding both layouts of one batch graph.  Build once, pass in place of ``edge_index``."""
 
-    def __init__(self, edge_index: torch.Tensor, n_rows: int, chunk_edges: int = DEFAULT_CHUNK_EDGES):
+    def __init__(self, edge_index: torch.Tensor, n_rows: int):
         if edge_index.dim() != 2 or edge_index.shape[0] != 2:
             raise ValueError("edge_index must be [2, E]")
         if not edge_index.is_cuda:
@@ -78,8 +57,7 @@ class SparseGraph:
         self.n_rows = int(n_rows)
         self.n_edges = int(edge_index.shape[1])
         self.device = edge_index.device
-        self.chunk_edges = int(chunk_edges)
-        self.by_dst = EdgeLayout(edge_index, self.n_rows, 1, self.chunk_edges)
+        self.by_dst = EdgeLayout(edge_index, self.n_rows, 1)
         self._edge_index = edge_index  # kept until by_src is built
         self._by_src: Optional[EdgeLayout] = None
 
@@ -87,7 +65,7 @@ class SparseGraph:
     def by_src(self) -> EdgeLayout:
         """Built on first backward (inference never needs it)."""
         if self._by_src is None:
-            self._by_src = EdgeLayout(self._edge_index, self.n_rows, 0, self.chunk_edges)
+            self._by_src = EdgeLayout(self._edge_index, self.n_rows, 0)
             self._edge_index = None
         return self._by_src
 

@@ -28,11 +28,11 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None or t.numel() == 0 else t.data_ptr()
 
 
-def _scratch(graph: SparseGraph, heads: int, head_dim: int, phase: int, device) -> torch.Tensor:
+def _scratch(graph: SparseGraph, heads: int, head_dim: int, dtype: int, phase: int, device) -> torch.Tensor:
     lib = _cabi.load()
     n = ctypes.c_size_t()
     by_src = graph.by_src.byref() if phase == 1 else None
-    _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), by_src, heads, head_dim, phase,
+    _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), by_src, heads, head_dim, dtype, phase,
                                                   ctypes.byref(n)))
     return torch.empty(max(n.value, 16), dtype=torch.uint8, device=device)
 
@@ -45,7 +45,7 @@ class _SparseGraphAttention(torch.autograd.Function):
         out = torch.empty_like(q)
         z = torch.empty((n_rows, heads), dtype=torch.float32, device=q.device)
         bias_heads = 0 if bias is None else (1 if bias.dim() == 1 else int(bias.shape[1]))
-        scratch = _scratch(graph, heads, head_dim, 0, q.device)
+        scratch = _scratch(graph, heads, head_dim, _DTYPES[q.dtype], 0, q.device)
         _cabi.check(lib.tgt_sparse_attn_fwd(
             _ptr(q), _ptr(k), _ptr(v), _ptr(bias), bias_heads, graph.by_dst.byref(), _ptr(out), _ptr(z),
             heads, head_dim, _DTYPES[q.dtype], scratch.data_ptr(), scratch.numel(), _stream(q)))
@@ -65,7 +65,7 @@ class _SparseGraphAttention(torch.autograd.Function):
         dbias = None
         if bias is not None and ctx.needs_input_grad[3]:
             dbias = torch.empty_like(bias)
-        scratch = _scratch(graph, heads, head_dim, 1, q.device)
+        scratch = _scratch(graph, heads, head_dim, _DTYPES[q.dtype], 1, q.device)
         _cabi.check(lib.tgt_sparse_attn_bwd(
             _ptr(dout), _ptr(q), _ptr(k), _ptr(v), _ptr(bias), ctx.bias_heads, _ptr(out), _ptr(z),
             graph.by_dst.byref(), graph.by_src.byref(), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dbias), heads,
