@@ -19,6 +19,8 @@
 // reproducible results.  Rows without edges are zero-filled by the group that walks the gap.
 #pragma once
 
+#include <type_traits>
+
 #include "tgt_common.cuh"
 
 namespace tgt {
@@ -147,18 +149,17 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
   float* my_head = s_carry + (g * 2 + 0) * (G * NACC) + c * NACC;
   float* my_tail = s_carry + (g * 2 + 1) * (G * NACC) + c * NACC;
 
-  // all groups of a warp run the same number of batches (the shuffles inside need the full warp)
-  const int warp_first_group = (tid / 32) * (32 / G);
-  const int warp_gb = min(warp_first_group * w.ge, n);
-  const int batches = (min(w.ge, n - warp_gb) + kUnroll - 1) / kUnroll;
-  for (int b = 0; b < batches; ++b) {
+  // State of the segmented walk, advanced one batch of kUnroll edges at a time.  FULL = every
+  // slot of the batch holds an edge of this group's range (all tiles but the last one).
+  auto batch = [&](int first, auto full_tag) {
+    constexpr bool FULL = decltype(full_tag)::value;
     typename Policy::Operands ops[kUnroll];
     int row[kUnroll], pe[kUnroll];
     bool valid[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int i = gb + b * kUnroll + u;
-      valid[u] = i < gend;
+      const int i = first + u;
+      valid[u] = FULL || i < gend;
       const int ii = valid[u] ? i : 0;
       row[u] = s_seg[ii + 1];
       pe[u] = w.need_perm ? s_perm[ii] : 0;
@@ -189,6 +190,17 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
         pol.accumulate(acc, ops[u], sc);
       }
     }
+  };
+  if (n == te) {
+    // ge is a multiple of kUnroll, so every batch of every group is full
+    for (int first = gb; first < gend; first += kUnroll) batch(first, std::true_type{});
+  } else {
+    // last tile: all groups of a warp run the same number of batches (the shuffles inside need
+    // the full warp), slots past the group's range are padding
+    const int warp_first_group = (tid / 32) * (32 / G);
+    const int warp_gb = min(warp_first_group * w.ge, n);
+    const int batches = (min(w.ge, n - warp_gb) + kUnroll - 1) / kUnroll;
+    for (int b = 0; b < batches; ++b) batch(gb + b * kUnroll, std::false_type{});
   }
   if (gb < gend) {  // close the last row of the range
     const bool cont_out = s_seg[gend + 1] == cur;
@@ -248,16 +260,15 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
   }
 }
 
-// Second kernel: rows that cross tile boundaries.  One warp per tile; the warp of the tile in
-// which such a row STARTS adds that tile's tail carry and the head carries of the following tiles
-// in tile order and finishes the row.
+// Second kernel: rows that cross tile boundaries.  One CTA per tile; the CTA of the tile in which
+// such a row STARTS adds that tile's tail carry and the head carries of the following tiles and
+// finishes the row.  The partials are dealt round-robin to 128 / G slots, each slot adds its share
+// in tile order, then the slots are combined in a fixed tree: the order never depends on timing.
 template <int G, class Policy>
-__device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol) {
+__device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol, float* s_part) {
   constexpr int NG = TileGeom<G>::NG;
   constexpr int NACC = Policy::NACC;
-  const int tile = blockIdx.x * (kBlockThreads / 32) + (threadIdx.x >> 5);
-  if (tile >= w.n_tiles) return;
-  const int lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;
   const int te = NG * w.ge;
   const int64_t t1 = int64_t(tile + 1) * te;
   if (t1 >= w.n_edges) return;                       // last tile: nothing runs past it
@@ -266,8 +277,7 @@ __device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol
   const int row_begin = __ldg(w.ptr + r);
   if (row_begin < t1 - te) return;                   // the row started in an earlier tile
   const int last_tile = (__ldg(w.ptr + r + 1) - 1) / te;
-  constexpr int NSLOT = 32 / G;
-  const int slot = lane / G, c = lane % G;
+  const int slot = threadIdx.x / G, c = threadIdx.x % G;
   const int lanes_all = gridDim.y * G;
   const int64_t stride = int64_t(lanes_all) * NACC;
   const float* base = w.gcarry + int64_t(blockIdx.y * G + c) * NACC;
@@ -276,17 +286,30 @@ __device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol
   for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
   // partial 0 = tail carry of `tile`, partial i > 0 = head carry of tile + i
   const int n_part = last_tile - tile + 1;
-  for (int i = slot; i < n_part; i += NSLOT) {
+#pragma unroll 4
+  for (int i = slot; i < n_part; i += NG) {
     const float* p = base + (int64_t(tile + i) * 2 + (i == 0 ? 1 : 0)) * stride;
 #pragma unroll
-    for (int a = 0; a < NACC; ++a) acc[a] += p[a];
+    for (int a = 0; a < NACC; ++a) acc[a] += __ldg(p + a);
   }
+  // combine the NG slots: halving tree through shared memory
+  float* mine = s_part + (slot * G + c) * NACC;
 #pragma unroll
-  for (int a = 0; a < NACC; ++a) {
+  for (int a = 0; a < NACC; ++a) mine[a] = acc[a];
+  __syncthreads();
+  for (int half = NG / 2; half >= 1; half >>= 1) {
+    if (slot < half) {
+      const float* o = s_part + ((slot + half) * G + c) * NACC;
 #pragma unroll
-    for (int off = G; off < 32; off <<= 1) acc[a] += __shfl_xor_sync(0xffffffffu, acc[a], off);
+      for (int a = 0; a < NACC; ++a) mine[a] += o[a];
+    }
+    __syncthreads();
   }
-  if (slot == 0) pol.finalize(r, acc);
+  if (slot == 0) {
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) acc[a] = mine[a];
+    pol.finalize(r, acc);
+  }
 }
 
 struct HeadSplit {

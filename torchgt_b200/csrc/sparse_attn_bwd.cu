@@ -72,7 +72,8 @@ struct DqPolicy {
   float* __restrict__ dbias;
   T* __restrict__ dq;
   int bias_stride, bias_off;
-  int row_elems, heads, col0, head;
+  unsigned row_vecs, cvec;
+  int heads, head;
   bool head_leader, group_leader;
   float inv_scale;
 
@@ -86,12 +87,12 @@ struct DqPolicy {
   };
 
   __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
-    const int64_t so = int64_t(src) * row_elems + col0;
-    const int64_t ro = int64_t(row) * row_elems + col0;
-    Vec16<T>::load(k + so, o.k);
-    Vec16<T>::load(v + so, o.v);
-    Vec16<T>::load(q + ro, o.q);
-    Vec16<T>::load(dout + ro, o.g);
+    const unsigned so = unsigned(src) * row_vecs + cvec;
+    const unsigned ro = unsigned(row) * row_vecs + cvec;
+    Vec16<T>::load_at(k, so, o.k);
+    Vec16<T>::load_at(v, so, o.v);
+    Vec16<T>::load_at(q, ro, o.q);
+    Vec16<T>::load_at(dout, ro, o.g);
     o.st = __ldg(stats + int64_t(row) * heads + head);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
@@ -128,13 +129,13 @@ struct DqPolicy {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = acc[j] * inv_scale;
-    Vec16<T>::store(dq + int64_t(row) * row_elems + col0, o);
+    Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
   }
   __device__ __forceinline__ void zero_row(int row) const {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    Vec16<T>::store(dq + int64_t(row) * row_elems + col0, o);
+    Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
   }
 };
 
@@ -153,7 +154,8 @@ struct DkvPolicy {
   T* __restrict__ dk;
   T* __restrict__ dv;
   int bias_stride, bias_off;
-  int row_elems, heads, col0, head;
+  unsigned row_vecs, cvec;
+  int heads, head;
   float inv_scale;
 
   struct Operands {
@@ -167,12 +169,12 @@ struct DkvPolicy {
 
   // `row` is the source (K/V row), `dst` the destination whose Q, dO and statistics are gathered
   __device__ __forceinline__ void load(Operands& o, int row, int dst, int pe) const {
-    const int64_t d = int64_t(dst) * row_elems + col0;
-    const int64_t ro = int64_t(row) * row_elems + col0;
-    Vec16<T>::load(q + d, o.q);
-    Vec16<T>::load(dout + d, o.g);
-    Vec16<T>::load(k + ro, o.k);
-    Vec16<T>::load(v + ro, o.v);
+    const unsigned d = unsigned(dst) * row_vecs + cvec;
+    const unsigned ro = unsigned(row) * row_vecs + cvec;
+    Vec16<T>::load_at(q, d, o.q);
+    Vec16<T>::load_at(dout, d, o.g);
+    Vec16<T>::load_at(k, ro, o.k);
+    Vec16<T>::load_at(v, ro, o.v);
     o.st = __ldg(stats + int64_t(dst) * heads + head);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
@@ -207,17 +209,17 @@ struct DkvPolicy {
       a[j] = acc[j] * inv_scale;
       b[j] = acc[VEC + j];
     }
-    const int64_t off = int64_t(row) * row_elems + col0;
-    Vec16<T>::store(dk + off, a);
-    Vec16<T>::store(dv + off, b);
+    const unsigned off = unsigned(row) * row_vecs + cvec;
+    Vec16<T>::store_at(dk, off, a);
+    Vec16<T>::store_at(dv, off, b);
   }
   __device__ __forceinline__ void zero_row(int row) const {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    const int64_t off = int64_t(row) * row_elems + col0;
-    Vec16<T>::store(dk + off, o);
-    Vec16<T>::store(dv + off, o);
+    const unsigned off = unsigned(row) * row_vecs + cvec;
+    Vec16<T>::store_at(dk, off, o);
+    Vec16<T>::store_at(dv, off, o);
   }
 };
 
@@ -237,9 +239,9 @@ __device__ __forceinline__ DqPolicy<T, LPH, G> make_dq_policy(const BwdParams& p
   pol.head = blockIdx.y * (G / LPH) + c / LPH;
   pol.bias_stride = p.bias_heads;
   pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
-  pol.row_elems = p.row_elems;
+  pol.row_vecs = unsigned(p.row_elems / VEC);
   pol.heads = p.heads;
-  pol.col0 = (blockIdx.y * G + c) * VEC;
+  pol.cvec = blockIdx.y * G + c;
   pol.head_leader = c % LPH == 0;
   pol.group_leader = c == 0;
   pol.inv_scale = p.inv_scale;
@@ -262,9 +264,9 @@ __device__ __forceinline__ DkvPolicy<T, LPH, G> make_dkv_policy(const BwdParams&
   pol.head = blockIdx.y * (G / LPH) + c / LPH;
   pol.bias_stride = p.bias_heads;
   pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
-  pol.row_elems = p.row_elems;
+  pol.row_vecs = unsigned(p.row_elems / VEC);
   pol.heads = p.heads;
-  pol.col0 = (blockIdx.y * G + c) * VEC;
+  pol.cvec = blockIdx.y * G + c;
   pol.inv_scale = p.inv_scale;
   return pol;
 }
@@ -281,7 +283,8 @@ template <typename T, int LPH, int G>
 __global__ void __launch_bounds__(kBlockThreads) bwd_dq_stitch_kernel(const BwdParams p) {
   using Policy = DqPolicy<T, LPH, G>;
   const Policy pol = make_dq_policy<T, LPH, G>(p);
-  stitch_tiles<G, Policy>(p.walk, pol);
+  __shared__ float s_part[kBlockThreads * Policy::NACC];
+  stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
 template <typename T, int LPH, int G>
@@ -296,7 +299,8 @@ template <typename T, int LPH, int G>
 __global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const BwdParams p) {
   using Policy = DkvPolicy<T, LPH, G>;
   const Policy pol = make_dkv_policy<T, LPH, G>(p);
-  stitch_tiles<G, Policy>(p.walk, pol);
+  __shared__ float s_part[kBlockThreads * Policy::NACC];
+  stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
 constexpr int kDqCtasPerSm = 4;
@@ -403,6 +407,9 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
   const int64_t n_rows = by_dst->n_rows, n_edges = by_dst->n_edges;
   if (n_rows == 0) return TGT_OK;
   TGT_CHECK_ARG(dout && q && k && v && out && z && dq && dk && dv, "tensor pointers must not be null");
+  TGT_CHECK_ARG(uint64_t(n_rows) * uint64_t(heads) * head_dim * (dtype == TGT_F32 ? 4 : 2) / 16 <
+                    (uint64_t(1) << 32),
+                "tensors larger than 64 GiB are not supported");
   TGT_CHECK_ARG(aligned16(dout) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
                     aligned16(z) && aligned16(dq) && aligned16(dk) && aligned16(dv) &&
                     aligned16(bias) && aligned16(dbias) && aligned16(scratch),
@@ -444,7 +451,7 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
     fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a),
               bias != nullptr || dbias != nullptr);
     const dim3 grid(sc.plan_a.n_tiles, hs.groups);
-    const dim3 sgrid((sc.plan_a.n_tiles + kBlockThreads / 32 - 1) / (kBlockThreads / 32), hs.groups);
+    const dim3 sgrid(sc.plan_a.n_tiles, hs.groups);
 #define TGT_LAUNCH_DQ(T, LPH, G)                                               \
   do {                                                                         \
     bwd_dq_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);           \
@@ -458,7 +465,7 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
     fill_walk(&p.walk, *by_src, sc.plan_b, reinterpret_cast<float*>(base + sc.carry_b),
               bias != nullptr);
     const dim3 grid(sc.plan_b.n_tiles, hs.groups);
-    const dim3 sgrid((sc.plan_b.n_tiles + kBlockThreads / 32 - 1) / (kBlockThreads / 32), hs.groups);
+    const dim3 sgrid(sc.plan_b.n_tiles, hs.groups);
 #define TGT_LAUNCH_DKV(T, LPH, G)                                               \
   do {                                                                          \
     bwd_dkv_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);           \

@@ -18,8 +18,8 @@ struct FwdPolicy {
   T* __restrict__ out;
   float* __restrict__ z;           // [n_rows, heads]
   int bias_stride, bias_off;
-  int row_elems, heads;
-  int col0, head;                  // this lane's first element in a row, and its head
+  unsigned row_vecs, cvec;         // 16-byte units per row; this lane's unit inside a row
+  int heads, head;                 // head count; the head this lane belongs to
   bool z_writer;                   // one lane per head stores Z
   float inv_scale;
 
@@ -32,10 +32,10 @@ struct FwdPolicy {
   };
 
   __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
-    const int64_t so = int64_t(src) * row_elems + col0;
-    Vec16<T>::load(k + so, o.k);
-    Vec16<T>::load(v + so, o.v);
-    Vec16<T>::load(q + int64_t(row) * row_elems + col0, o.q);
+    const unsigned so = unsigned(src) * row_vecs + cvec;
+    Vec16<T>::load_at(k, so, o.k);
+    Vec16<T>::load_at(v, so, o.v);
+    Vec16<T>::load_at(q, unsigned(row) * row_vecs + cvec, o.q);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
   __device__ __forceinline__ void clear(Operands& o) const {
@@ -60,14 +60,14 @@ struct FwdPolicy {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = acc[j] * inv;
-    Vec16<T>::store(out + int64_t(row) * row_elems + col0, o);
+    Vec16<T>::store_at(out, unsigned(row) * row_vecs + cvec, o);
     if (z_writer) z[int64_t(row) * heads + head] = acc[VEC];
   }
   __device__ __forceinline__ void zero_row(int row) const {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    Vec16<T>::store(out + int64_t(row) * row_elems + col0, o);
+    Vec16<T>::store_at(out, unsigned(row) * row_vecs + cvec, o);
     if (z_writer) z[int64_t(row) * heads + head] = 0.f;
   }
 };
@@ -99,9 +99,9 @@ __device__ __forceinline__ FwdPolicy<T, LPH, G> make_policy(const FwdParams& p) 
   pol.head = blockIdx.y * (G / LPH) + c / LPH;
   pol.bias_stride = p.bias_heads;
   pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
-  pol.row_elems = p.row_elems;
+  pol.row_vecs = unsigned(p.row_elems / VEC);
   pol.heads = p.heads;
-  pol.col0 = (blockIdx.y * G + c) * VEC;
+  pol.cvec = blockIdx.y * G + c;
   pol.z_writer = c % LPH == 0;
   pol.inv_scale = p.inv_scale;
   return pol;
@@ -120,7 +120,8 @@ __global__ void __launch_bounds__(kBlockThreads) fwd_stitch_kernel(const FwdPara
   using Policy = FwdPolicy<T, LPH, G>;
   // 32 % G == 0, so threadIdx.x % G is also the column of a lane inside its warp
   const Policy pol = make_policy<T, LPH, G>(p);
-  stitch_tiles<G, Policy>(p.walk, pol);
+  __shared__ float s_part[kBlockThreads * Policy::NACC];
+  stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
 constexpr int kFwdCtasPerSm = 5;
@@ -166,6 +167,9 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   const tgt_layout& L = *by_dst;
   if (L.n_rows == 0) return TGT_OK;
   TGT_CHECK_ARG(q && k && v && out && z, "q/k/v/out/z must not be null");
+  TGT_CHECK_ARG(uint64_t(L.n_rows) * uint64_t(heads) * head_dim * (dtype == TGT_F32 ? 4 : 2) / 16 <
+                    (uint64_t(1) << 32),
+                "tensors larger than 64 GiB are not supported");
   TGT_CHECK_ARG(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(z) &&
                     aligned16(bias) && aligned16(scratch),
                 "device pointers must be 16-byte aligned");
@@ -194,7 +198,7 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   p.walk.need_perm = bias != nullptr;
 
   const dim3 grid(tp.n_tiles, hs.groups);
-  const dim3 sgrid((tp.n_tiles + kBlockThreads / 32 - 1) / (kBlockThreads / 32), hs.groups);
+  const dim3 sgrid(tp.n_tiles, hs.groups);
 #define TGT_LAUNCH_FWD(T, LPH, G)                                     \
   do {                                                                \
     fwd_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);     \

@@ -49,6 +49,13 @@ struct Vec16<float> {
   __device__ __forceinline__ static void store(float* p, const float (&r)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(r[0], r[1], r[2], r[3]);
   }
+  // The same with the position given as a 32-bit index in units of 16 bytes (cheaper addressing).
+  __device__ __forceinline__ static void load_at(const float* base, unsigned v, float (&r)[4]) {
+    load(reinterpret_cast<const float*>(reinterpret_cast<const float4*>(base) + v), r);
+  }
+  __device__ __forceinline__ static void store_at(float* base, unsigned v, const float (&r)[4]) {
+    store(reinterpret_cast<float*>(reinterpret_cast<float4*>(base) + v), r);
+  }
 };
 
 template <>
@@ -72,6 +79,14 @@ struct Vec16<__nv_bfloat16> {
       w[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  __device__ __forceinline__ static void load_at(const __nv_bfloat16* base, unsigned v,
+                                                 float (&r)[8]) {
+    load(reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint4*>(base) + v), r);
+  }
+  __device__ __forceinline__ static void store_at(__nv_bfloat16* base, unsigned v,
+                                                  const float (&r)[8]) {
+    store(reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint4*>(base) + v), r);
   }
 };
 
