@@ -125,6 +125,31 @@ TGT_API int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, con
                         int head_dim, int dtype, void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * Forward for callers that cannot allocate.  No counterpart in the reference.
+ *
+ * tgt_sparse_attn_fwd needs scratch from its caller.  Some callers have none to give and may not
+ * create any: a process whose own arena took the whole GPU at start-up, a plug-in inside such a
+ * process, a loop that must never reach cudaMalloc because that call can stall the device.  This
+ * entry point computes exactly what tgt_sparse_attn_fwd computes (same kernels, same results) but
+ * keeps the scratch in a 4 MiB array that is part of the library image, so the call allocates
+ * nothing and neither must the caller; every GPU that loads the library carries those 4 MiB until
+ * the process exits.  Inputs and outputs are still the caller's.
+ *
+ * Limit: the graph's cross-tile carry must fit the 4 MiB (for 8 heads x 8 in fp32 that is about
+ * 6.5 million edges); a larger graph is refused with TGT_ERR_WORKSPACE before anything runs.
+ * The first call on each device looks the array's device address up (one cudaGetSymbolAddress with
+ * that device current) and remembers it; make that first call outside any stream capture.
+ * All calls on one GPU share the array: two calls whose kernels can overlap on the GPU (different
+ * streams, no ordering between them) race on it and corrupt each other's rows; calls ordered on
+ * one stream are safe.  Nothing in the array has to start at zero — every slot that is read was
+ * written earlier in the same call — so stale contents of a previous call are harmless.
+ */
+TGT_API int tgt_sparse_attn_fwd_noalloc(const void* q, const void* k, const void* v,
+                                        const float* bias, int bias_heads,
+                                        const tgt_layout* by_dst, void* out, float* z, int heads,
+                                        int head_dim, int dtype, void* stream);
+
+/*
  * Backward of the same op (the reference has no hand-written backward; this replaces the autograd
  * graph of attn_module.py:141-187: three index_put_(accumulate=True), two gathers and the
  * elementwise chain).  With G = dout, inv = 1/(Z+1e-6):

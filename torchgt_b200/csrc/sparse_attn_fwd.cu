@@ -210,3 +210,63 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }
+
+// ---- forward without any allocation by anybody ---------------------------------------------------
+// Some hosts cannot give this library scratch memory at call time: a serving process that handed
+// every byte of the GPU to its own arena at start-up, a plug-in living inside such a process, or a
+// latency-critical loop that must never reach cudaMalloc (which may stall the whole device).  For
+// them the cross-tile carry of the forward pass lives in the module itself.
+namespace tgt {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;  // 4 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+
+// The array's name is only a handle on the host; the address the kernels need comes from the
+// runtime, once per device, with that device current.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  TGT_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices)
+    return set_error(TGT_ERR_UNSUPPORTED, "device ordinal %d is outside the supported range", dev);
+  void* p = __atomic_load_n(&g_static_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    TGT_CHECK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    __atomic_store_n(&g_static_scratch_ptr[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return TGT_OK;
+}
+
+}  // namespace
+}  // namespace tgt
+
+extern "C" int tgt_sparse_attn_fwd_noalloc(const void* q, const void* k, const void* v,
+                                           const float* bias, int bias_heads,
+                                           const tgt_layout* by_dst, void* out, float* z,
+                                           int heads, int head_dim, int dtype, void* stream) {
+  using namespace tgt;
+  TGT_CHECK_ARG(dtype == TGT_F32 || dtype == TGT_BF16, "dtype must be TGT_F32 or TGT_BF16");
+  int rc = check_layout(by_dst, "by_dst");
+  if (rc != TGT_OK) return rc;
+  HeadSplit hs;
+  if (!split_heads(heads, head_dim, dtype, &hs))
+    return set_error(TGT_ERR_UNSUPPORTED, "heads=%d head_dim=%d dtype=%d is not supported", heads,
+                     head_dim, dtype);
+  // size check first: nothing is launched and nothing is looked up for a graph that does not fit
+  const size_t need = fwd_scratch_bytes(by_dst, heads, head_dim, dtype);
+  if (need > kStaticScratchBytes)
+    return set_error(TGT_ERR_WORKSPACE,
+                     "this graph needs %zu bytes of carry space, the built-in scratch of "
+                     "tgt_sparse_attn_fwd_noalloc holds %zu; use tgt_sparse_attn_fwd with caller "
+                     "scratch",
+                     need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != TGT_OK) return rc;
+  return tgt_sparse_attn_fwd(q, k, v, bias, bias_heads, by_dst, out, z, heads, head_dim, dtype,
+                             scratch, kStaticScratchBytes, stream);
+}
