@@ -398,19 +398,75 @@ def run_multi_gpu(args, dtype, rank, world):
         out.backward(dout)
         q.grad = k.grad = v.grad = None
 
+    def timed(fn):
+        for i in range(args.warmup):
+            fn(i)
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(args.steps):
+            fn(i)
+        stop.record()
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def note(msg):
+        if os.environ.get("TGT_BENCH_TRACE"):
+            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     sampler = ClockSampler(local) if rank == 0 else None
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(args.steps):
-        step(i)
-    stop.record()
-    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
-    ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(ms.item())
+    eager_ms = timed(step)
+    note(f"eager {eager_ms:.3f} ms")
+    # The same step (layer forward, backward, both exchanges) captured once per input set in a CUDA
+    # graph: the NCCL all-to-alls and every kernel replay without host work in between.
+    graphs = []
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(ROTATING_SETS):
+            step(i)
+    side.synchronize(); dist.barrier()
+    note("side-stream warm-up done")
+    for i in range(ROTATING_SETS):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            step(i)
+        graphs.append(g)
+        note(f"captured step graph {i}")
+    torch.cuda.synchronize(); dist.barrier()
+    note("replaying")
+    ms_per_step = timed(lambda i: graphs[i % ROTATING_SETS].replay())
+    note(f"graph {ms_per_step:.3f} ms")
+
+    # the attention alone (no exchange) on this rank's head slice of the same graph, for reference
+    heads_local = HEADS // world
+    op_sets = []
+    for i in range(ROTATING_SETS):
+        gen = torch.Generator().manual_seed(99 + i)
+        t = [torch.randn(n_rows, heads_local, HEAD_DIM, generator=gen).to(dtype).to(dev).requires_grad_()
+             for _ in range(3)]
+        op_sets.append((t, torch.randn(n_rows, heads_local, HEAD_DIM, generator=gen).to(dtype).to(dev)))
+
+    def op_step(i):
+        (q, k, v), dout = op_sets[i % ROTATING_SETS]
+        from torchgt_b200 import sparse_graph_attention
+        sparse_graph_attention(q, k, v, graph).backward(dout)
+        q.grad = k.grad = v.grad = None
+
+    with torch.cuda.stream(side):
+        for i in range(ROTATING_SETS):
+            op_step(i)
+    side.synchronize()
+    op_graphs = []
+    for i in range(ROTATING_SETS):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            op_step(i)
+        op_graphs.append(g)
+    torch.cuda.synchronize(); dist.barrier()
+    op_ms = timed(lambda i: op_graphs[i % ROTATING_SETS].replay())
 
     # end to end: this rank's q, k, v, dO come from pinned host memory, the result goes back
     host = [t.detach().cpu().pin_memory() for t in sets[0]]
@@ -440,7 +496,6 @@ def run_multi_gpu(args, dtype, rank, world):
 
     if rank == 0:
         elem = 4 if dtype == torch.float32 else 2
-        heads_local = HEADS // world
         peak, peak_kind = measured_hbm_peak()
         bytes_ = algorithmic_bytes(n_rows, n_edges, heads_local, HEAD_DIM, elem, 0)
         step_bytes = sum(bytes_.values())
@@ -453,7 +508,8 @@ def run_multi_gpu(args, dtype, rank, world):
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32" if dtype == torch.float32 else "bf16 i/o, f32 math", "data": "synthetic",
             "config": workload_config(world, n_rows, n_edges, args.dtype) |
-                      {"step": "DistributedAttentionNoMerge fwd+bwd: all-to-all(q,k,v) -> attention with "
+                      {"timing": "step captured in a CUDA graph per input set (NCCL inside), replayed",
+                       "step": "DistributedAttentionNoMerge fwd+bwd: all-to-all(q,k,v) -> attention with "
                                f"{heads_local} head(s) over all rows -> all-to-all(out), reversed in backward",
                        "bias": "none (the models pass attn_bias=None on this path)"},
             "clocks": clocks,
@@ -462,14 +518,23 @@ def run_multi_gpu(args, dtype, rank, world):
                     "includes": "per rank: pinned-host uploads of q,k,v,dO, layer forward+backward with both "
                                 "exchanges, downloads of out,dq,dk,dv; edge layouts resident"},
             "gpu_launches": launches * args.steps,
+            "eager_ms_per_step": eager_ms,
+            "attention_only": {"ms_per_step": op_ms, "value": n_edges / (op_ms * 1e-3), "unit": "edges/s",
+                               "note": "same graph, this rank's head slice, no exchange (CUDA graph)",
+                               "frac_of_hbm_peak": step_bytes / (op_ms * 1e-3) / 1e9 / peak},
             "roofline": {"bound": "hbm", "kernel": "whole step per GPU (attention phases + exchange)",
                          "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
                          "traffic": None, "algorithmic_bytes_per_launch": step_bytes},
         }
         print(json.dumps(line), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
+    # graphs that hold NCCL nodes must be gone, and the device idle, before the communicator is torn down
+    graphs.clear(); op_graphs.clear()
+    import gc
+    gc.collect()
+    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    sys.stdout.flush(); sys.stderr.flush()
+    os._exit(0)   # every rank is past its last collective; skip the communicator teardown
 
 
 def main():

@@ -102,19 +102,22 @@ def extend_global_token0(x_layer: Tensor, extend_dim: int) -> Tensor:
 
 
 class _CopyGlobalToken0(torch.autograd.Function):
-    """In-place ``x[:, rows, :] = x[:, 0:1, :]`` on the device, index list resident on the GPU."""
+    """``y = x; y[:, rows, :] = x[:, 0:1, :]`` on the device, index list resident on the GPU.
+
+    Returns a new tensor: the input is the attention output, which the attention backward needs
+    unchanged (it recomputes the softmax gradient from it), so it must not be edited in place."""
 
     @staticmethod
     def forward(ctx, x: Tensor, rows: Tensor):
         lib = _cabi.load()
-        b, s, w = x.shape
-        dtype, mult = _elem(x)
-        _cabi.check(lib.tgt_global_rows_broadcast(x.data_ptr(), rows.data_ptr(), rows.numel(), b, s,
+        y = x.clone(memory_format=torch.contiguous_format)
+        b, s, w = y.shape
+        dtype, mult = _elem(y)
+        _cabi.check(lib.tgt_global_rows_broadcast(y.data_ptr(), rows.data_ptr(), rows.numel(), b, s,
                                                   w * mult, dtype,
-                                                  torch.cuda.current_stream(x.device).cuda_stream))
-        ctx.mark_dirty(x)
+                                                  torch.cuda.current_stream(y.device).cuda_stream))
         ctx.save_for_backward(rows)
-        return x
+        return y
 
     @staticmethod
     def backward(ctx, grad: Tensor):
@@ -144,7 +147,8 @@ def _elem(t: Tensor):
 
 def copy_global_token0(x_layer: Tensor, extend_dim: int) -> Tensor:
     """gt_sp/utils.py:817-838: x_layer [b, s + p, hp]; every rank's slot of the global token (rows
-    ``get_global_token_indices``) takes the value computed at row 0.  In place, like the reference."""
+    ``get_global_token_indices``) takes the value computed at row 0.  Host tensors are edited in place
+    like the reference does; CUDA tensors come back as a new tensor (see ``_CopyGlobalToken0``)."""
     world = get_sequence_parallel_world_size()
     if extend_dim != 1 or x_layer.dim() != 3:
         raise ValueError("copy_global_token0 expects [b, s+p, hp] and extend_dim == 1")
@@ -152,8 +156,6 @@ def copy_global_token0(x_layer: Tensor, extend_dim: int) -> Tensor:
         raise ValueError(f"{x_layer.size(1)} rows cannot be split over {world} ranks")
     if x_layer.is_cuda:
         rows = get_global_token_rows_on(x_layer.device, get_last_batch_flag())
-        if not x_layer.is_contiguous():
-            x_layer = x_layer.contiguous()
         return _CopyGlobalToken0.apply(x_layer, rows)
     # host tensors (multi-rank logic tests on gloo): plain indexing
     rows = torch.tensor(_active_global_rows(), dtype=torch.long)
