@@ -40,8 +40,9 @@ HEADS, HEAD_DIM = 8, 8
 NODES_PER_RANK = 64000
 ROTATING_SETS = 4
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
-# summarised in profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES = {"fwd_kernel": None, "bwd_dq_kernel": None, "bwd_dkv_kernel": None}
+# summarised in profiles/sparse_attn_64k_fp32_kernels.md (fp32 workload; the dQ phase includes the
+# row-statistics kernel).
+NCU_TRAFFIC_BYTES = {"fwd_kernel": 63.1e6, "bwd_dq_kernel": 90.4e6 + 34.8e6, "bwd_dkv_kernel": 100.1e6}
 
 
 def measured_hbm_peak():
@@ -350,7 +351,7 @@ def run_single_gpu(args, dtype):
         "gpu_launches": kernels_per_step(graph) * args.steps,
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                     "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+                     "traffic": NCU_TRAFFIC_BYTES.get(dominant) if dtype == torch.float32 else None,
                      "algorithmic_bytes_per_launch": bytes_[dominant],
                      "phases_ms": phase_ms,
                      "phases_frac": {n: bytes_[n] / (phase_ms[n] * 1e-3) / 1e9 / peak for n in names},
