@@ -158,15 +158,14 @@ def cpu_reference_rate(edge_index, n_rows, steps, warmup, budget_s=20.0, seed=12
 def run_reference_arm(args, rank):
     if rank != 0:
         return
-    from torchgt_b200.synthetic import benchmark_64k
-    edge_index, n_rows = benchmark_64k(ranks=args.gpus)
+    edge_index, n_rows = load_workload(args.workload, ranks=args.gpus)
     base, mean = cpu_reference_rate(edge_index, n_rows, args.steps, max(args.warmup, 1), budget_s=150.0)
     line = {
         "impl": "reference", "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": base["value"],
         "unit": "edges/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus, n_rows, edge_index.shape[1], "fp32") | {"device": "host CPU"},
+        "config": workload_config(args.gpus, n_rows, edge_index.shape[1], "fp32", args.workload) | {"device": "host CPU"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -174,9 +173,25 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus, n_rows, n_edges, dtype):
-    return {"workload": "sparse-attention op microbench: 64,000 nodes per GPU + global node, 8 clusters of 8,000 "
-                        "per GPU, 17.5% of edges crossing clusters, scalar edge bias, fwd+bwd",
+WORKLOADS = {
+    "64k": "sparse-attention op microbench: 64,000 nodes per GPU + global node, 8 clusters of 8,000 per GPU, "
+           "17.5% of edges crossing clusters, scalar edge bias, fwd+bwd",
+    "870k": "long-sequence batch: 870,000 nodes + global node, 18,214,272 edges, power-law out-degrees "
+            "(exponent 2.1), 8 clusters with 7.1% of edges cut, scalar edge bias, fwd+bwd",
+}
+
+
+def load_workload(name, ranks=1):
+    from torchgt_b200.synthetic import benchmark_64k, benchmark_870k
+    if name == "870k":
+        if ranks != 1:
+            raise SystemExit("--workload 870k is a single-GPU workload")
+        return benchmark_870k()
+    return benchmark_64k(ranks=ranks)
+
+
+def workload_config(n_gpus, n_rows, n_edges, dtype, name="64k"):
+    return {"workload": WORKLOADS[name],
             "rows": n_rows, "edges": n_edges, "heads": HEADS, "head_dim": HEAD_DIM, "io_dtype": dtype,
             "parallelism": "single GPU" if n_gpus == 1 else f"Ulysses sequence parallel x{n_gpus} (heads sharded)",
             "l2": f"{ROTATING_SETS} rotating input sets, footprint > 126 MB L2, no explicit flush"}
@@ -247,10 +262,9 @@ def kernels_per_step(graph):
 
 def run_single_gpu(args, dtype):
     from torchgt_b200 import SparseGraph, sparse_graph_attention
-    from torchgt_b200.synthetic import benchmark_64k
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    edge_index, n_rows = benchmark_64k()
+    edge_index, n_rows = load_workload(args.workload)
     n_edges = edge_index.shape[1]
     graph = SparseGraph(edge_index.to(dev), n_rows)
     graph.by_src  # build both layouts before timing
@@ -340,7 +354,7 @@ def run_single_gpu(args, dtype):
         "unit": "edges/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32" if dtype == torch.float32 else "bf16 i/o, f32 math", "data": "synthetic",
-        "config": workload_config(1, n_rows, n_edges, args.dtype),
+        "config": workload_config(1, n_rows, n_edges, args.dtype, args.workload),
         "clocks": clocks,
         "e2e": {"value": n_edges / results["full"], "unit": "edges/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": results["full"] * 1e3,
@@ -351,7 +365,7 @@ def run_single_gpu(args, dtype):
         "gpu_launches": kernels_per_step(graph) * args.steps,
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                     "traffic": NCU_TRAFFIC_BYTES.get(dominant) if dtype == torch.float32 else None,
+                     "traffic": NCU_TRAFFIC_BYTES.get(dominant) if (dtype == torch.float32 and args.workload == "64k") else None,
                      "algorithmic_bytes_per_launch": bytes_[dominant],
                      "phases_ms": phase_ms,
                      "phases_frac": {n: bytes_[n] / (phase_ms[n] * 1e-3) / 1e9 / peak for n in names},
@@ -545,6 +559,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--dtype", choices=["fp32", "bf16"], default="fp32")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="64k",
+                    help="N=1 only: 64k (default, the headline) or 870k (long-sequence batch)")
     ap.add_argument("--profile", action="store_true",
                     help="N=1 only: launch warmup+steps plain forward+backward steps and exit (for ncu)")
     args = ap.parse_args()
