@@ -230,6 +230,41 @@ TGT_API int tgt_global_rows_broadcast(void* x, const int32_t* global_rows, int n
 TGT_API int tgt_global_rows_reduce(void* dx, const int32_t* global_rows, int n_global, int64_t batch,
                            int64_t seq, int64_t width, int dtype, void* stream);
 
+/*
+ * Ulysses exchange over NVLink peer memory: the same head<->sequence all-to-all as above, done by this
+ * library's kernels storing straight into the destination ranks' memory instead of by a collective
+ * library plus pack / unpack passes.  Replaces _SeqAllToAll.forward (gt_sp/layer.py:30-45) and, with
+ * alias rows, copy_global_token0 (gt_sp/utils.py:817-838) in the same pass.
+ *
+ * Every rank owns one peer-visible "landing" area of tgt_p2p_control_bytes() + 2 * half_bytes bytes,
+ * zero-filled once before first use; peer_landing[i] is the address of rank i's area AS SEEN FROM
+ * THIS GPU (peer mapping), a host array of `world` pointers, world <= 16.  One exchange is
+ * tgt_p2p_push -> tgt_p2p_barrier -> tgt_p2p_fetch on one stream, called by every rank in the same
+ * order with the same sizes.  The two halves alternate on the device (the barrier advances a counter
+ * kept in the area), so the sequence may be replayed from a CUDA graph.
+ *
+ * tgt_p2p_push: tensor t is [outer_s][world][width_s_bytes] (what _SeqAllToAll splits along
+ * scatter_idx); on every destination it lands as [outer_g][world][width_g_bytes] (what cat along
+ * gather_idx produces) with this rank's piece in column block `rank`.  If n_alias > 0, source rows
+ * (of alias_row_bytes each, counted inside one outer row) listed in the device array alias_rows are
+ * read from row 0 instead.
+ * tgt_p2p_barrier: all ranks' pushes are complete and visible when the kernel ends.  Waits are
+ * bounded: after spin_limit polls it gives up, writes 1 + (rank it waited for) to *status (a
+ * host-readable, device-writable int32, e.g. pinned memory) and returns; the context stays usable.
+ * tgt_p2p_fetch: copies the n_tensors landed tensors (bytes_per_tensor each) out of the landing
+ * half the last barrier completed, into ordinary device tensors.
+ */
+TGT_API size_t tgt_p2p_control_bytes(void);
+TGT_API int tgt_p2p_push(const void* x0, const void* x1, const void* x2, int n_tensors,
+                         void* const* peer_landing, size_t half_bytes, int64_t outer_s,
+                         int64_t width_s_bytes, int64_t width_g_bytes, int world, int rank,
+                         const int32_t* alias_rows, int n_alias, int64_t alias_row_bytes,
+                         void* stream);
+TGT_API int tgt_p2p_barrier(void* const* peer_landing, int world, int rank, uint32_t spin_limit,
+                            int32_t* status, void* stream);
+TGT_API int tgt_p2p_fetch(const void* landing_mine, size_t half_bytes, int n_tensors, void* y0,
+                          void* y1, void* y2, int64_t bytes_per_tensor, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -137,3 +137,80 @@ def test_relayout_argument_errors():
     assert lib.tgt_a2a_pack_heads(x.data_ptr(), None, None, 1, x.data_ptr(), 1, 4, 4, 2, 7, None) == 1
     assert lib.tgt_a2a_pack_heads(x.data_ptr() + 4, None, None, 1, x.data_ptr(), 1, 4, 4, 2, 0, None) == 1
     assert "aligned" in _cabi.last_error()
+
+
+def _peer_table(areas):
+    return (ctypes.c_void_p * len(areas))(*[a.data_ptr() for a in areas])
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("shape,s,g,n_t,alias", [((1, 9, 8, 8), 2, 1, 3, False), ((2, 6, 8, 8), 2, 1, 2, False),
+                                                 ((1, 32, 64), 1, 2, 1, False), ((2, 16, 32), 1, 2, 1, True)])
+def test_peer_push_and_fetch_match_all_to_all_semantics(world, shape, s, g, n_t, alias):
+    """The peer-memory transport on one GPU: every rank's landing area is an ordinary local buffer, the
+    ranks push one after the other, and the per-area epoch is advanced by a one-rank barrier (a real
+    multi-rank barrier needs one GPU per rank and is covered by the multi-GPU test)."""
+    import math
+    from torchgt_b200 import _cabi
+    lib = _cabi.load()
+    if shape[s] % world != 0:
+        pytest.skip("scatter axis not divisible")
+    gen = torch.Generator().manual_seed(world + n_t)
+    xs = [[torch.randn(shape, generator=gen).cuda() for _ in range(n_t)] for _ in range(world)]
+    nbytes = xs[0][0].numel() * 4
+    half = ((n_t * nbytes + 255) // 256) * 256
+    ctl = int(lib.tgt_p2p_control_bytes())
+    areas = [torch.zeros(ctl + 2 * half, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = _peer_table(areas)
+    status = torch.zeros(1, dtype=torch.int32).pin_memory()
+    stream = torch.cuda.current_stream().cuda_stream
+    chunk = list(shape); chunk[s] //= world
+    out_shape = list(chunk); out_shape[g] *= world
+    outer_s = math.prod(shape[:s])
+    ws_bytes = chunk[s] * math.prod(shape[s + 1:]) * 4
+    wg_bytes = math.prod(chunk[g:]) * 4
+    rows = torch.tensor([0, 4, 12], dtype=torch.int32, device="cuda") if alias else None
+    for step in range(3):          # three exchanges in a row: both landing halves get reused
+        for r in range(world):
+            ptrs = [t.data_ptr() for t in xs[r]] + [None] * (3 - n_t)
+            _cabi.check(lib.tgt_p2p_push(ptrs[0], ptrs[1], ptrs[2], n_t, table, half, outer_s, ws_bytes, wg_bytes,
+                                         world, r, rows.data_ptr() if alias else None, 3 if alias else 0,
+                                         shape[-1] * 4 if alias else 0, stream))
+        outs = []
+        for r in range(world):
+            one = _peer_table([areas[r]])
+            _cabi.check(lib.tgt_p2p_barrier(one, 1, 0, 10, status.data_ptr(), stream))
+            ys = [torch.empty(out_shape, device="cuda") for _ in range(n_t)]
+            optrs = [t.data_ptr() for t in ys] + [None] * (3 - n_t)
+            _cabi.check(lib.tgt_p2p_fetch(areas[r].data_ptr(), half, n_t, optrs[0], optrs[1], optrs[2], nbytes, stream))
+            outs.append(ys)
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        for t in range(n_t):
+            srcs = [xs[r][t].cpu().numpy() for r in range(world)]
+            if alias:
+                srcs = [uo.copy_global_token0(x, [0, 4, 12]) for x in srcs]
+            ref = uo.seq_all_to_all(srcs, s, g)
+            for r in range(world):
+                assert np.array_equal(outs[r][t].cpu().numpy(), ref[r]), (step, t, r)
+        xs = [[x + 1.0 for x in row] for row in xs]      # new values for the next exchange
+
+
+def test_peer_barrier_gives_up_after_its_poll_limit_and_reports_the_rank():
+    """A peer that never signals: the barrier must return after spin_limit polls, name the rank it waited
+    for in the status word, and leave the context usable."""
+    from torchgt_b200 import _cabi
+    lib = _cabi.load()
+    ctl = int(lib.tgt_p2p_control_bytes())
+    areas = [torch.zeros(ctl + 512, dtype=torch.uint8, device="cuda") for _ in range(3)]
+    status = torch.zeros(1, dtype=torch.int32).pin_memory()
+    stream = torch.cuda.current_stream().cuda_stream
+    _cabi.check(lib.tgt_p2p_barrier(_peer_table(areas), 3, 1, 2000, status.data_ptr(), stream))
+    torch.cuda.synchronize()
+    assert int(status[0]) in (1, 3)            # 1 + rank 0 or 1 + rank 2, whichever lane gave up last
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+    # argument errors are reported before any launch
+    assert lib.tgt_p2p_barrier(_peer_table(areas), 3, 5, 10, status.data_ptr(), stream) == 1
+    assert lib.tgt_p2p_barrier(_peer_table(areas), 3, 1, 10, None, stream) == 1
+    assert lib.tgt_p2p_push(areas[0].data_ptr(), None, None, 1, _peer_table(areas), 32, 1, 16, 16, 3, 0, None, 0, 0,
+                            stream) == 1   # 48 bytes do not fit a 32-byte landing half

@@ -23,9 +23,10 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, transport, ret):
     sys.path.insert(0, str(ROOT))
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TGT_EXCHANGE=transport, TGT_P2P_SPIN_LIMIT="4000000")
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -53,20 +54,28 @@ def _worker(rank, world, port, ret):
             ref = t(name)
             errs[name] = float((mine - ref).abs().max() / ref.abs().max())
         torch.cuda.synchronize()
+        from torchgt_b200.gt_sp import p2p
+        px = p2p.peer_exchange_for(group, dev)
+        errs["used_peer_memory"] = px is not None
+        if px is not None:
+            px.check()
         ret[rank] = errs
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("world", [2, 4])
-def test_nomerge_layer_over_nccl(world):
+@pytest.mark.parametrize("transport", ["p2p", "nccl"])
+def test_nomerge_layer_on_real_gpus(world, transport):
+    """transport = p2p: the library's own NVLink peer-memory exchange; nccl: one all_to_all_single."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     with ctx.Manager() as manager:
         ret = manager.dict()
-        mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), transport, ret), nprocs=world, join=True)
         for rank in range(world):
             errs = dict(ret[rank])
+            assert errs.pop("used_peer_memory") == (transport == "p2p")
             assert errs["a2a_21"] == 0.0 and errs["a2a_12"] == 0.0, (rank, errs)
             assert max(errs.values()) < 1e-5, (rank, errs)

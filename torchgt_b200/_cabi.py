@@ -5,7 +5,7 @@ There is no CPU fallback: if the library is missing or a call fails this module 
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_char_p, c_int, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, c_char_p, c_int, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtorchgt_b200.so"
@@ -78,6 +78,11 @@ SIGNATURES = {
                                           c_void_p]),
     "tgt_global_rows_reduce": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int,
                                        c_void_p]),
+    "tgt_p2p_control_bytes": (c_size_t, []),
+    "tgt_p2p_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), c_size_t, c_int64, c_int64,
+                             c_int64, c_int, c_int, c_void_p, c_int, c_int64, c_void_p]),
+    "tgt_p2p_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_uint32, c_void_p, c_void_p]),
+    "tgt_p2p_fetch": (c_int, [c_void_p, c_size_t, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
 }
 
 _lib = None

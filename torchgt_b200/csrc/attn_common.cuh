@@ -25,8 +25,18 @@
 
 namespace tgt {
 
+// Build-time tuning knobs (defaults are what the measurements in the repository use).
+#ifndef TGT_UNROLL
+#define TGT_UNROLL 4
+#endif
+#ifdef TGT_MIN_CTAS
+#define TGT_WALK_BOUNDS __launch_bounds__(128, TGT_MIN_CTAS)
+#else
+#define TGT_WALK_BOUNDS __launch_bounds__(128)
+#endif
+
 constexpr int kBlockThreads = 128;
-constexpr int kUnroll = 4;
+constexpr int kUnroll = TGT_UNROLL;  // edges per lane group whose gathers are in flight together
 
 template <int G>
 struct TileGeom {
@@ -367,6 +377,21 @@ inline bool split_heads(int heads, int head_dim, int dtype, HeadSplit* hs) {
   } while (0)
 
 int check_layout(const tgt_layout* L, const char* name);
+
+// Resident CTAs per SM of a walk kernel on the current device (asked from the runtime once per
+// instantiation): the tile size is chosen so that one wave of CTAs covers the graph.
+template <typename Kernel>
+inline int resident_ctas(Kernel kernel, int* cache) {
+  if (*cache <= 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kBlockThreads, 0) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = 4;
+    }
+    *cache = n;
+  }
+  return *cache;
+}
 
 // Tiling of one pass: edges per lane group, number of tiles, bytes of cross-tile carry.
 struct TilePlan {

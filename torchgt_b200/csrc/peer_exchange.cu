@@ -1,0 +1,229 @@
+// Ulysses exchange over NVLink peer memory: the head<->sequence all-to-all done by this GPU's own
+// kernels instead of a library collective.
+//
+// Every rank owns a "landing" area in memory that all peers can address (two halves, used
+// alternately).  An exchange is three launches on the caller's stream:
+//   push   : each rank reads its tensors once and stores every 16-byte piece directly at its final
+//            position in the destination rank's landing half (local pieces included) — the split,
+//            the transfer and the concatenation of the reference's _SeqAllToAll in one pass;
+//   barrier: every rank tells every peer "my pushes are done" and waits for the same from all
+//            peers (one flag word per peer pair, release/acquire at system scope);
+//   fetch  : each rank copies what landed into ordinary tensors, which frees the landing half.
+// The half in use is picked on the device from a counter the barrier advances, so the sequence is
+// correct under CUDA-graph replay.  A landing half is overwritten two exchanges after it was
+// filled; the barrier in between is what guarantees that every peer has fetched it.
+//
+// Waits are bounded: after `spin_limit` polls the barrier gives up, records the rank it was waiting
+// for in a status word the host can read, and returns; the context stays usable.
+#include "tgt_common.cuh"
+
+namespace tgt {
+namespace {
+
+constexpr int kMaxWorld = 16;
+constexpr int kThreads = 256;
+
+struct PeerTable {
+  void* p[kMaxWorld];
+};
+struct Ptrs3 {
+  void* p[3];
+};
+
+// Control block at the start of every rank's peer-visible area.
+//   flags[j]  : last epoch announced by rank j (written only by rank j)
+//   epoch     : number of barriers this rank has passed (local use)
+struct Control {
+  unsigned flags[kMaxWorld];
+  unsigned epoch;
+  unsigned pad[15];
+};
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Fused split + transfer + concatenate.  Source tensor t is [outer_s][world][ws] in 16-byte units
+// (ws units go to each peer from every outer row); the destination tensor on peer r' is
+// [outer_g][world][wg] units, this rank filling column block `rank`.  A chunk's flat unit index
+// f = a * ws + w maps to (f / wg, f % wg) on the destination.
+template <typename U>
+__global__ void push_kernel(Ptrs3 src, PeerTable landing, const Control* __restrict__ ctl,
+                            size_t half_bytes, int n_tensors, int64_t outer_s, int64_t ws,
+                            int64_t wg, int world, int rank, const int32_t* __restrict__ alias_rows,
+                            int n_alias, int64_t alias_period_units) {
+  const unsigned half = ctl->epoch & 1u;
+  const int64_t chunk = outer_s * ws;                       // units one peer gets per tensor
+  const int64_t per_tensor_dst = chunk * world;             // units of one destination tensor
+  const int64_t total = chunk * world * n_tensors;
+  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    // i enumerates (peer, tensor, f) with f fastest: consecutive threads write consecutive units
+    const int64_t f = i % chunk;
+    const int t = int((i / chunk) % n_tensors);
+    const int peer = int(i / (chunk * n_tensors));
+    const int64_t a = f / ws;
+    const int64_t w = f % ws;
+    int64_t pos = int64_t(peer) * ws + w;   // unit position inside outer row a of the source
+    if (n_alias > 0) {
+      // rows listed in alias_rows are read from row 0 of the same outer row instead
+      // (copy_global_token0 folded into the transfer); a row is alias_period_units wide
+      const int64_t row = pos / alias_period_units;
+      for (int j = 0; j < n_alias; ++j)
+        if (row == alias_rows[j]) {
+          pos = pos % alias_period_units;
+          break;
+        }
+    }
+    const U val = static_cast<const U*>(src.p[t])[a * world * ws + pos];
+    const int64_t og = f / wg, o = f % wg;
+    U* dst = reinterpret_cast<U*>(static_cast<char*>(landing.p[peer]) + sizeof(Control) +
+                                  half * half_bytes) + t * per_tensor_dst;
+    dst[(og * world + rank) * wg + o] = val;
+  }
+}
+
+// One block; thread j talks to peer j.
+__global__ void barrier_kernel(PeerTable landing, int world, int rank, unsigned spin_limit,
+                               int* __restrict__ status) {
+  Control* mine = static_cast<Control*>(landing.p[rank]);
+  __shared__ unsigned next;
+  if (threadIdx.x == 0) next = mine->epoch + 1;
+  __syncthreads();
+  const unsigned epoch = next;
+  const int j = threadIdx.x;
+  if (j < world && j != rank) {
+    Control* theirs = static_cast<Control*>(landing.p[j]);
+    __threadfence_system();
+    st_release_sys(&theirs->flags[rank], epoch);             // "my pushes of this epoch are done"
+    unsigned polls = 0;
+    // epochs only grow; a difference test survives the 32-bit wrap
+    while (int(ld_acquire_sys(&mine->flags[j]) - epoch) < 0) {
+      if (++polls >= spin_limit) {
+        *reinterpret_cast<volatile int*>(status) = 1 + j;    // gave up waiting for rank j
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mine->epoch = epoch;
+}
+
+// Copy the landing half that the LAST barrier completed into ordinary tensors.
+template <typename U>
+__global__ void fetch_kernel(Ptrs3 dst, const void* landing_mine, size_t half_bytes, int n_tensors,
+                             int64_t units_per_tensor) {
+  const Control* ctl = static_cast<const Control*>(landing_mine);
+  const unsigned half = (ctl->epoch - 1u) & 1u;
+  const U* src = reinterpret_cast<const U*>(static_cast<const char*>(landing_mine) +
+                                            sizeof(Control) + half * half_bytes);
+  const int64_t total = units_per_tensor * n_tensors;
+  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int t = int(i / units_per_tensor);
+    static_cast<U*>(dst.p[t])[i - t * units_per_tensor] = src[i];
+  }
+}
+
+int grid_for(int64_t n) {
+  int64_t b = (n + kThreads - 1) / kThreads;
+  const int64_t cap = int64_t(kSmCount) * 8;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return int(b);
+}
+
+int fill_table(PeerTable* tab, void* const* peers, int world) {
+  TGT_CHECK_ARG(world >= 1 && world <= kMaxWorld, "world must be between 1 and 16");
+  TGT_CHECK_ARG(peers != nullptr, "peer table is null");
+  for (int i = 0; i < kMaxWorld; ++i) tab->p[i] = nullptr;
+  for (int i = 0; i < world; ++i) {
+    TGT_CHECK_ARG(peers[i] != nullptr && aligned16(peers[i]), "peer landing pointers must be non-null and 16-byte aligned");
+    tab->p[i] = peers[i];
+  }
+  return TGT_OK;
+}
+
+}  // namespace
+}  // namespace tgt
+
+extern "C" size_t tgt_p2p_control_bytes(void) { return sizeof(tgt::Control); }
+
+extern "C" int tgt_p2p_push(const void* x0, const void* x1, const void* x2, int n_tensors,
+                            void* const* peer_landing, size_t half_bytes, int64_t outer_s,
+                            int64_t width_s_bytes, int64_t width_g_bytes, int world, int rank,
+                            const int32_t* alias_rows, int n_alias, int64_t alias_row_bytes,
+                            void* stream_) {
+  using namespace tgt;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  TGT_CHECK_ARG(n_tensors >= 1 && n_tensors <= 3, "n_tensors must be 1, 2 or 3");
+  const void* xs[3] = {x0, x1, x2};
+  for (int t = 0; t < 3; ++t)
+    TGT_CHECK_ARG((t < n_tensors) == (xs[t] != nullptr), "tensor pointers do not match n_tensors");
+  TGT_CHECK_ARG(rank >= 0 && rank < world, "rank outside the world");
+  TGT_CHECK_ARG(outer_s >= 1 && width_s_bytes >= 16 && width_g_bytes >= 16, "sizes must be positive");
+  TGT_CHECK_ARG(width_s_bytes % 16 == 0 && width_g_bytes % 16 == 0,
+                "per-peer widths must be multiples of 16 bytes");
+  TGT_CHECK_ARG((outer_s * width_s_bytes) % width_g_bytes == 0, "chunk is not a whole number of destination rows");
+  TGT_CHECK_ARG(aligned16(x0) && aligned16(x1) && aligned16(x2), "tensors must be 16-byte aligned");
+  TGT_CHECK_ARG(half_bytes % 16 == 0 &&
+                    size_t(n_tensors) * size_t(outer_s) * size_t(width_s_bytes) * size_t(world) <= half_bytes,
+                "the landing half is too small for this exchange");
+  TGT_CHECK_ARG(n_alias >= 0 && (n_alias == 0 || (alias_rows != nullptr && alias_row_bytes >= 16 &&
+                                                  alias_row_bytes % 16 == 0)),
+                "bad alias row arguments");
+  PeerTable tab;
+  int rc = fill_table(&tab, peer_landing, world);
+  if (rc != TGT_OK) return rc;
+  Ptrs3 src;
+  for (int t = 0; t < 3; ++t) src.p[t] = const_cast<void*>(xs[t]);
+  const int64_t ws = width_s_bytes / 16, wg = width_g_bytes / 16;
+  const int64_t total = outer_s * ws * world * n_tensors;
+  push_kernel<uint4><<<grid_for(total), kThreads, 0, stream>>>(
+      src, tab, static_cast<const Control*>(tab.p[rank]), half_bytes, n_tensors, outer_s, ws, wg,
+      world, rank, alias_rows, n_alias, n_alias > 0 ? alias_row_bytes / 16 : 1);
+  TGT_CHECK_CUDA(cudaGetLastError());
+  return TGT_OK;
+}
+
+extern "C" int tgt_p2p_barrier(void* const* peer_landing, int world, int rank, uint32_t spin_limit,
+                               int32_t* status, void* stream_) {
+  using namespace tgt;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  TGT_CHECK_ARG(rank >= 0 && rank < world, "rank outside the world");
+  TGT_CHECK_ARG(status != nullptr, "status is null");
+  TGT_CHECK_ARG(spin_limit >= 1, "spin_limit must be >= 1");
+  PeerTable tab;
+  int rc = fill_table(&tab, peer_landing, world);
+  if (rc != TGT_OK) return rc;
+  barrier_kernel<<<1, 32, 0, stream>>>(tab, world, rank, spin_limit, status);
+  TGT_CHECK_CUDA(cudaGetLastError());
+  return TGT_OK;
+}
+
+extern "C" int tgt_p2p_fetch(const void* landing_mine, size_t half_bytes, int n_tensors, void* y0,
+                             void* y1, void* y2, int64_t bytes_per_tensor, void* stream_) {
+  using namespace tgt;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  TGT_CHECK_ARG(n_tensors >= 1 && n_tensors <= 3, "n_tensors must be 1, 2 or 3");
+  void* ys[3] = {y0, y1, y2};
+  for (int t = 0; t < 3; ++t)
+    TGT_CHECK_ARG((t < n_tensors) == (ys[t] != nullptr), "tensor pointers do not match n_tensors");
+  TGT_CHECK_ARG(landing_mine != nullptr && aligned16(landing_mine), "landing pointer is null or misaligned");
+  TGT_CHECK_ARG(bytes_per_tensor >= 16 && bytes_per_tensor % 16 == 0, "bytes_per_tensor must be a multiple of 16");
+  TGT_CHECK_ARG(size_t(bytes_per_tensor) * n_tensors <= half_bytes, "the landing half is smaller than the request");
+  TGT_CHECK_ARG(aligned16(y0) && aligned16(y1) && aligned16(y2), "tensors must be 16-byte aligned");
+  Ptrs3 dst;
+  for (int t = 0; t < 3; ++t) dst.p[t] = ys[t];
+  const int64_t units = bytes_per_tensor / 16;
+  fetch_kernel<uint4><<<grid_for(units * n_tensors), kThreads, 0, stream>>>(dst, landing_mine, half_bytes,
+                                                                            n_tensors, units);
+  TGT_CHECK_CUDA(cudaGetLastError());
+  return TGT_OK;
+}

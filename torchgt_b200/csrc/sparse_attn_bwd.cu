@@ -272,7 +272,7 @@ __device__ __forceinline__ DkvPolicy<T, LPH, G> make_dkv_policy(const BwdParams&
 }
 
 template <typename T, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) bwd_dq_kernel(const BwdParams p) {
+__global__ void TGT_WALK_BOUNDS bwd_dq_kernel(const BwdParams p) {
   using Policy = DqPolicy<T, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
   const Policy pol = make_dq_policy<T, LPH, G>(p);
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(kBlockThreads) bwd_dq_stitch_kernel(const BwdP
 }
 
 template <typename T, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) bwd_dkv_kernel(const BwdParams p) {
+__global__ void TGT_WALK_BOUNDS bwd_dkv_kernel(const BwdParams p) {
   using Policy = DkvPolicy<T, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
   const Policy pol = make_dkv_policy<T, LPH, G>(p);
@@ -303,8 +303,19 @@ __global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const Bwd
   stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
-constexpr int kDqCtasPerSm = 4;
-constexpr int kDkvCtasPerSm = 4;
+int bwd_resident_ctas(int dtype, const HeadSplit& hs, bool dkv) {
+  static int cache[2][2][6][6] = {};
+  auto log2i = [](int x) { int l = 0; while ((1 << l) < x) ++l; return l; };
+  int* slot = &cache[dkv ? 1 : 0][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
+  int result = 4;
+#define TGT_OCC_DQ(T, LPH, G) result = resident_ctas(bwd_dq_kernel<T, LPH, G>, slot)
+#define TGT_OCC_DKV(T, LPH, G) result = resident_ctas(bwd_dkv_kernel<T, LPH, G>, slot)
+  if (dkv) TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DKV);
+  else TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DQ);
+#undef TGT_OCC_DQ
+#undef TGT_OCC_DKV
+  return result;
+}
 
 struct BwdScratch {
   size_t stats, carry_a, carry_b, total;
@@ -314,8 +325,8 @@ struct BwdScratch {
 BwdScratch plan_bwd_scratch(const tgt_layout* by_dst, const HeadSplit& hs, int heads, int dtype) {
   BwdScratch s;
   const int vec = dtype == TGT_F32 ? 4 : 8;
-  s.plan_a = plan_tiles(by_dst->n_edges, hs, vec, kDqCtasPerSm);
-  s.plan_b = plan_tiles(by_dst->n_edges, hs, 2 * vec, kDkvCtasPerSm);
+  s.plan_a = plan_tiles(by_dst->n_edges, hs, vec, bwd_resident_ctas(dtype, hs, false));
+  s.plan_b = plan_tiles(by_dst->n_edges, hs, 2 * vec, bwd_resident_ctas(dtype, hs, true));
   size_t off = 0;
   s.stats = off; off += round_up(size_t(by_dst->n_rows) * heads * 8, 256);
   s.carry_a = off; off += s.plan_a.carry_bytes;

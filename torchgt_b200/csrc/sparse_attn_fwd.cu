@@ -108,7 +108,7 @@ __device__ __forceinline__ FwdPolicy<T, LPH, G> make_policy(const FwdParams& p) 
 }
 
 template <typename T, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) fwd_kernel(const FwdParams p) {
+__global__ void TGT_WALK_BOUNDS fwd_kernel(const FwdParams p) {
   using Policy = FwdPolicy<T, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
   const Policy pol = make_policy<T, LPH, G>(p);
@@ -124,7 +124,17 @@ __global__ void __launch_bounds__(kBlockThreads) fwd_stitch_kernel(const FwdPara
   stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
-constexpr int kFwdCtasPerSm = 5;
+// Resident CTAs per SM of fwd_kernel<T, LPH, G> for the run-time triple.
+int fwd_resident_ctas(int dtype, const HeadSplit& hs) {
+  static int cache[2][6][6] = {};
+  auto log2i = [](int x) { int l = 0; while ((1 << l) < x) ++l; return l; };
+  int* slot = &cache[dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
+  int result = 4;
+#define TGT_OCC_FWD(T, LPH, G) result = resident_ctas(fwd_kernel<T, LPH, G>, slot)
+  TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_FWD);
+#undef TGT_OCC_FWD
+  return result;
+}
 
 }  // namespace
 
@@ -141,7 +151,7 @@ size_t fwd_scratch_bytes(const tgt_layout* L, int heads, int head_dim, int dtype
   HeadSplit hs;
   if (!split_heads(heads, head_dim, dtype, &hs) || L->n_edges == 0) return 0;
   const int nacc = (dtype == TGT_F32 ? 4 : 8) + 1;
-  return plan_tiles(L->n_edges, hs, nacc, kFwdCtasPerSm).carry_bytes;
+  return plan_tiles(L->n_edges, hs, nacc, fwd_resident_ctas(dtype, hs)).carry_bytes;
 }
 
 }  // namespace tgt
@@ -180,7 +190,7 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
     return TGT_OK;
   }
   const int nacc = (dtype == TGT_F32 ? 4 : 8) + 1;
-  const TilePlan tp = plan_tiles(L.n_edges, hs, nacc, kFwdCtasPerSm);
+  const TilePlan tp = plan_tiles(L.n_edges, hs, nacc, fwd_resident_ctas(dtype, hs));
   if (scratch == nullptr || scratch_bytes < tp.carry_bytes)
     return set_error(TGT_ERR_WORKSPACE, "scratch holds %zu bytes, %zu needed", scratch_bytes,
                      tp.carry_bytes);

@@ -15,8 +15,8 @@ from torch import Tensor
 from torch.nn import Module
 
 from .exchange import _exchange, seq_all_to_all_many
-from .initialize import (get_sequence_parallel_group, get_sequence_parallel_rank,
-                         get_sequence_parallel_world_size)
+from .initialize import (get_global_token_rows_on, get_last_batch_flag, get_sequence_parallel_group,
+                         get_sequence_parallel_rank, get_sequence_parallel_world_size)
 from .utils import (copy_global_token0, extend_global_token, extend_global_token0, merge_global_token,
                     merge_global_token0)
 
@@ -94,9 +94,9 @@ class _UlyssesBase(Module):
         """[b, s/p(+1), H, D] x3 -> [b, s(+p), H/p, D] x3 in one collective."""
         return seq_all_to_all_many(self.spg, [query, key, value], self.scatter_idx, self.gather_idx)
 
-    def _scatter_sequence(self, context: Tensor) -> Tensor:
-        """[b, s(+p), (H/p) D] -> [b, s/p(+1), H D]."""
-        return seq_all_to_all_many(self.spg, [context], self.gather_idx, self.scatter_idx)[0]
+    def _scatter_sequence(self, context: Tensor, alias_rows=None) -> Tensor:
+        """[b, s(+p), (H/p) D] -> [b, s/p(+1), H D]; rows listed in alias_rows travel as copies of row 0."""
+        return seq_all_to_all_many(self.spg, [context], self.gather_idx, self.scatter_idx, alias_rows)[0]
 
 
 class DistributedAttention(_UlyssesBase):
@@ -167,5 +167,9 @@ class DistributedAttentionNoMerge(_UlyssesBase):
         if bias is not None:  # [b, s/p+1, s+1, H] -> [b, s+p, s+1, H/p] -> [b, s+p, s+p, H/p]
             bias = extend_global_token0(_SeqAllToAll.apply(self.spg, bias, 3, 1), extend_dim=2)
         context = self.local_attn(q, k, v, bias, edge_index, attn_type, *args)
+        if context.is_cuda:
+            # copy_global_token0 folded into the exchange: the slots are filled while the data moves
+            rows = get_global_token_rows_on(context.device, get_last_batch_flag())
+            return self._scatter_sequence(context, alias_rows=rows)
         context = copy_global_token0(context, extend_dim=1)
         return self._scatter_sequence(context)
