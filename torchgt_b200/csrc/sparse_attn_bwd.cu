@@ -77,8 +77,9 @@ struct DqPolicy {
   bool head_leader, group_leader;
   float inv_scale;
 
+  using Raw = typename Vec16<T>::Raw;
   struct Operands {
-    float k[VEC], v[VEC], q[VEC], g[VEC];
+    Raw k, v, q, g;  // packed 16-byte pieces, unpacked where they are used
     float2 st;
     float b;
   };
@@ -89,22 +90,26 @@ struct DqPolicy {
   __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
     const unsigned so = unsigned(src) * row_vecs + cvec;
     const unsigned ro = unsigned(row) * row_vecs + cvec;
-    Vec16<T>::load_at(k, so, o.k);
-    Vec16<T>::load_at(v, so, o.v);
-    Vec16<T>::load_at(q, ro, o.q);
-    Vec16<T>::load_at(dout, ro, o.g);
+    o.k = Vec16<T>::raw_at(k, so);
+    o.v = Vec16<T>::raw_at(v, so);
+    o.q = Vec16<T>::raw_at(q, ro);
+    o.g = Vec16<T>::raw_at(dout, ro);
     o.st = __ldg(stats + int64_t(row) * heads + head);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
   __device__ __forceinline__ void clear(Operands& o) const {
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o.k[j] = o.v[j] = o.q[j] = o.g[j] = 0.f;
+    o.k = o.v = o.q = o.g = Vec16<T>::raw_zero();
     o.st = make_float2(0.f, 0.f);
     o.b = 0.f;
   }
   __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int pe) const {
-    const float raw = group_sum<LPH>(dot<VEC>(o.q, o.k)) * inv_scale;
-    const float gv = group_sum<LPH>(dot<VEC>(o.g, o.v));
+    float a[VEC], b[VEC];
+    Vec16<T>::unpack(o.q, a);
+    Vec16<T>::unpack(o.k, b);
+    const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
+    Vec16<T>::unpack(o.g, a);
+    Vec16<T>::unpack(o.v, b);
+    const float gv = group_sum<LPH>(dot<VEC>(a, b));
     const float wgt = fast_exp(clamp_score(raw) + o.b);
     const float dt = valid ? (gv - o.st.y) * o.st.x * wgt : 0.f;
     if (dbias != nullptr) {
@@ -122,8 +127,10 @@ struct DqPolicy {
   }
   __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
                                              const Scalars& s) const {
+    float kf[VEC];
+    Vec16<T>::unpack(o.k, kf);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) acc[j] = fmaf(s.da, o.k[j], acc[j]);
+    for (int j = 0; j < VEC; ++j) acc[j] = fmaf(s.da, kf[j], acc[j]);
   }
   __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {
     float o[VEC];
@@ -158,8 +165,9 @@ struct DkvPolicy {
   int heads, head;
   float inv_scale;
 
+  using Raw = typename Vec16<T>::Raw;
   struct Operands {
-    float q[VEC], g[VEC], k[VEC], v[VEC];
+    Raw q, g, k, v;  // packed 16-byte pieces, unpacked where they are used
     float2 st;
     float b;
   };
@@ -171,22 +179,26 @@ struct DkvPolicy {
   __device__ __forceinline__ void load(Operands& o, int row, int dst, int pe) const {
     const unsigned d = unsigned(dst) * row_vecs + cvec;
     const unsigned ro = unsigned(row) * row_vecs + cvec;
-    Vec16<T>::load_at(q, d, o.q);
-    Vec16<T>::load_at(dout, d, o.g);
-    Vec16<T>::load_at(k, ro, o.k);
-    Vec16<T>::load_at(v, ro, o.v);
+    o.q = Vec16<T>::raw_at(q, d);
+    o.g = Vec16<T>::raw_at(dout, d);
+    o.k = Vec16<T>::raw_at(k, ro);
+    o.v = Vec16<T>::raw_at(v, ro);
     o.st = __ldg(stats + int64_t(dst) * heads + head);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
   __device__ __forceinline__ void clear(Operands& o) const {
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o.k[j] = o.v[j] = o.q[j] = o.g[j] = 0.f;
+    o.k = o.v = o.q = o.g = Vec16<T>::raw_zero();
     o.st = make_float2(0.f, 0.f);
     o.b = 0.f;
   }
   __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
-    const float raw = group_sum<LPH>(dot<VEC>(o.q, o.k)) * inv_scale;
-    const float gv = group_sum<LPH>(dot<VEC>(o.g, o.v));
+    float a[VEC], b[VEC];
+    Vec16<T>::unpack(o.q, a);
+    Vec16<T>::unpack(o.k, b);
+    const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
+    Vec16<T>::unpack(o.g, a);
+    Vec16<T>::unpack(o.v, b);
+    const float gv = group_sum<LPH>(dot<VEC>(a, b));
     const float wgt = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
     const float dt = (gv - o.st.y) * o.st.x * wgt;
     Scalars s;
@@ -196,10 +208,13 @@ struct DkvPolicy {
   }
   __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
                                              const Scalars& s) const {
+    float qf[VEC], gf[VEC];
+    Vec16<T>::unpack(o.q, qf);
+    Vec16<T>::unpack(o.g, gf);
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
-      acc[j] = fmaf(s.da, o.q[j], acc[j]);
-      acc[VEC + j] = fmaf(s.wi, o.g[j], acc[VEC + j]);
+      acc[j] = fmaf(s.da, qf[j], acc[j]);
+      acc[VEC + j] = fmaf(s.wi, gf[j], acc[VEC + j]);
     }
   }
   __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {

@@ -23,8 +23,9 @@ struct FwdPolicy {
   bool z_writer;                   // one lane per head stores Z
   float inv_scale;
 
+  using Raw = typename Vec16<T>::Raw;
   struct Operands {
-    float k[VEC], v[VEC], q[VEC];
+    Raw k, v, q;  // packed 16-byte pieces, unpacked where they are used
     float b;
   };
   struct Scalars {
@@ -33,26 +34,30 @@ struct FwdPolicy {
 
   __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
     const unsigned so = unsigned(src) * row_vecs + cvec;
-    Vec16<T>::load_at(k, so, o.k);
-    Vec16<T>::load_at(v, so, o.v);
-    Vec16<T>::load_at(q, unsigned(row) * row_vecs + cvec, o.q);
+    o.k = Vec16<T>::raw_at(k, so);
+    o.v = Vec16<T>::raw_at(v, so);
+    o.q = Vec16<T>::raw_at(q, unsigned(row) * row_vecs + cvec);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
   __device__ __forceinline__ void clear(Operands& o) const {
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o.k[j] = o.v[j] = o.q[j] = 0.f;
+    o.k = o.v = o.q = Vec16<T>::raw_zero();
     o.b = 0.f;
   }
   __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
-    const float raw = group_sum<LPH>(dot<VEC>(o.q, o.k)) * inv_scale;
+    float qf[VEC], kf[VEC];
+    Vec16<T>::unpack(o.q, qf);
+    Vec16<T>::unpack(o.k, kf);
+    const float raw = group_sum<LPH>(dot<VEC>(qf, kf)) * inv_scale;
     Scalars s;
     s.w = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
     return s;
   }
   __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
                                              const Scalars& s) const {
+    float vf[VEC];
+    Vec16<T>::unpack(o.v, vf);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) acc[j] = fmaf(s.w, o.v[j], acc[j]);
+    for (int j = 0; j < VEC; ++j) acc[j] = fmaf(s.w, vf[j], acc[j]);
     acc[VEC] += s.w;
   }
   __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {

@@ -49,6 +49,15 @@ struct Vec16<float> {
   __device__ __forceinline__ static void store(float* p, const float (&r)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(r[0], r[1], r[2], r[3]);
   }
+  // Packed form of one 16-byte piece: operands wait in registers in this form until they are used.
+  using Raw = float4;
+  __device__ __forceinline__ static Raw raw_at(const float* base, unsigned v) {
+    return __ldg(reinterpret_cast<const float4*>(base) + v);
+  }
+  __device__ __forceinline__ static Raw raw_zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ static void unpack(const Raw& t, float (&r)[4]) {
+    r[0] = t.x; r[1] = t.y; r[2] = t.z; r[3] = t.w;
+  }
   // The same with the position given as a 32-bit index in units of 16 bytes (cheaper addressing).
   __device__ __forceinline__ static void load_at(const float* base, unsigned v, float (&r)[4]) {
     load(reinterpret_cast<const float*>(reinterpret_cast<const float4*>(base) + v), r);
@@ -79,6 +88,19 @@ struct Vec16<__nv_bfloat16> {
       w[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  using Raw = uint4;
+  __device__ __forceinline__ static Raw raw_at(const __nv_bfloat16* base, unsigned v) {
+    return __ldg(reinterpret_cast<const uint4*>(base) + v);
+  }
+  __device__ __forceinline__ static Raw raw_zero() { return make_uint4(0u, 0u, 0u, 0u); }
+  __device__ __forceinline__ static void unpack(const Raw& t, float (&r)[8]) {
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      r[2 * i] = __uint_as_float(w[i] << 16);
+      r[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
   }
   __device__ __forceinline__ static void load_at(const __nv_bfloat16* base, unsigned v,
                                                  float (&r)[8]) {
