@@ -71,17 +71,27 @@ int forced_ge();  // 0 unless tgt_debug_set_tile_edges() overrides the choice
 
 inline int choose_ge(int64_t n_edges, int g, int ctas_per_sm) {
   const int ng = kBlockThreads / g;
+  const int ge_max = host_ge_max(g);
   if (forced_ge() > 0) {
     int f = (forced_ge() + kUnroll - 1) / kUnroll * kUnroll;
-    return f > host_ge_max(g) ? host_ge_max(g) : f;
+    return f > ge_max ? ge_max : f;
   }
-  const int64_t groups = int64_t(kSmCount) * ctas_per_sm * ng;
-  int64_t ge = (n_edges + groups - 1) / groups;
-  ge = (ge + kUnroll - 1) / kUnroll * kUnroll;
-  const int lo = 4 * kUnroll > host_ge_max(g) ? host_ge_max(g) : 4 * kUnroll;
-  if (ge < lo) ge = lo;
-  if (ge > host_ge_max(g)) ge = host_ge_max(g);
-  return int(ge);
+  // Time is roughly (number of CTA waves) x (work of one tile); a tile costs its ge edges per lane
+  // group plus a fixed part (index staging, barriers, stitching) worth about 8 edges.  Few, full
+  // waves win; with many waves the tail does not matter and larger tiles amortise the fixed part.
+  const int64_t capacity = int64_t(kSmCount) * ctas_per_sm;
+  int best = ge_max;
+  double best_cost = 1e300;
+  for (int ge = (ge_max < 16 ? ge_max : 16); ge <= ge_max; ge += kUnroll) {
+    const int64_t tiles = (n_edges + int64_t(ng) * ge - 1) / (int64_t(ng) * ge);
+    const int64_t waves = (tiles + capacity - 1) / capacity;
+    const double cost = double(waves) * (ge + 8);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = ge;
+    }
+  }
+  return best;
 }
 
 template <int VEC>
@@ -135,14 +145,21 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
   const int64_t t0 = int64_t(blockIdx.x) * te;
   const int n = int(min(int64_t(te), int64_t(w.n_edges) - t0));  // edges in this tile (>= 1)
 
-  // ---- stage the tile's indices: s_seg[i + 1] = row of tile edge i, with one edge of halo each side
-  for (int i = tid; i < n + 2; i += kBlockThreads) {
-    const int64_t e = t0 - 1 + i;
-    s_seg[i] = e < 0 ? -1 : (e >= w.n_edges ? -2 : __ldg(w.seg + e));
-  }
+  // ---- stage the tile's indices.  Tile edge i lives at position i + i / ge: one pad word per
+  // lane-group range, so the groups of a warp (which read ranges ge apart) hit different banks.
+  // The rows of the edge before and after the tile go to the two words behind the padded array.
+  const int ge = w.ge;
+  auto pos = [ge](int i) { return i + i / ge; };
+  int32_t* s_halo = s_seg + TileGeom<G>::TE_MAX + NG;   // [0] = row before the tile, [1] = row after
   for (int i = tid; i < n; i += kBlockThreads) {
-    s_other[i] = __ldg(w.other + t0 + i);
-    if (w.need_perm) s_perm[i] = __ldg(w.perm + t0 + i);
+    const int p = pos(i);
+    s_seg[p] = __ldg(w.seg + t0 + i);
+    s_other[p] = __ldg(w.other + t0 + i);
+    if (w.need_perm) s_perm[p] = __ldg(w.perm + t0 + i);
+  }
+  if (tid == 0) {
+    s_halo[0] = t0 == 0 ? -1 : __ldg(w.seg + t0 - 1);
+    s_halo[1] = t0 + n >= w.n_edges ? -2 : __ldg(w.seg + t0 + n);
   }
   for (int i = tid; i < 2 * NG; i += kBlockThreads) s_carry_row[i] = -3;  // [g][0] head row, [g][1] tail row
   __syncthreads();
@@ -153,8 +170,11 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
   float acc[NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
-  int cur = s_seg[gb];                         // row of the edge just before the range
-  bool own = gb < gend && s_seg[gb + 1] == cur;  // the range starts inside row `cur`
+  // row of tile edge i, for i in [-1, n]
+  auto row_of = [&](int i) { return i < 0 ? s_halo[0] : (i >= n ? s_halo[1] : s_seg[pos(i)]); };
+  int cur = row_of(gb - 1);                          // row of the edge just before the range
+  bool own = gb < gend && row_of(gb) == cur;         // the range starts inside row `cur`
+  const int gb_pos = pos(gb);                        // the range is contiguous in padded positions
   bool head_pending = own;
   float* my_head = s_carry + (g * 2 + 0) * (G * NACC) + c * NACC;
   float* my_tail = s_carry + (g * 2 + 1) * (G * NACC) + c * NACC;
@@ -170,8 +190,8 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
     for (int u = 0; u < kUnroll; ++u) {
       const int i = first + u;
       valid[u] = FULL || i < gend;
-      const int ii = valid[u] ? i : 0;
-      row[u] = s_seg[ii + 1];
+      const int ii = valid[u] ? gb_pos + (i - gb) : 0;
+      row[u] = s_seg[ii];
       pe[u] = w.need_perm ? s_perm[ii] : 0;
       if (valid[u]) pol.load(ops[u], row[u], s_other[ii], pe[u]);
       else pol.clear(ops[u]);
@@ -213,7 +233,7 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
     for (int b = 0; b < batches; ++b) batch(gb + b * kUnroll, std::false_type{});
   }
   if (gb < gend) {  // close the last row of the range
-    const bool cont_out = s_seg[gend + 1] == cur;
+    const bool cont_out = row_of(gend) == cur;
     if (head_pending) {
 #pragma unroll
       for (int a = 0; a < NACC; ++a) my_head[a] = acc[a];
@@ -231,15 +251,15 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
   __syncthreads();
 
   // ---- stitch rows that cross group boundaries, in group order
-  const int last_row = s_seg[n];            // row of the tile's last edge
-  const bool tile_cont_out = s_seg[n + 1] == last_row;
+  const int last_row = row_of(n - 1);       // row of the tile's last edge
+  const bool tile_cont_out = s_halo[1] == last_row;
   const int lanes_all = gridDim.y * G;
   float* tile_carry = w.gcarry + (int64_t(blockIdx.x) * 2) * (int64_t(lanes_all) * NACC) +
                       int64_t(blockIdx.y * G + c) * NACC;
-  if (g == 0 && s_seg[0] == s_seg[1]) {
+  if (g == 0 && s_halo[0] == row_of(0)) {
     // the tile starts inside a row that began in an earlier tile: sum its heads into the tile's
     // head carry
-    const int r = s_seg[1];
+    const int r = row_of(0);
 #pragma unroll
     for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
     for (int j = 0; j < NG && s_carry_row[j * 2] == r; ++j) {
@@ -406,9 +426,9 @@ template <int G, int NACC>
 struct TileSmem {
   static constexpr int TE = TileGeom<G>::TE_MAX;
   static constexpr int NG = TileGeom<G>::NG;
-  int32_t other[TE];
-  int32_t seg[TE + 4];
-  int32_t perm[TE];
+  int32_t other[TE + NG];
+  int32_t seg[TE + NG + 2];   // padded rows + the two halo words
+  int32_t perm[TE + NG];
   float carry[NG * 2 * G * NACC];
   int32_t carry_row[NG * 2];
 };
