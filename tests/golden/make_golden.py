@@ -14,6 +14,8 @@ Outputs (all small .npz files, committed):
   attn_*.npz     CoreAttention.sparse_attention_bias forward + autograd gradients
   edges.npz      fix_edge_index / adjust_edge_index_nomerge / flatten_edge_index_nopad known answers
   ulysses_P*.npz _SeqAllToAll both directions and the DistributedAttentionNoMerge layer, P ranks
+  graphormer_node_level.npz  the reference's node-level Graphormer: parameters, log-probabilities, loss and
+                 parameter gradients of one training step (3 layers, dropout 0, one rank)
 """
 from __future__ import annotations
 
@@ -195,6 +197,60 @@ def _ulysses_worker(rank, world, ref_path, port, out_path):
     dist.destroy_process_group()
 
 
+def _model_worker(rank, world, ref_path, port, out_path):
+    """Reference node-level Graphormer, one rank (the exchange degenerates to a copy), dropout 0."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ref_path)
+    install_shims()
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def all_to_all_copy(output_list, input_list, group=None):
+        for o, i in zip(output_list, input_list):
+            o.copy_(i)
+    dist.all_to_all = all_to_all_copy
+    torch.distributed.all_to_all = all_to_all_copy
+    import gt_sp.initialize as init
+    n = 300
+    init._GLOBAL_TOKEN_NUM = 1
+    init.initialize_sequence_parallel(n, 1, 1, 1)
+    init.set_global_token_indices([0])
+    from models.graphormer_dist_node_level import Graphormer
+    from gt_sp.utils import adjust_edge_index_nomerge, fix_edge_index
+    torch.manual_seed(11)
+    model = Graphormer(3, 8, 24, 64, 7, 1, 0.0, 0.0, 0.0, 64, 1)
+    # the reference initialises with std 0.02/sqrt(L): scale up so that attention scores are not all ~0
+    with torch.no_grad():
+        for p_ in model.parameters():
+            p_.mul_(8.0)
+    gen = torch.Generator().manual_seed(12)
+    x = torch.randn(n, 24, generator=gen)
+    y = torch.randint(0, 7, (n,), generator=gen)
+    raw = torch.cat([torch.randint(0, n, (2, 6 * n), generator=gen), torch.arange(n).repeat(2, 1)], dim=1)
+    ei = adjust_edge_index_nomerge(fix_edge_index(raw, n), n)
+    model.train()
+    out = model(x, None, ei, attn_type="sparse")
+    loss = torch.nn.functional.nll_loss(out, y)
+    loss.backward()
+    rec = {"x": x.numpy(), "y": y.numpy(), "edge_index": ei.numpy(), "out": out.detach().numpy(),
+           "loss": np.float64(loss.item())}
+    for name, p_ in model.state_dict().items():
+        rec["param/" + name] = p_.numpy()
+    for name, p_ in model.named_parameters():
+        if p_.grad is not None:
+            rec["grad/" + name] = p_.grad.numpy()
+    n_params = sum(p_.numel() for p_ in Graphormer(4, 8, 128, 64, 40, 1, 0.0, 0.0, 0.0, 64, 1).parameters())
+    rec["params_of_the_readme_model"] = np.int64(n_params)     # the reference's README logs 111913
+    np.savez_compressed(out_path, **rec)
+    print("wrote", out_path, "loss", loss.item(), "params(4L/64/8h/128->40)", n_params)
+    dist.destroy_process_group()
+
+
+def make_model_case(ref_path):
+    import torch.multiprocessing as mp
+    mp.spawn(_model_worker, args=(1, ref_path, 29621, str(OUT_DIR / "graphormer_node_level.npz")), nprocs=1, join=True)
+
+
 def make_ulysses_cases(ref_path):
     import torch.multiprocessing as mp
     for i, world in enumerate((2, 4)):
@@ -212,6 +268,7 @@ def main():
     make_attention_cases()
     make_edge_cases()
     make_ulysses_cases(args.reference)
+    make_model_case(args.reference)
 
 
 if __name__ == "__main__":

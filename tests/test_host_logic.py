@@ -125,3 +125,15 @@ def test_product_code_never_imports_the_oracle():
     for path in pkg.rglob("*.py"):
         text = path.read_text()
         assert "import oracle" not in text and "from oracle" not in text, path
+
+
+def test_graphormer_shell_loads_reference_checkpoints_and_counts_the_same_parameters(sp_state):
+    from torchgt_b200.graphormer import Graphormer
+    g = load_golden("graphormer_node_level.npz")
+    model = Graphormer(3, 8, 24, 64, 7, 1, 0.0, 0.0, 0.0, 64, 1)
+    state = {k[len("param/"):]: torch.from_numpy(v) for k, v in g.items() if k.startswith("param/")}
+    assert sorted(state) == sorted(model.state_dict())          # same keys as the reference's state_dict
+    model.load_state_dict(state, strict=True)
+    readme_model = Graphormer(4, 8, 128, 64, 40, 1, 0.3, 0.1, 0.5, 64, 1)
+    n = sum(p.numel() for p in readme_model.parameters())
+    assert n == 111913 == int(g["params_of_the_readme_model"])   # the count the reference's README logs

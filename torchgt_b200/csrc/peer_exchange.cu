@@ -57,34 +57,46 @@ __global__ void push_kernel(Ptrs3 src, PeerTable landing, const Control* __restr
                             size_t half_bytes, int n_tensors, int64_t outer_s, int64_t ws,
                             int64_t wg, int world, int rank, const int32_t* __restrict__ alias_rows,
                             int n_alias, int64_t alias_period_units) {
+  constexpr int kBatch = 4;  // loads in flight per thread before the (posted) remote stores
   const unsigned half = ctl->epoch & 1u;
   const int64_t chunk = outer_s * ws;                       // units one peer gets per tensor
   const int64_t per_tensor_dst = chunk * world;             // units of one destination tensor
   const int64_t total = chunk * world * n_tensors;
-  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total;
-       i += int64_t(gridDim.x) * blockDim.x) {
-    // i enumerates (peer, tensor, f) with f fastest: consecutive threads write consecutive units
-    const int64_t f = i % chunk;
-    const int t = int((i / chunk) % n_tensors);
-    const int peer = int(i / (chunk * n_tensors));
-    const int64_t a = f / ws;
-    const int64_t w = f % ws;
-    int64_t pos = int64_t(peer) * ws + w;   // unit position inside outer row a of the source
-    if (n_alias > 0) {
-      // rows listed in alias_rows are read from row 0 of the same outer row instead
-      // (copy_global_token0 folded into the transfer); a row is alias_period_units wide
-      const int64_t row = pos / alias_period_units;
-      for (int j = 0; j < n_alias; ++j)
-        if (row == alias_rows[j]) {
-          pos = pos % alias_period_units;
-          break;
-        }
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i0 = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i0 < total;
+       i0 += stride * kBatch) {
+    U val[kBatch];
+    U* dst[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      // i enumerates (peer, tensor, f) with f fastest: consecutive threads write consecutive units
+      const int64_t i = i0 + u * stride;
+      dst[u] = nullptr;
+      if (i >= total) continue;
+      const int64_t f = i % chunk;
+      const int t = int((i / chunk) % n_tensors);
+      const int peer = int(i / (chunk * n_tensors));
+      const int64_t a = f / ws;
+      const int64_t w = f % ws;
+      int64_t pos = int64_t(peer) * ws + w;   // unit position inside outer row a of the source
+      if (n_alias > 0) {
+        // rows listed in alias_rows are read from row 0 of the same outer row instead
+        // (copy_global_token0 folded into the transfer); a row is alias_period_units wide
+        const int64_t row = pos / alias_period_units;
+        for (int j = 0; j < n_alias; ++j)
+          if (row == alias_rows[j]) {
+            pos = pos % alias_period_units;
+            break;
+          }
+      }
+      val[u] = static_cast<const U*>(src.p[t])[a * world * ws + pos];
+      const int64_t og = f / wg, o = f % wg;
+      dst[u] = reinterpret_cast<U*>(static_cast<char*>(landing.p[peer]) + sizeof(Control) +
+                                    half * half_bytes) + t * per_tensor_dst + (og * world + rank) * wg + o;
     }
-    const U val = static_cast<const U*>(src.p[t])[a * world * ws + pos];
-    const int64_t og = f / wg, o = f % wg;
-    U* dst = reinterpret_cast<U*>(static_cast<char*>(landing.p[peer]) + sizeof(Control) +
-                                  half * half_bytes) + t * per_tensor_dst;
-    dst[(og * world + rank) * wg + o] = val;
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u)
+      if (dst[u] != nullptr) *dst[u] = val[u];
   }
 }
 
@@ -124,10 +136,23 @@ __global__ void fetch_kernel(Ptrs3 dst, const void* landing_mine, size_t half_by
   const U* src = reinterpret_cast<const U*>(static_cast<const char*>(landing_mine) +
                                             sizeof(Control) + half * half_bytes);
   const int64_t total = units_per_tensor * n_tensors;
-  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total;
-       i += int64_t(gridDim.x) * blockDim.x) {
-    const int t = int(i / units_per_tensor);
-    static_cast<U*>(dst.p[t])[i - t * units_per_tensor] = src[i];
+  constexpr int kBatch = 4;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i0 = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * kBatch) {
+    U val[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < total) val[u] = src[i];
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < total) {
+        const int t = int(i / units_per_tensor);
+        static_cast<U*>(dst.p[t])[i - t * units_per_tensor] = val[u];
+      }
+    }
   }
 }
 

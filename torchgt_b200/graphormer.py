@@ -1,0 +1,127 @@
+"""Node-level Graphormer shell around the sparse attention path.
+
+Same constructor arguments, sub-module names and ``state_dict`` keys as the reference model
+(models/graphormer_dist_node_level.py:226-395), so its checkpoints load with ``strict=True``.  The dense
+layers are ordinary ``torch.nn`` modules (library GEMMs); the attention and its sequence-parallel
+exchange are this library's kernels.  It exists so that end-to-end step and epoch times can be measured
+without the reference's code; the dense-bias branch of the reference model (never taken on the sparse
+path: every caller passes ``attn_bias=None``) is not reproduced.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+from torch.nn import functional as F
+
+from .attn_module import CoreAttention
+from .gt_sp.initialize import get_sequence_parallel_group, sequence_parallel_is_initialized
+from .gt_sp.layer import DistributedAttentionNoMerge
+
+
+def _init_params(module: nn.Module, n_layers: int) -> None:
+    """models/graphormer_dist_node_level.py:18-25: N(0, 0.02/sqrt(L)) linears, N(0, 0.02) embeddings."""
+    if isinstance(module, nn.Linear):
+        module.weight.data.normal_(mean=0.0, std=0.02 / math.sqrt(n_layers))
+        if module.bias is not None:
+            module.bias.data.zero_()
+    elif isinstance(module, nn.Embedding):
+        module.weight.data.normal_(mean=0.0, std=0.02)
+
+
+class FeedForwardNetwork(nn.Module):
+    def __init__(self, hidden_size: int, ffn_size: int, dropout_rate: float):
+        super().__init__()
+        self.layer1 = nn.Linear(hidden_size, ffn_size)
+        self.gelu = nn.GELU()
+        self.layer2 = nn.Linear(ffn_size, hidden_size)
+
+    def forward(self, x):
+        return self.layer2(self.gelu(self.layer1(x)))
+
+
+class MultiHeadAttention(nn.Module):
+    """Q/K/V projections, the Ulysses layer around the sparse attention, output projection
+    (models/graphormer_dist_node_level.py:226-273)."""
+
+    def __init__(self, hidden_size: int, attention_dropout_rate: float, num_heads: int, attn_bias_dim: int):
+        super().__init__()
+        self.num_heads = num_heads
+        self.att_size = hidden_size // num_heads
+        self.linear_q = nn.Linear(hidden_size, num_heads * self.att_size)
+        self.linear_k = nn.Linear(hidden_size, num_heads * self.att_size)
+        self.linear_v = nn.Linear(hidden_size, num_heads * self.att_size)
+        core = CoreAttention(hidden_size, attention_dropout_rate, num_heads, attn_bias_dim)
+        group = get_sequence_parallel_group() if sequence_parallel_is_initialized() else None
+        self.dist_attn = DistributedAttentionNoMerge(core, group)
+        self.output_layer = nn.Linear(num_heads * self.att_size, hidden_size)
+
+    def forward(self, x, attn_bias=None, edge_index=None, attn_type=None):
+        b = x.size(0)
+        q = self.linear_q(x).view(b, -1, self.num_heads, self.att_size)
+        k = self.linear_k(x).view(b, -1, self.num_heads, self.att_size)
+        v = self.linear_v(x).view(b, -1, self.num_heads, self.att_size)
+        if sequence_parallel_is_initialized():
+            ctx = self.dist_attn(q, k, v, attn_bias, edge_index, attn_type)
+        else:  # single process without a sequence-parallel group: the layer would only pass through
+            ctx = self.dist_attn.local_attn(q, k, v, attn_bias, edge_index, attn_type)
+        return self.output_layer(ctx)
+
+
+class EncoderLayer(nn.Module):
+    """Pre-norm attention block + pre-norm feed-forward block (models/graphormer_dist_node_level.py:276-314)."""
+
+    def __init__(self, hidden_size, ffn_size, dropout_rate, attention_dropout_rate, num_heads, attn_bias_dim):
+        super().__init__()
+        self.self_attention_norm = nn.LayerNorm(hidden_size)
+        self.self_attention = MultiHeadAttention(hidden_size, attention_dropout_rate, num_heads, attn_bias_dim)
+        self.self_attention_dropout = nn.Dropout(dropout_rate)
+        self.ffn_norm = nn.LayerNorm(hidden_size)
+        self.ffn = FeedForwardNetwork(hidden_size, ffn_size, dropout_rate)
+        self.ffn_dropout = nn.Dropout(dropout_rate)
+
+    def forward(self, x, attn_bias=None, edge_index=None, attn_type=None):
+        y = self.self_attention(self.self_attention_norm(x), attn_bias, edge_index, attn_type=attn_type)
+        x = x + self.self_attention_dropout(y)
+        y = self.ffn(self.ffn_norm(x))
+        return x + self.ffn_dropout(y)
+
+
+class Graphormer(nn.Module):
+    """``Graphormer(n_layers, num_heads, input_dim, hidden_dim, output_dim, attn_bias_dim, dropout_rate,
+    input_dropout_rate, attention_dropout_rate, ffn_dim, num_global_node)`` — one node per token, the
+    global token at local row 0 (models/graphormer_dist_node_level.py:317-395)."""
+
+    def __init__(self, n_layers, num_heads, input_dim, hidden_dim, output_dim, attn_bias_dim, dropout_rate,
+                 input_dropout_rate, attention_dropout_rate, ffn_dim, num_global_node):
+        super().__init__()
+        self.num_heads = num_heads
+        self.node_encoder = nn.Linear(input_dim, hidden_dim)
+        self.input_dropout = nn.Dropout(input_dropout_rate)
+        self.layers = nn.ModuleList(
+            [EncoderLayer(hidden_dim, ffn_dim, dropout_rate, attention_dropout_rate, num_heads, attn_bias_dim)
+             for _ in range(n_layers)])
+        self.n_layers = n_layers
+        self.final_ln = nn.LayerNorm(hidden_dim)
+        self.downstream_out_proj = nn.Linear(hidden_dim, output_dim)
+        self.hidden_dim = hidden_dim
+        self.num_global_node = num_global_node
+        self.graph_token = nn.Embedding(num_global_node, hidden_dim)
+        self.graph_token_virtual_distance = nn.Embedding(num_global_node, attn_bias_dim)
+        self.apply(lambda m: _init_params(m, n_layers))
+
+    def forward(self, x, attn_bias, edge_index, perturb=None, attn_type=None):
+        """x: this rank's [s/p, input_dim] features; edge_index: the batch's [2, E] edges (or a
+        ``SparseGraph``) in the numbering of the gathered sequence; returns log-probabilities [s/p, C]."""
+        if attn_bias is not None:
+            raise NotImplementedError("the sparse path takes attn_bias=None (as every caller in the reference does)")
+        h = self.node_encoder(x.unsqueeze(0))
+        if perturb is not None:
+            h = h + perturb
+        token = self.graph_token.weight.unsqueeze(0).expand(h.size(0), -1, -1)
+        h = self.input_dropout(torch.cat([token, h], dim=1))
+        for layer in self.layers:
+            h = layer(h, attn_bias=None, edge_index=edge_index, attn_type=attn_type)
+        h = self.final_ln(h)
+        return F.log_softmax(self.downstream_out_proj(h[0, 1:, :]), dim=1)

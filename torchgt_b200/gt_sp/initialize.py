@@ -138,12 +138,10 @@ def get_global_token_num() -> int:
 
 def set_global_token_indices(global_token_indices) -> None:
     _state.global_token_indices = list(global_token_indices)
-    _state.device_rows.clear()
 
 
 def set_last_batch_global_token_indices(global_token_indices_last_batch) -> None:
     _state.global_token_indices_last_batch = list(global_token_indices_last_batch)
-    _state.device_rows.clear()
 
 
 def get_global_token_indices(last_batch: bool = False):
@@ -157,10 +155,13 @@ def get_global_token_indices(last_batch: bool = False):
 def get_global_token_rows_on(device, last_batch: bool = False) -> torch.Tensor:
     """The active index list as an int32 tensor on ``device``, uploaded once and cached (the reference
     rebuilds a LongTensor and uploads it on every layer call, gt_sp/utils.py:836)."""
-    key = (str(device), bool(last_batch))
+    indices = tuple(get_global_token_indices(last_batch))
+    key = (str(device), indices)
     rows = _state.device_rows.get(key)
     if rows is None:
-        rows = torch.tensor(get_global_token_indices(last_batch), dtype=torch.int32, device=device)
+        if len(_state.device_rows) > 64:
+            _state.device_rows.clear()
+        rows = torch.tensor(indices, dtype=torch.int32, device=device)
         _state.device_rows[key] = rows
     return rows
 
