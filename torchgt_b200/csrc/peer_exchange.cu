@@ -57,11 +57,16 @@ __global__ void push_kernel(Ptrs3 src, PeerTable landing, const Control* __restr
                             size_t half_bytes, int n_tensors, int64_t outer_s, int64_t ws,
                             int64_t wg, int world, int rank, const int32_t* __restrict__ alias_rows,
                             int n_alias, int64_t alias_period_units) {
-  constexpr int kBatch = 4;  // loads in flight per thread before the (posted) remote stores
+  constexpr int kBatch = 4;      // loads in flight per thread before the (posted) remote stores
+  constexpr int kBurst = 256;    // consecutive 16-byte units (4 KB) written to one peer by one CTA pass
   const unsigned half = ctl->epoch & 1u;
   const int64_t chunk = outer_s * ws;                       // units one peer gets per tensor
   const int64_t per_tensor_dst = chunk * world;             // units of one destination tensor
-  const int64_t total = chunk * world * n_tensors;
+  // Work is cut into bursts; consecutive bursts go to DIFFERENT peers, starting with the next rank,
+  // so at any moment the CTAs of every GPU are spread over all links and no destination is hit by
+  // all senders at once.
+  const int64_t bursts_per_chunk = (chunk + kBurst - 1) / kBurst;
+  const int64_t total = bursts_per_chunk * world * n_tensors * kBurst;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t i0 = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i0 < total;
        i0 += stride * kBatch) {
@@ -69,13 +74,15 @@ __global__ void push_kernel(Ptrs3 src, PeerTable landing, const Control* __restr
     U* dst[kBatch];
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
-      // i enumerates (peer, tensor, f) with f fastest: consecutive threads write consecutive units
       const int64_t i = i0 + u * stride;
       dst[u] = nullptr;
       if (i >= total) continue;
-      const int64_t f = i % chunk;
-      const int t = int((i / chunk) % n_tensors);
-      const int peer = int(i / (chunk * n_tensors));
+      const int64_t burst = i / kBurst;
+      const int pk = int(burst % world);
+      const int t = int((burst / world) % n_tensors);
+      const int64_t f = (burst / (int64_t(world) * n_tensors)) * kBurst + (i % kBurst);
+      if (f >= chunk) continue;
+      const int peer = (rank + 1 + pk) % world;
       const int64_t a = f / ws;
       const int64_t w = f % ws;
       int64_t pos = int64_t(peer) * ws + w;   // unit position inside outer row a of the source
@@ -209,8 +216,8 @@ extern "C" int tgt_p2p_push(const void* x0, const void* x1, const void* x2, int 
   Ptrs3 src;
   for (int t = 0; t < 3; ++t) src.p[t] = const_cast<void*>(xs[t]);
   const int64_t ws = width_s_bytes / 16, wg = width_g_bytes / 16;
-  const int64_t total = outer_s * ws * world * n_tensors;
-  push_kernel<uint4><<<grid_for(total), kThreads, 0, stream>>>(
+  const int64_t total = ((outer_s * ws + 255) / 256) * 256 * world * n_tensors;
+  push_kernel<uint4><<<grid_for((total + 3) / 4), kThreads, 0, stream>>>(
       src, tab, static_cast<const Control*>(tab.p[rank]), half_bytes, n_tensors, outer_s, ws, wg,
       world, rank, alias_rows, n_alias, n_alias > 0 ? alias_row_bytes / 16 : 1);
   TGT_CHECK_CUDA(cudaGetLastError());
