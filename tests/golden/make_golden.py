@@ -14,6 +14,8 @@ Outputs (all small .npz files, committed):
   attn_*.npz     CoreAttention.sparse_attention_bias forward + autograd gradients
   edges.npz      fix_edge_index / adjust_edge_index_nomerge / flatten_edge_index_nopad known answers
   ulysses_P*.npz _SeqAllToAll both directions and the DistributedAttentionNoMerge layer, P ranks
+  layer_variants_P*.npz  the four Ulysses layer variants no reference model instantiates (global tokens
+                 merged by mean), around a toy local attention: outputs and gradients, P ranks
   graphormer_node_level.npz  the reference's node-level Graphormer: parameters, log-probabilities, loss and
                  parameter gradients of one training step (3 layers, dropout 0, one rank)
 """
@@ -197,6 +199,83 @@ def _ulysses_worker(rank, world, ref_path, port, out_path):
     dist.destroy_process_group()
 
 
+class ToyAttention(torch.nn.Module):
+    """Stand-in local attention for the layer variants nothing in the reference instantiates: an
+    elementwise mix of q, k, v plus a per-row bias term, so that only the layers' own exchange /
+    merge / extend logic is under test.  tests/test_ulysses_gloo.py carries an identical copy."""
+
+    def forward(self, q, k, v, attn_bias=None, *args):
+        b, s = q.size(0), q.size(1)
+        out = (0.5 * q + 0.25 * k * k - v).reshape(b, s, -1)
+        if attn_bias is not None:
+            sq = attn_bias * attn_bias                    # (a dense gradient, not a broadcast one)
+            if attn_bias.size(1) == s:                    # [b, s, x, y]
+                out = out + sq.sum(dim=(2, 3)).unsqueeze(-1)
+            else:                                         # [b, heads, s, y]
+                out = out + sq.sum(dim=(1, 3)).unsqueeze(-1)
+        return out
+
+
+def _variants_worker(rank, world, ref_path, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ref_path)
+    install_shims()
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def all_to_all_via_single(output_list, input_list, group=None):
+        out = torch.empty_like(torch.stack(input_list))
+        dist.all_to_all_single(out, torch.stack(input_list).contiguous(), group=group)
+        for o, chunk in zip(output_list, out):
+            o.copy_(chunk)
+    dist.all_to_all = all_to_all_via_single
+    torch.distributed.all_to_all = all_to_all_via_single
+    import gt_sp.initialize as init
+    L, H, D = 5, 8, 4
+    S = L * world
+    init._GLOBAL_TOKEN_NUM = 1
+    init.initialize_sequence_parallel(S, 1, 1, world)
+    init.set_global_token_indices(list(range(0, world * (L + 1), L + 1)))
+    import gt_sp.layer as ref_layer
+    group = init.get_sequence_parallel_group()
+    gen = torch.Generator().manual_seed(900 + rank)
+    rec = {}
+    cases = {
+        "DistributedAttention": lambda: torch.randn(1, L + 1, S + 1, 2, generator=gen),
+        "DistributedAttentionGlobal0": lambda: torch.randn(1, L + 1, S + 1, 2, generator=gen),
+        "DistributedAttentionLocalBias": lambda: torch.randn(1, H, S + 1, S + 1, generator=torch.Generator().manual_seed(5)),
+        "DistributedAttentionAll2all": lambda: torch.randn(1, H, L + 1, S + 1, generator=gen),
+    }
+    for name, make_bias in cases.items():
+        q, k, v = (torch.randn(1, L + 1, H, D, generator=gen).requires_grad_() for _ in range(3))
+        bias = make_bias().requires_grad_()
+        dout = torch.randn(1, L + 1, H * D, generator=gen)
+        layer = getattr(ref_layer, name)(ToyAttention(), group).train()
+        if name == "DistributedAttention":
+            out = layer(q, k, v, bias)
+        else:
+            out = layer(q, k, v, bias, None)
+        (out * dout).sum().backward()
+        for key, val in (("q", q), ("k", k), ("v", v), ("bias", bias), ("dout", dout), ("out", out),
+                         ("dq", q.grad), ("dk", k.grad), ("dv", v.grad), ("dbias", bias.grad)):
+            rec[f"{name}/{key}"] = val.detach().numpy()
+    gathered = [None] * world
+    dist.all_gather_object(gathered, rec)
+    if rank == 0:
+        flat = {f"r{r}/{name}": val for r, g in enumerate(gathered) for name, val in g.items()}
+        flat["L"], flat["H"], flat["D"] = np.int64(L), np.int64(H), np.int64(D)
+        np.savez_compressed(out_path, **flat)
+        print("wrote", out_path)
+    dist.destroy_process_group()
+
+
+def make_variant_cases(ref_path):
+    import torch.multiprocessing as mp
+    for i, world in enumerate((2, 4)):
+        mp.spawn(_variants_worker, args=(world, ref_path, 29631 + i, str(OUT_DIR / f"layer_variants_P{world}.npz")),
+                 nprocs=world, join=True)
+
+
 def _model_worker(rank, world, ref_path, port, out_path):
     """Reference node-level Graphormer, one rank (the exchange degenerates to a copy), dropout 0."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
@@ -269,6 +348,7 @@ def main():
     make_edge_cases()
     make_ulysses_cases(args.reference)
     make_model_case(args.reference)
+    make_variant_cases(args.reference)
 
 
 if __name__ == "__main__":

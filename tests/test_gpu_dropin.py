@@ -76,3 +76,35 @@ def test_eval_mode_uses_all_heads_and_prebuilt_graph_is_accepted():
     out = core(q.cuda(), k.cuda(), v.cuda(), None, graph, "sparse")
     ref = sao.sparse_attention_ops(q[0], k[0], v[0], ei).reshape(1, n, h * d)
     assert rel_err(out, ref) < TOL_F32
+
+
+def test_graph_level_batch_of_16_call_graphs():
+    """The graph-level configuration: 16 sparse DAG-like graphs with 2,000-20,000 nodes (average degree
+    about 2.5), padded to the largest and flattened to one block-diagonal edge list with per-graph offsets
+    (data/collator_sp_sparse.py:126-133), run through the module as the GT models do ([b, N, H, D] in)."""
+    from torchgt_b200 import CoreAttention
+    from torchgt_b200.gt_sp.utils import flatten_edge_index_nopad
+    gen = torch.Generator().manual_seed(16)
+    sizes = torch.randint(2000, 20001, (16,), generator=gen).tolist()
+    n_max = max(sizes)
+    graphs = []
+    for n in sizes:
+        e = int(n * 2.5)
+        src = torch.randint(0, n, (e,), generator=gen)
+        dst = torch.minimum(src + 1 + torch.randint(0, 50, (e,), generator=gen), torch.tensor(n - 1))  # forward edges
+        graphs.append(torch.stack([src, dst]))
+    ei = flatten_edge_index_nopad(graphs, n_max)
+    b, h, d = 16, 8, 8
+    q, k, v = (torch.randn(b, n_max, h, d, generator=gen) for _ in range(3))
+    w = torch.randn(b * n_max, h, d, generator=gen)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+    ref = sao.sparse_attention_ops(qr.view(-1, h, d), kr.view(-1, h, d), vr.view(-1, h, d), ei)
+    (ref * w).sum().backward()
+    core = CoreAttention(h * d, 0.0, h)
+    qc, kc, vc = (t.clone().cuda().requires_grad_() for t in (q, k, v))
+    out = core(qc, kc, vc, None, ei.cuda(), "sparse")
+    assert out.shape == (b, n_max, h * d)
+    (out.view(b * n_max, h, d) * w.cuda()).sum().backward()
+    assert rel_err(out.reshape(-1), ref.reshape(-1)) < TOL_F32
+    for mine, theirs in ((qc, qr), (kc, kr), (vc, vr)):
+        assert rel_err(mine.grad, theirs.grad) < TOL_F32

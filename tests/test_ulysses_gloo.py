@@ -34,6 +34,25 @@ class OracleAttention(torch.nn.Module):
         return out.view(b, s, -1)
 
 
+class ToyAttention(torch.nn.Module):
+    """Identical copy of the stand-in local attention in tests/golden/make_golden.py."""
+
+    def forward(self, q, k, v, attn_bias=None, *args):
+        b, s = q.size(0), q.size(1)
+        out = (0.5 * q + 0.25 * k * k - v).reshape(b, s, -1)
+        if attn_bias is not None:
+            sq = attn_bias * attn_bias
+            if attn_bias.size(1) == s:
+                out = out + sq.sum(dim=(2, 3)).unsqueeze(-1)
+            else:
+                out = out + sq.sum(dim=(1, 3)).unsqueeze(-1)
+        return out
+
+
+VARIANTS = ["DistributedAttention", "DistributedAttentionGlobal0", "DistributedAttentionLocalBias",
+            "DistributedAttentionAll2all"]
+
+
 def _worker(rank, world, port, case, ret):
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests"))
@@ -43,7 +62,8 @@ def _worker(rank, world, port, case, ret):
     try:
         import torchgt_b200.gt_sp.initialize as init
         from torchgt_b200.gt_sp import gt_layer, layer
-        with np.load(GOLDEN / f"ulysses_P{world}.npz") as z:
+        golden_file = f"layer_variants_P{world}.npz" if case == "variants" else f"ulysses_P{world}.npz"
+        with np.load(GOLDEN / golden_file) as z:
             g = {k: z[k] for k in z.files}
         L, H, D = int(g["L"]), int(g["H"]), int(g["D"])
         init.set_global_token_num(1)
@@ -85,6 +105,17 @@ def _worker(rank, world, port, case, ret):
             lay.eval()
             ev = lay(q.detach(), k.detach(), v.detach(), None, torch.tensor([[0], [0]]), "sparse")
             assert ev.shape == (1, L + 1, H * D)
+        elif case == "variants":
+            for name in VARIANTS:
+                tv = lambda key: torch.from_numpy(g[f"r{rank}/{name}/{key}"])
+                q, k, v, bias = (tv(n).clone().requires_grad_() for n in ("q", "k", "v", "bias"))
+                lay = getattr(layer, name)(ToyAttention(), group).train()
+                out = lay(q, k, v, bias) if name == "DistributedAttention" else lay(q, k, v, bias, None)
+                (out * tv("dout")).sum().backward()
+                for key, mine in (("out", out.detach()), ("dq", q.grad), ("dk", k.grad), ("dv", v.grad),
+                                  ("dbias", bias.grad)):
+                    ref = tv(key)
+                    errs[f"{name}/{key}"] = float((mine - ref).abs().max() / max(float(ref.abs().max()), 1e-30))
         elif case == "gt":
             # GT layers: no global token.  Every rank checks against a single-process evaluation of the
             # whole sequence with all heads.
@@ -136,3 +167,12 @@ def test_nomerge_layer_matches_reference_outputs_and_gradients(world):
 def test_gt_layers_match_single_process_attention(world):
     for rank, errs in _run(world, "gt").items():
         assert max(errs.values()) < 1e-5, (rank, errs)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_layer_variants_with_merged_global_tokens_match_the_reference(world):
+    """DistributedAttention, ...Global0, ...LocalBias, ...All2all of the reference (no model uses them):
+    same outputs and gradients around the same toy local attention, bias paths included."""
+    for rank, errs in _run(world, "variants").items():
+        assert len(errs) == 20
+        assert max(errs.values()) < 1e-6, (rank, errs)
