@@ -155,8 +155,8 @@ TGT_API int tgt_sparse_attn_fwd_noalloc(const void* q, const void* k, const void
  * elementwise chain).  With G = dout, inv = 1/(Z+1e-6):
  *   dw = (G_d . V_s - G_d . O_d) * inv_d;  dV_s += w * inv_d * G_d;  dt = dw * w  (= dbias)
  *   da = dt * [-5 <= raw <= 5];  dQ_d += da * K_s / sqrt(D);  dK_s += da * Q_d / sqrt(D)
- * A streaming pre-pass computes the per-row statistics, pass A walks by_dst (dQ, dbias), pass B
- * walks by_src (dK, dV); scores are recomputed, nothing per-edge is read from forward.  dbias is device fp32 in ORIGINAL edge order
+ * Pass A walks by_dst (dQ, dbias, per-row statistics), pass B walks by_src (dK, dV); scores are
+ * recomputed, nothing per-edge is read from forward.  dbias is device fp32 in ORIGINAL edge order
  * with the shape bias has, or NULL when not wanted.  Deterministic (no atomics).
  */
 TGT_API int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
@@ -166,11 +166,12 @@ TGT_API int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* k, 
                         size_t scratch_bytes, void* stream);
 
 /*
- * The same backward with its stages selectable by bit mask: 1 = row statistics
- * (1/(Z+1e-6) and dO.O per row and head, into `scratch`), 2 = pass A (dQ, dbias), 4 = pass B
- * (dK, dV).  Passes A and B need the statistics a stage-1 call left in the same scratch for the same
- * inputs.  7 = tgt_sparse_attn_bwd.  Lets a caller time or overlap the stages separately; replaces
- * the same reference code as tgt_sparse_attn_bwd.
+ * The same backward with its stages selectable by bit mask: 2 = pass A (dQ and, into `scratch`, the
+ * per-row statistics 1/(Z+1e-6) and dO.O that pass B reads), 4 = pass B (dK, dV; needs the statistics
+ * a pass A left in the same scratch for the same inputs), 1 = streaming pre-pass that computes the
+ * statistics from dO and O — required (in the same or an earlier call) only when dbias is wanted,
+ * because dbias needs them per edge before a row is complete.  tgt_sparse_attn_bwd runs 6, or 7 with
+ * dbias.  Lets a caller time or overlap the stages; replaces the same reference code.
  */
 TGT_API int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const void* k, const void* v,
                                        const float* bias, int bias_heads, const void* out,

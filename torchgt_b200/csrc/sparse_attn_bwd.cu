@@ -1,8 +1,13 @@
-// Backward of the sparse graph attention: a row-statistics pre-pass and two atomics-free passes that
-// recompute the scores.
-//   stats : stats[d,h] = { 1/(Z+1e-6), dO_d . O_d }                       (streams dO and O once)
-//   pass A: edges sorted by destination -> dQ and dbias
+// Backward of the sparse graph attention: two atomics-free passes that recompute the scores.
+//   pass A: edges sorted by destination -> dQ, and the row statistics
+//           stats[d,h] = { inv_d = 1/(Z+1e-6), delta_d = dO_d . O_d } that pass B reads
 //   pass B: edges sorted by source      -> dK and dV
+// Pass A needs delta_d before the row is complete.  Because O_d = inv_d * sum_e w_e V_s,
+// delta_d = inv_d * sum_e w_e (dO_d . V_s) is a sum over the same edges, so the pass accumulates
+//   A1 = sum mask w (dO.V) K,  A2 = sum mask w K,  S = sum w (dO.V)
+// and finishes the row with delta = inv S, dQ = inv (A1 - delta A2) / sqrt(D): no separate statistics
+// pass and no read of O.  Only when dbias is wanted (it needs delta per edge) a streaming pre-pass
+// computes the statistics from dO and O first and pass A uses them per edge.
 // With G = dO, inv = 1/(Z+1e-6), w = exp(clamp(raw)+bias):
 //   dw = (G_d.V_s - G_d.O_d) * inv_d      dV_s += w * inv_d * G_d      dt = dw * w  (= dbias)
 //   da = dt * [-5 <= raw <= 5]            dQ_d += da * K_s / sqrt(D)   dK_s += da * Q_d / sqrt(D)
@@ -137,6 +142,91 @@ struct DqPolicy {
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = acc[j] * inv_scale;
     Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
+  }
+  __device__ __forceinline__ void zero_row(int row) const {
+    float o[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o[j] = 0.f;
+    Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
+  }
+};
+
+// ---- pass A without a statistics pre-pass (no dbias) ---------------------------------------------
+template <typename T, int LPH, int G>
+struct DqFusedPolicy {
+  static constexpr int VEC = Vec16<T>::kElems;
+  static constexpr int NACC = 2 * VEC + 1;  // A1, A2, S
+
+  const T* __restrict__ q;
+  const T* __restrict__ k;
+  const T* __restrict__ v;
+  const T* __restrict__ dout;
+  const float* __restrict__ z;
+  const float* __restrict__ bias;
+  float2* __restrict__ stats;
+  T* __restrict__ dq;
+  int bias_stride, bias_off;
+  unsigned row_vecs, cvec;
+  int heads, head;
+  bool head_leader;
+  float inv_scale;
+
+  using Raw = typename Vec16<T>::Raw;
+  struct Operands {
+    Raw k, v, q, g;
+    float b;
+  };
+  struct Scalars {
+    float wm, wgv_m, wgv;  // mask*w, mask*w*(dO.V), w*(dO.V)
+  };
+
+  __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
+    const unsigned so = unsigned(src) * row_vecs + cvec;
+    const unsigned ro = unsigned(row) * row_vecs + cvec;
+    o.k = Vec16<T>::raw_at(k, so);
+    o.v = Vec16<T>::raw_at(v, so);
+    o.q = Vec16<T>::raw_at(q, ro);
+    o.g = Vec16<T>::raw_at(dout, ro);
+    o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
+  }
+  __device__ __forceinline__ void clear(Operands& o) const {
+    o.k = o.v = o.q = o.g = Vec16<T>::raw_zero();
+    o.b = 0.f;
+  }
+  __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
+    float a[VEC], b[VEC];
+    Vec16<T>::unpack(o.q, a);
+    Vec16<T>::unpack(o.k, b);
+    const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
+    Vec16<T>::unpack(o.g, a);
+    Vec16<T>::unpack(o.v, b);
+    const float gv = group_sum<LPH>(dot<VEC>(a, b));
+    const float wgt = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
+    Scalars s;
+    s.wgv = wgt * gv;
+    s.wm = clamp_passes_grad(raw) ? wgt : 0.f;
+    s.wgv_m = s.wm * gv;
+    return s;
+  }
+  __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
+                                             const Scalars& s) const {
+    float kf[VEC];
+    Vec16<T>::unpack(o.k, kf);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      acc[j] = fmaf(s.wgv_m, kf[j], acc[j]);
+      acc[VEC + j] = fmaf(s.wm, kf[j], acc[VEC + j]);
+    }
+    acc[2 * VEC] += s.wgv;
+  }
+  __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {
+    const float inv = 1.0f / (__ldg(z + int64_t(row) * heads + head) + kZEps);
+    const float delta = inv * acc[2 * VEC];
+    float o[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o[j] = (acc[j] - delta * acc[VEC + j]) * (inv * inv_scale);
+    Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
+    if (head_leader) stats[int64_t(row) * heads + head] = make_float2(inv, delta);
   }
   __device__ __forceinline__ void zero_row(int row) const {
     float o[VEC];
@@ -287,6 +377,46 @@ __device__ __forceinline__ DkvPolicy<T, LPH, G> make_dkv_policy(const BwdParams&
 }
 
 template <typename T, int LPH, int G>
+__device__ __forceinline__ DqFusedPolicy<T, LPH, G> make_dq_fused_policy(const BwdParams& p) {
+  constexpr int VEC = Vec16<T>::kElems;
+  const int c = threadIdx.x % G;
+  DqFusedPolicy<T, LPH, G> pol;
+  pol.q = static_cast<const T*>(p.q);
+  pol.k = static_cast<const T*>(p.k);
+  pol.v = static_cast<const T*>(p.v);
+  pol.dout = static_cast<const T*>(p.dout);
+  pol.z = p.z;
+  pol.bias = p.bias;
+  pol.stats = p.stats;
+  pol.dq = static_cast<T*>(p.dq);
+  pol.head = blockIdx.y * (G / LPH) + c / LPH;
+  pol.bias_stride = p.bias_heads;
+  pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
+  pol.row_vecs = unsigned(p.row_elems / VEC);
+  pol.heads = p.heads;
+  pol.cvec = blockIdx.y * G + c;
+  pol.head_leader = c % LPH == 0;
+  pol.inv_scale = p.inv_scale;
+  return pol;
+}
+
+template <typename T, int LPH, int G>
+__global__ void TGT_WALK_BOUNDS bwd_dq_fused_kernel(const BwdParams p) {
+  using Policy = DqFusedPolicy<T, LPH, G>;
+  __shared__ TileSmem<G, Policy::NACC> sm;
+  const Policy pol = make_dq_fused_policy<T, LPH, G>(p);
+  walk_tile<G, Policy>(p.walk, pol, sm.other, sm.seg, sm.perm, sm.carry, sm.carry_row);
+}
+
+template <typename T, int LPH, int G>
+__global__ void __launch_bounds__(kBlockThreads) bwd_dq_fused_stitch_kernel(const BwdParams p) {
+  using Policy = DqFusedPolicy<T, LPH, G>;
+  const Policy pol = make_dq_fused_policy<T, LPH, G>(p);
+  __shared__ float s_part[kBlockThreads * Policy::NACC];
+  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+}
+
+template <typename T, int LPH, int G>
 __global__ void TGT_WALK_BOUNDS bwd_dq_kernel(const BwdParams p) {
   using Policy = DqPolicy<T, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
@@ -318,33 +448,40 @@ __global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const Bwd
   stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
-int bwd_resident_ctas(int dtype, const HeadSplit& hs, bool dkv) {
-  static int cache[2][2][6][6] = {};
+enum { kWalkDq = 0, kWalkDkv = 1, kWalkDqFused = 2 };
+
+int bwd_resident_ctas(int dtype, const HeadSplit& hs, int which) {
+  static int cache[3][2][6][6] = {};
   auto log2i = [](int x) { int l = 0; while ((1 << l) < x) ++l; return l; };
-  int* slot = &cache[dkv ? 1 : 0][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
+  int* slot = &cache[which][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
   int result = 4;
 #define TGT_OCC_DQ(T, LPH, G) result = resident_ctas(bwd_dq_kernel<T, LPH, G>, slot)
 #define TGT_OCC_DKV(T, LPH, G) result = resident_ctas(bwd_dkv_kernel<T, LPH, G>, slot)
-  if (dkv) TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DKV);
+#define TGT_OCC_DQF(T, LPH, G) result = resident_ctas(bwd_dq_fused_kernel<T, LPH, G>, slot)
+  if (which == kWalkDkv) TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DKV);
+  else if (which == kWalkDqFused) TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DQF);
   else TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DQ);
 #undef TGT_OCC_DQ
 #undef TGT_OCC_DKV
+#undef TGT_OCC_DQF
   return result;
 }
 
 struct BwdScratch {
   size_t stats, carry_a, carry_b, total;
-  TilePlan plan_a, plan_b;
+  TilePlan plan_a, plan_a_fused, plan_b;
 };
 
 BwdScratch plan_bwd_scratch(const tgt_layout* by_dst, const HeadSplit& hs, int heads, int dtype) {
   BwdScratch s;
   const int vec = dtype == TGT_F32 ? 4 : 8;
-  s.plan_a = plan_tiles(by_dst->n_edges, hs, vec, bwd_resident_ctas(dtype, hs, false));
-  s.plan_b = plan_tiles(by_dst->n_edges, hs, 2 * vec, bwd_resident_ctas(dtype, hs, true));
+  s.plan_a = plan_tiles(by_dst->n_edges, hs, vec, bwd_resident_ctas(dtype, hs, kWalkDq));
+  s.plan_a_fused = plan_tiles(by_dst->n_edges, hs, 2 * vec + 1, bwd_resident_ctas(dtype, hs, kWalkDqFused));
+  s.plan_b = plan_tiles(by_dst->n_edges, hs, 2 * vec, bwd_resident_ctas(dtype, hs, kWalkDkv));
   size_t off = 0;
   s.stats = off; off += round_up(size_t(by_dst->n_rows) * heads * 8, 256);
-  s.carry_a = off; off += s.plan_a.carry_bytes;
+  s.carry_a = off;
+  off += s.plan_a.carry_bytes > s.plan_a_fused.carry_bytes ? s.plan_a.carry_bytes : s.plan_a_fused.carry_bytes;
   s.carry_b = off; off += s.plan_b.carry_bytes;
   s.total = off;
   return s;
@@ -393,9 +530,10 @@ extern "C" int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* 
                                    const tgt_layout* by_src, void* dq, void* dk, void* dv,
                                    float* dbias, int heads, int head_dim, int dtype, void* scratch,
                                    size_t scratch_bytes, void* stream) {
+  // the statistics pre-pass is only needed when dbias is wanted
   return tgt_sparse_attn_bwd_passes(dout, q, k, v, bias, bias_heads, out, z, by_dst, by_src, dq, dk,
                                     dv, dbias, heads, head_dim, dtype, scratch, scratch_bytes, stream,
-                                    7);
+                                    dbias != nullptr ? 7 : 6);
 }
 
 extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const void* k,
@@ -408,7 +546,7 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
   using namespace tgt;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(passes >= 1 && passes <= 7,
-                "passes is a bit mask: 1 = row statistics, 2 = dQ/dbias, 4 = dK/dV");
+                "passes is a bit mask: 1 = row-statistics pre-pass, 2 = dQ/dbias, 4 = dK/dV");
   TGT_CHECK_ARG(dtype == TGT_F32 || dtype == TGT_BF16, "dtype must be TGT_F32 or TGT_BF16");
   int rc = check_layout(by_dst, "by_dst");
   if (rc != TGT_OK) return rc;
@@ -473,9 +611,22 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
     TGT_DISPATCH(dtype, hs.lph, hs.lph, TGT_LAUNCH_STATS);
 #undef TGT_LAUNCH_STATS
   }
-  if (passes & 2) {
-    fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a),
-              bias != nullptr || dbias != nullptr);
+  if ((passes & 2) && dbias == nullptr) {
+    // pass A that derives the row statistics itself (and leaves them in scratch for pass B)
+    fill_walk(&p.walk, *by_dst, sc.plan_a_fused, reinterpret_cast<float*>(base + sc.carry_a),
+              bias != nullptr);
+    const dim3 grid(sc.plan_a_fused.n_tiles, hs.groups);
+#define TGT_LAUNCH_DQF(T, LPH, G)                                                   \
+  do {                                                                              \
+    bwd_dq_fused_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
+    if (sc.plan_a_fused.n_tiles > 1)                                                \
+      bwd_dq_fused_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
+  } while (0)
+    TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQF);
+#undef TGT_LAUNCH_DQF
+  } else if (passes & 2) {
+    // pass A with per-edge dbias: uses the statistics of the pre-pass (stage 1)
+    fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a), true);
     const dim3 grid(sc.plan_a.n_tiles, hs.groups);
     const dim3 sgrid(sc.plan_a.n_tiles, hs.groups);
 #define TGT_LAUNCH_DQ(T, LPH, G)                                               \
