@@ -248,23 +248,27 @@ TGT_API int tgt_global_rows_reduce(void* dx, const int32_t* global_rows, int n_g
  * scatter_idx); on every destination it lands as [outer_g][world][width_g_bytes] (what cat along
  * gather_idx produces) with this rank's piece in column block `rank`.  If n_alias > 0, source rows
  * (of alias_row_bytes each, counted inside one outer row) listed in the device array alias_rows are
- * read from row 0 instead.
+ * read from row 0 instead.  staged = 0 stores every piece at its final position on the destination;
+ * staged = 1 stores this rank's whole chunk as one contiguous block and leaves the concatenation to
+ * tgt_p2p_fetch (use it when width_g_bytes is small: NVLink stores of less than 128 bytes are slow).
  * tgt_p2p_barrier: all ranks' pushes are complete and visible when the kernel ends.  Waits are
  * bounded: after spin_limit polls it gives up, writes 1 + (rank it waited for) to *status (a
  * host-readable, device-writable int32, e.g. pinned memory) and returns; the context stays usable.
  * tgt_p2p_fetch: copies the n_tensors landed tensors (bytes_per_tensor each) out of the landing
- * half the last barrier completed, into ordinary device tensors.
+ * half the last barrier completed, into ordinary device tensors; `staged`, `world` and
+ * `width_g_bytes` must repeat what the push was given.
  */
 TGT_API size_t tgt_p2p_control_bytes(void);
 TGT_API int tgt_p2p_push(const void* x0, const void* x1, const void* x2, int n_tensors,
                          void* const* peer_landing, size_t half_bytes, int64_t outer_s,
                          int64_t width_s_bytes, int64_t width_g_bytes, int world, int rank,
                          const int32_t* alias_rows, int n_alias, int64_t alias_row_bytes,
-                         void* stream);
+                         int staged, void* stream);
 TGT_API int tgt_p2p_barrier(void* const* peer_landing, int world, int rank, uint32_t spin_limit,
                             int32_t* status, void* stream);
 TGT_API int tgt_p2p_fetch(const void* landing_mine, size_t half_bytes, int n_tensors, void* y0,
-                          void* y1, void* y2, int64_t bytes_per_tensor, void* stream);
+                          void* y1, void* y2, int64_t bytes_per_tensor, int staged, int world,
+                          int64_t width_g_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -144,9 +144,11 @@ def _peer_table(areas):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("staged", [0, 1])
 @pytest.mark.parametrize("shape,s,g,n_t,alias", [((1, 9, 8, 8), 2, 1, 3, False), ((2, 6, 8, 8), 2, 1, 2, False),
-                                                 ((1, 32, 64), 1, 2, 1, False), ((2, 16, 32), 1, 2, 1, True)])
-def test_peer_push_and_fetch_match_all_to_all_semantics(world, shape, s, g, n_t, alias):
+                                                 ((1, 32, 64), 1, 2, 1, False), ((2, 16, 32), 1, 2, 1, True),
+                                                 ((1, 64, 8), 1, 2, 3, False)])
+def test_peer_push_and_fetch_match_all_to_all_semantics(world, staged, shape, s, g, n_t, alias):
     """The peer-memory transport on one GPU: every rank's landing area is an ordinary local buffer, the
     ranks push one after the other, and the per-area epoch is advanced by a one-rank barrier (a real
     multi-rank barrier needs one GPU per rank and is covered by the multi-GPU test)."""
@@ -175,14 +177,15 @@ def test_peer_push_and_fetch_match_all_to_all_semantics(world, shape, s, g, n_t,
             ptrs = [t.data_ptr() for t in xs[r]] + [None] * (3 - n_t)
             _cabi.check(lib.tgt_p2p_push(ptrs[0], ptrs[1], ptrs[2], n_t, table, half, outer_s, ws_bytes, wg_bytes,
                                          world, r, rows.data_ptr() if alias else None, 3 if alias else 0,
-                                         shape[-1] * 4 if alias else 0, stream))
+                                         shape[-1] * 4 if alias else 0, staged, stream))
         outs = []
         for r in range(world):
             one = _peer_table([areas[r]])
             _cabi.check(lib.tgt_p2p_barrier(one, 1, 0, 10, status.data_ptr(), stream))
             ys = [torch.empty(out_shape, device="cuda") for _ in range(n_t)]
             optrs = [t.data_ptr() for t in ys] + [None] * (3 - n_t)
-            _cabi.check(lib.tgt_p2p_fetch(areas[r].data_ptr(), half, n_t, optrs[0], optrs[1], optrs[2], nbytes, stream))
+            _cabi.check(lib.tgt_p2p_fetch(areas[r].data_ptr(), half, n_t, optrs[0], optrs[1], optrs[2], nbytes, staged,
+                                          world, wg_bytes, stream))
             outs.append(ys)
         torch.cuda.synchronize()
         assert int(status[0]) == 0
@@ -213,4 +216,4 @@ def test_peer_barrier_gives_up_after_its_poll_limit_and_reports_the_rank():
     assert lib.tgt_p2p_barrier(_peer_table(areas), 3, 5, 10, status.data_ptr(), stream) == 1
     assert lib.tgt_p2p_barrier(_peer_table(areas), 3, 1, 10, None, stream) == 1
     assert lib.tgt_p2p_push(areas[0].data_ptr(), None, None, 1, _peer_table(areas), 32, 1, 16, 16, 3, 0, None, 0, 0,
-                            stream) == 1   # 48 bytes do not fit a 32-byte landing half
+                            0, stream) == 1   # 48 bytes do not fit a 32-byte landing half

@@ -80,9 +80,10 @@ SIGNATURES = {
                                        c_void_p]),
     "tgt_p2p_control_bytes": (c_size_t, []),
     "tgt_p2p_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), c_size_t, c_int64, c_int64,
-                             c_int64, c_int, c_int, c_void_p, c_int, c_int64, c_void_p]),
+                             c_int64, c_int, c_int, c_void_p, c_int, c_int64, c_int, c_void_p]),
     "tgt_p2p_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_uint32, c_void_p, c_void_p]),
-    "tgt_p2p_fetch": (c_int, [c_void_p, c_size_t, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "tgt_p2p_fetch": (c_int, [c_void_p, c_size_t, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64,
+                              c_void_p]),
 }
 
 _lib = None

@@ -56,7 +56,7 @@ template <typename U>
 __global__ void push_kernel(Ptrs3 src, PeerTable landing, const Control* __restrict__ ctl,
                             size_t half_bytes, int n_tensors, int64_t outer_s, int64_t ws,
                             int64_t wg, int world, int rank, const int32_t* __restrict__ alias_rows,
-                            int n_alias, int64_t alias_period_units) {
+                            int n_alias, int64_t alias_period_units, bool staged) {
   constexpr int kBatch = 4;      // loads in flight per thread before the (posted) remote stores
   constexpr int kBurst = 256;    // consecutive 16-byte units (4 KB) written to one peer by one CTA pass
   const unsigned half = ctl->epoch & 1u;
@@ -97,9 +97,11 @@ __global__ void push_kernel(Ptrs3 src, PeerTable landing, const Control* __restr
           }
       }
       val[u] = static_cast<const U*>(src.p[t])[a * world * ws + pos];
+      // final position on the destination, or (staged) this rank's contiguous block of the landing half
       const int64_t og = f / wg, o = f % wg;
+      const int64_t where = staged ? int64_t(rank) * chunk + f : (og * world + rank) * wg + o;
       dst[u] = reinterpret_cast<U*>(static_cast<char*>(landing.p[peer]) + sizeof(Control) +
-                                    half * half_bytes) + t * per_tensor_dst + (og * world + rank) * wg + o;
+                                    half * half_bytes) + t * per_tensor_dst + where;
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u)
@@ -134,15 +136,18 @@ __global__ void barrier_kernel(PeerTable landing, int world, int rank, unsigned 
   if (threadIdx.x == 0) mine->epoch = epoch;
 }
 
-// Copy the landing half that the LAST barrier completed into ordinary tensors.
+// Copy the landing half that the LAST barrier completed into ordinary tensors.  In staged mode the
+// half holds one contiguous block per source rank and the concatenation happens here: output unit
+// j = (og * world + r) * wg + o comes from block r, unit og * wg + o.
 template <typename U>
 __global__ void fetch_kernel(Ptrs3 dst, const void* landing_mine, size_t half_bytes, int n_tensors,
-                             int64_t units_per_tensor) {
+                             int64_t units_per_tensor, bool staged, int world, int64_t wg) {
   const Control* ctl = static_cast<const Control*>(landing_mine);
   const unsigned half = (ctl->epoch - 1u) & 1u;
   const U* src = reinterpret_cast<const U*>(static_cast<const char*>(landing_mine) +
                                             sizeof(Control) + half * half_bytes);
   const int64_t total = units_per_tensor * n_tensors;
+  const int64_t chunk = units_per_tensor / world;
   constexpr int kBatch = 4;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t i0 = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * kBatch) {
@@ -150,7 +155,15 @@ __global__ void fetch_kernel(Ptrs3 dst, const void* landing_mine, size_t half_by
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
       const int64_t i = i0 + u * stride;
-      if (i < total) val[u] = src[i];
+      if (i < total) {
+        int64_t from = i;
+        if (staged) {
+          const int64_t t = i / units_per_tensor, j = i - t * units_per_tensor;
+          const int64_t o = j % wg, r = (j / wg) % world, og = j / (wg * world);
+          from = t * units_per_tensor + r * chunk + og * wg + o;
+        }
+        val[u] = src[from];
+      }
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
@@ -191,10 +204,11 @@ extern "C" int tgt_p2p_push(const void* x0, const void* x1, const void* x2, int 
                             void* const* peer_landing, size_t half_bytes, int64_t outer_s,
                             int64_t width_s_bytes, int64_t width_g_bytes, int world, int rank,
                             const int32_t* alias_rows, int n_alias, int64_t alias_row_bytes,
-                            void* stream_) {
+                            int staged, void* stream_) {
   using namespace tgt;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(n_tensors >= 1 && n_tensors <= 3, "n_tensors must be 1, 2 or 3");
+  TGT_CHECK_ARG(staged == 0 || staged == 1, "staged must be 0 or 1");
   const void* xs[3] = {x0, x1, x2};
   for (int t = 0; t < 3; ++t)
     TGT_CHECK_ARG((t < n_tensors) == (xs[t] != nullptr), "tensor pointers do not match n_tensors");
@@ -219,7 +233,7 @@ extern "C" int tgt_p2p_push(const void* x0, const void* x1, const void* x2, int 
   const int64_t total = ((outer_s * ws + 255) / 256) * 256 * world * n_tensors;
   push_kernel<uint4><<<grid_for((total + 3) / 4), kThreads, 0, stream>>>(
       src, tab, static_cast<const Control*>(tab.p[rank]), half_bytes, n_tensors, outer_s, ws, wg,
-      world, rank, alias_rows, n_alias, n_alias > 0 ? alias_row_bytes / 16 : 1);
+      world, rank, alias_rows, n_alias, n_alias > 0 ? alias_row_bytes / 16 : 1, staged != 0);
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }
@@ -240,10 +254,15 @@ extern "C" int tgt_p2p_barrier(void* const* peer_landing, int world, int rank, u
 }
 
 extern "C" int tgt_p2p_fetch(const void* landing_mine, size_t half_bytes, int n_tensors, void* y0,
-                             void* y1, void* y2, int64_t bytes_per_tensor, void* stream_) {
+                             void* y1, void* y2, int64_t bytes_per_tensor, int staged, int world,
+                             int64_t width_g_bytes, void* stream_) {
   using namespace tgt;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(n_tensors >= 1 && n_tensors <= 3, "n_tensors must be 1, 2 or 3");
+  TGT_CHECK_ARG(staged == 0 || staged == 1, "staged must be 0 or 1");
+  TGT_CHECK_ARG(staged == 0 || (world >= 1 && width_g_bytes >= 16 && width_g_bytes % 16 == 0 &&
+                                bytes_per_tensor % (int64_t(world) * width_g_bytes) == 0),
+                "staged fetch needs world and a destination row width that divide the tensor");
   void* ys[3] = {y0, y1, y2};
   for (int t = 0; t < 3; ++t)
     TGT_CHECK_ARG((t < n_tensors) == (ys[t] != nullptr), "tensor pointers do not match n_tensors");
@@ -254,8 +273,9 @@ extern "C" int tgt_p2p_fetch(const void* landing_mine, size_t half_bytes, int n_
   Ptrs3 dst;
   for (int t = 0; t < 3; ++t) dst.p[t] = ys[t];
   const int64_t units = bytes_per_tensor / 16;
-  fetch_kernel<uint4><<<grid_for(units * n_tensors), kThreads, 0, stream>>>(dst, landing_mine, half_bytes,
-                                                                            n_tensors, units);
+  fetch_kernel<uint4><<<grid_for((units * n_tensors + 3) / 4), kThreads, 0, stream>>>(
+      dst, landing_mine, half_bytes, n_tensors, units, staged != 0, staged ? world : 1,
+      staged ? width_g_bytes / 16 : 1);
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }

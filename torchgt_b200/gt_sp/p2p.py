@@ -78,15 +78,19 @@ class PeerExchange:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         ptrs = [t.data_ptr() for t in xs] + [None] * (3 - n_t)
         n_alias = 0 if alias_rows is None else int(alias_rows.numel())
+        # small destination runs (narrow head slices) would become slow sub-128-byte NVLink stores: send
+        # each rank's chunk as one block instead and concatenate while fetching
+        staged = 1 if width_g_bytes < 128 else 0
         _cabi.check(lib.tgt_p2p_push(ptrs[0], ptrs[1], ptrs[2], n_t, self.peers, self.half_bytes, outer_s,
                                      width_s_bytes, width_g_bytes, self.world, self.rank,
-                                     alias_rows.data_ptr() if n_alias else None, n_alias, alias_row_bytes, stream))
+                                     alias_rows.data_ptr() if n_alias else None, n_alias, alias_row_bytes, staged,
+                                     stream))
         _cabi.check(lib.tgt_p2p_barrier(self.peers, self.world, self.rank, self.spin_limit,
                                         self.status.data_ptr(), stream))
         outs = [torch.empty(out_shape, dtype=xs[0].dtype, device=self.device) for _ in range(n_t)]
         optrs = [t.data_ptr() for t in outs] + [None] * (3 - n_t)
         _cabi.check(lib.tgt_p2p_fetch(self.buffer.data_ptr(), self.half_bytes, n_t, optrs[0], optrs[1], optrs[2],
-                                      nbytes, stream))
+                                      nbytes, staged, self.world, width_g_bytes, stream))
         return outs
 
 
