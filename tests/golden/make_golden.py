@@ -339,7 +339,7 @@ def make_ulysses_cases(ref_path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of zxmeng98/torchgt")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     install_shims()
