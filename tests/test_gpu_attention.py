@@ -107,10 +107,12 @@ def test_shapes_bf16(heads, head_dim, with_bias):
 def test_edge_cases_empty_graph_single_row_and_self_loop_only():
     gen = torch.Generator().manual_seed(0)
     q, k, v, dout = (torch.randn(6, 8, 8, generator=gen) for _ in range(4))
-    # no edges at all: output and all gradients are exactly zero
+    # no edges at all: output and all gradients are exactly zero (with or without an empty bias)
     res = _run_cuda(q, k, v, torch.zeros((2, 0), dtype=torch.long), dout)
     for t in res.values():
         assert torch.count_nonzero(t) == 0
+    res = _run_cuda(q, k, v, torch.zeros((2, 0), dtype=torch.long), dout, bias=torch.zeros(0), bias_grad=False)
+    assert torch.count_nonzero(res["out"]) == 0
     # one row, one self loop: out = v * w/(w + 1e-6)
     loop = torch.zeros((2, 1), dtype=torch.long)
     res = _run_cuda(q[:1], k[:1], v[:1], loop, dout[:1])
@@ -313,3 +315,45 @@ def test_long_sequence_batch_870k_nodes_sampled_rows_against_the_oracle():
     # rows in `srcs` have ALL their out-edges inside sub2 (every destination of theirs is in `dests`)
     assert rel_err(kc.grad.cpu()[srcs], dk[srcs.numpy()]) < TOL_F32
     assert rel_err(vc.grad.cpu()[srcs], dv[srcs.numpy()]) < TOL_F32
+
+
+def test_many_small_random_graphs_with_forced_tile_sizes():
+    """Randomised sweep over the segmented walk's corner cases: tiny tiles so that rows cross lane-group
+    and tile boundaries everywhere, rows without edges at the start, in the middle and at the end, hubs,
+    duplicates, every head split; forward and all gradients against the fp64 oracle."""
+    rng = np.random.default_rng(2024)
+    for trial in range(60):
+        n = int(rng.integers(1, 70))
+        e = int(rng.integers(0, 500))
+        heads = int(rng.choice([1, 2, 3, 4, 8]))
+        head_dim = int(rng.choice([4, 8, 16]))
+        tile_edges = int(rng.choice([0, 4, 8, 12, 16, 20]))
+        lo, hi = sorted(rng.integers(0, n, size=2).tolist())
+        hi = max(hi, lo + 1) if n > 1 else 1
+        dst = rng.integers(lo, hi, size=e)                       # leading / trailing rows without in-edges
+        src = rng.integers(0, n, size=e)
+        if e > 10 and rng.random() < 0.5:
+            dst[: e // 2] = dst[0]                               # a hub row
+        if e > 10 and rng.random() < 0.5:
+            src[e // 3: 2 * e // 3] = src[-1]                    # a hub column
+        ei = torch.from_numpy(np.stack([src, dst])).long()
+        gen = torch.Generator().manual_seed(trial)
+        scale = float(rng.choice([0.5, 1.5, 4.0]))
+        q, k = (torch.randn(n, heads, head_dim, generator=gen) * scale for _ in range(2))
+        v, dout = (torch.randn(n, heads, head_dim, generator=gen) for _ in range(2))
+        kind = rng.choice(["none", "edge", "edge_head"])
+        bias = {"none": None, "edge": torch.randn(e, generator=gen) * 0.3,
+                "edge_head": torch.randn(e, heads, generator=gen) * 0.3}[str(kind)]
+        res = _run_cuda(q, k, v, ei, dout, bias, tile_edges=tile_edges)
+        ref_out, _ = sao.forward_closed_form(q, k, v, ei, bias)
+        dq, dk, dv, dt = sao.backward_closed_form(q, k, v, ei, dout, bias)
+        ctx = (trial, n, e, heads, head_dim, tile_edges, str(kind))
+        # absolute floor: rows with a single in-edge have gradients that cancel to ~1e-7 of their operands
+        floor = 1e-6 * max(1.0, scale * scale)
+        for name, ref in (("out", ref_out), ("dq", dq), ("dk", dk), ("dv", dv)):
+            err = np.abs(res[name].double().cpu().numpy() - ref).max() if ref.size else 0.0
+            assert err < TOL_F32 * max(float(np.abs(ref).max()) if ref.size else 0.0, 0.0) + floor, (name, err, ctx)
+        if bias is not None and e > 0:
+            ref = dt if str(kind) == "edge_head" else dt.sum(axis=1)
+            err = np.abs(res["dbias"].double().cpu().numpy() - ref).max()
+            assert err < TOL_F32 * float(np.abs(ref).max()) + floor, ("dbias", err, ctx)

@@ -110,4 +110,6 @@ def sparse_graph_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
             # the kernels reduce a shared bias gradient inside one lane group only; let autograd sum heads
             bias = bias.unsqueeze(1).expand(-1, heads)
         bias = bias.contiguous()
+        if graph.n_edges == 0:
+            bias = None  # nothing to add the (empty) bias to
     return _SparseGraphAttention.apply(q, k, v, bias, graph)
