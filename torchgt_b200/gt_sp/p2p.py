@@ -21,7 +21,7 @@ from torch import Tensor
 from .. import _cabi
 
 _GROW_ALIGN = 2 << 20
-DEFAULT_SPIN_LIMIT = 20_000_000  # polls of the barrier before it gives up (tens of seconds)
+DEFAULT_SPIN_LIMIT = 60_000_000  # polls of the barrier before it gives up (about a minute)
 
 
 class PeerExchangeTimeout(RuntimeError):
