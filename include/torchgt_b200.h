@@ -91,13 +91,16 @@ TGT_API int tgt_edge_layout_sizes(int64_t n_rows, int64_t n_edges, size_t* works
  * edge_index is a device int64 [2, n_edges] array, row 0 = source (K/V row), row 1 = destination
  * (Q / output row), exactly as consumed by CoreAttention.sparse_attention (attn_module.py:146-147).
  * ptr [n_rows + 1], other, perm, seg [n_edges] are device output buffers.
- * This call SYNCHRONISES the stream once (it is made once per batch, not per layer) and returns
- * TGT_ERR_INDEX_RANGE if any node id is outside [0, n_rows).
+ * With deferred_status == NULL this call SYNCHRONISES the stream once (it is made once per batch,
+ * not per layer) and returns TGT_ERR_INDEX_RANGE if any node id is outside [0, n_rows).  With a
+ * device int32 word in deferred_status nothing is synchronised: the word is set to 0, or to 1 if an
+ * id was out of range (such ids are replaced by 0 in the layout, so later kernels stay in bounds),
+ * and the caller reads it when convenient.
  */
 TGT_API int tgt_edge_layout_build(const int64_t* edge_index, int64_t n_edges, int64_t n_rows,
                                   int group_by, int32_t* ptr, int32_t* other, int32_t* perm,
                                   int32_t* seg, void* workspace, size_t workspace_bytes,
-                                  void* stream);
+                                  int32_t* deferred_status, void* stream);
 
 /*
  * Bytes of scratch tgt_sparse_attn_fwd (phase 0) / tgt_sparse_attn_bwd (phase 1) need for these

@@ -43,8 +43,8 @@ def test_argument_checks_run_before_any_cuda_call(lib):
     assert b"n_rows" in lib.tgt_last_error()
     assert lib.tgt_edge_layout_sizes(2**31, 0, ctypes.byref(n)) == 1
     assert lib.tgt_edge_layout_sizes(4, 4, None) == 1
-    assert lib.tgt_edge_layout_build(None, 5, 0, 1, None, None, None, None, None, 0, None) == 1
-    assert lib.tgt_edge_layout_build(None, 5, 10, 3, None, None, None, None, None, 0, None) == 1
+    assert lib.tgt_edge_layout_build(None, 5, 0, 1, None, None, None, None, None, 0, None, None) == 1
+    assert lib.tgt_edge_layout_build(None, 5, 10, 3, None, None, None, None, None, 0, None, None) == 1
     assert lib.tgt_debug_set_tile_edges(-1) == 1
     assert lib.tgt_debug_set_tile_edges(0) == 0
     layout = _cabi.TgtLayout(n_rows=4, n_edges=0, ptr=None, other=None, perm=None, seg=None)

@@ -59,6 +59,19 @@ def test_out_of_range_index_is_reported():
     SparseGraph(torch.tensor([[0, 1], [1, 2]]).cuda(), 5)
 
 
+def test_deferred_range_check_does_not_raise_at_build_time_but_on_check():
+    from torchgt_b200._cabi import TgtError
+    from torchgt_b200.graph import SparseGraph
+    good = SparseGraph(random_graph(2, 50, 3.0).cuda(), 50, defer_check=True)
+    good.by_src
+    good.check()
+    bad = SparseGraph(torch.tensor([[0, 1, 9], [1, 2, 0]]).cuda(), 5, defer_check=True)   # id 9 >= 5
+    with pytest.raises(TgtError, match="INDEX_RANGE"):
+        bad.check()
+    # the layout itself is in bounds (the bad id was replaced by 0), so using it cannot fault
+    assert int(bad.by_dst.other.max()) < 5 and int(bad.by_dst.seg.max()) < 5
+
+
 def test_graph_cache_hits_on_identity_and_on_content():
     from torchgt_b200.graph import clear_graph_cache, graph_for
     clear_graph_cache()

@@ -53,7 +53,7 @@ SIGNATURES = {
     "tgt_debug_set_tile_edges": (c_int, [c_int]),
     "tgt_edge_layout_sizes": (c_int, [c_int64, c_int64, POINTER(c_size_t)]),
     "tgt_edge_layout_build": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
-                                      c_void_p, c_void_p, c_size_t, c_void_p]),
+                                      c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "tgt_sparse_attn_scratch_bytes": (c_int, [_PL, _PL, c_int, c_int, c_int, c_int, POINTER(c_size_t)]),
     "tgt_sparse_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, _PL, c_void_p,
                                     c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),

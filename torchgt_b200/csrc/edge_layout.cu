@@ -116,7 +116,7 @@ extern "C" int tgt_edge_layout_sizes(int64_t n_rows, int64_t n_edges, size_t* wo
 extern "C" int tgt_edge_layout_build(const int64_t* edge_index, int64_t n_edges, int64_t n_rows,
                                      int group_by, int32_t* ptr, int32_t* other, int32_t* perm,
                                      int32_t* seg, void* workspace, size_t workspace_bytes,
-                                     void* stream_) {
+                                     int32_t* deferred_status, void* stream_) {
   using namespace tgt;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(n_rows >= 0 && n_edges >= 0, "n_rows and n_edges must be >= 0");
@@ -140,7 +140,8 @@ extern "C" int tgt_edge_layout_build(const int64_t* edge_index, int64_t n_edges,
   char* base = static_cast<char*>(workspace);
   int32_t* keys = reinterpret_cast<int32_t*>(base + w.keys);
   int32_t* iota = reinterpret_cast<int32_t*>(base + w.iota);
-  int32_t* flag = reinterpret_cast<int32_t*>(base + w.flag);
+  // the range-check result goes to the caller's word when the check is deferred
+  int32_t* flag = deferred_status != nullptr ? deferred_status : reinterpret_cast<int32_t*>(base + w.flag);
   void* cub_tmp = base + w.cub;
 
   const int64_t* key64 = edge_index + (group_by == 1 ? n_edges : 0);
@@ -157,6 +158,7 @@ extern "C" int tgt_edge_layout_build(const int64_t* edge_index, int64_t n_edges,
   finalize_kernel<<<grid_for(n_edges + 1), kThreads, 0, stream>>>(seg, perm, other64, n_edges,
                                                                   n_rows, other, ptr);
   TGT_CHECK_CUDA(cudaGetLastError());
+  if (deferred_status != nullptr) return TGT_OK;  // no synchronisation: the caller reads the word later
 
   int32_t h_flag = 0;
   TGT_CHECK_CUDA(cudaMemcpyAsync(&h_flag, flag, 4, cudaMemcpyDeviceToHost, stream));

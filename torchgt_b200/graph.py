@@ -20,7 +20,7 @@ class EdgeLayout:
     ``perm`` is the stable argsort of the grouping endpoint, ``seg`` that endpoint in sorted order,
     ``other`` the opposite endpoint in sorted order, ``ptr`` the row pointers (all int32, on the GPU)."""
 
-    def __init__(self, edge_index: torch.Tensor, n_rows: int, group_by: int):
+    def __init__(self, edge_index: torch.Tensor, n_rows: int, group_by: int, defer_check: bool = False):
         lib = _cabi.load()
         dev = edge_index.device
         n_edges = int(edge_index.shape[1])
@@ -34,9 +34,12 @@ class EdgeLayout:
         workspace = torch.empty(max(ws.value, 16), dtype=torch.uint8, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
         nz = lambda t: t.data_ptr() if t.numel() else None
+        # deferred check: the build does not synchronise; `bad_index` is read by SparseGraph.check()
+        self.bad_index = torch.zeros(1, **i32) if defer_check else None
         _cabi.check(lib.tgt_edge_layout_build(
             nz(edge_index), n_edges, n_rows, group_by, self.ptr.data_ptr(), nz(self.other), nz(self.perm),
-            nz(self.seg), workspace.data_ptr(), workspace.numel(), stream))
+            nz(self.seg), workspace.data_ptr(), workspace.numel(),
+            self.bad_index.data_ptr() if defer_check else None, stream))
         self.n_rows, self.n_edges, self.group_by = n_rows, n_edges, group_by
         self.c = _cabi.TgtLayout(n_rows=n_rows, n_edges=n_edges, ptr=self.ptr.data_ptr(), other=nz(self.other),
                                  perm=nz(self.perm), seg=nz(self.seg))
@@ -48,7 +51,10 @@ class EdgeLayout:
 class SparseGraph:
     """Handle holding both layouts of one batch graph.  Build once, pass in place of ``edge_index``."""
 
-    def __init__(self, edge_index: torch.Tensor, n_rows: int):
+    def __init__(self, edge_index: torch.Tensor, n_rows: int, defer_check: bool = False):
+        """``defer_check=True`` builds without synchronising the stream (for pipelined input loops): node
+        ids outside [0, n_rows) are then not raised here but by a later :meth:`check` (they are replaced by
+        0 in the layout, so kernels stay in bounds)."""
         if edge_index.dim() != 2 or edge_index.shape[0] != 2:
             raise ValueError("edge_index must be [2, E]")
         if not edge_index.is_cuda:
@@ -57,7 +63,8 @@ class SparseGraph:
         self.n_rows = int(n_rows)
         self.n_edges = int(edge_index.shape[1])
         self.device = edge_index.device
-        self.by_dst = EdgeLayout(edge_index, self.n_rows, 1)
+        self._defer = bool(defer_check)
+        self.by_dst = EdgeLayout(edge_index, self.n_rows, 1, self._defer)
         self._edge_index = edge_index  # kept until by_src is built
         self._by_src: Optional[EdgeLayout] = None
 
@@ -65,9 +72,15 @@ class SparseGraph:
     def by_src(self) -> EdgeLayout:
         """Built on first backward (inference never needs it)."""
         if self._by_src is None:
-            self._by_src = EdgeLayout(self._edge_index, self.n_rows, 0)
+            self._by_src = EdgeLayout(self._edge_index, self.n_rows, 0, self._defer)
             self._edge_index = None
         return self._by_src
+
+    def check(self) -> None:
+        """Raise if a deferred build saw a node id outside [0, n_rows) (synchronises)."""
+        for lay in (self.by_dst, self._by_src):
+            if lay is not None and lay.bad_index is not None and int(lay.bad_index.item()) != 0:
+                raise _cabi.TgtError(5, f"edge_index holds a node id outside [0, {self.n_rows})")
 
 
 # ---- cache: the reference passes a raw edge_index tensor to every layer ---------------------------
