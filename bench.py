@@ -198,11 +198,24 @@ def workload_config(n_gpus, n_rows, n_edges, dtype, name="64k"):
 
 
 # ---------------------------------------------------------------------------------------------------
-def epoch_benchmark(rank, world, dev, epochs=12):
-    """End-to-end training epoch of the node-level Graphormer at sequence length 64K, timed the way the
-    reference times it (main_sp_sparse_node_level.py:196-221): per iteration from "inputs are on the GPU"
-    to "optimizer step done and device idle", summed over the epoch's two batches (64,000 and 37,608
-    nodes — the sizes of its ogbn-arxiv run), averaged over the epochs after the fourth.  The sequence
+EPOCH_SHAPES = {
+    # (seed, nodes, random edges, cross-cluster fraction, zipf exponent) per batch; features; classes
+    "64k": {"batches": ((42, 64000, 334450, 0.315, 0.0), (43, 37608, 228357 - 3 * 37608, 0.315, 0.0)),
+            "features": 128, "classes": 40, "epochs": 12},
+    # the shape of the reference's ogbn-products run at sequence length 870,000: a full batch and a shorter
+    # last one (about 599 K nodes and 9.2 M edges; 8 clusters of 74,878 nodes here)
+    "870k": {"batches": ((42, 870000, 18214272 - 3 * 870000, 0.0812, 2.1),
+                         (43, 599024, 9200000 - 3 * 599024, 0.0812, 2.1)),
+             "features": 100, "classes": 47, "epochs": 8},
+}
+
+
+def epoch_benchmark(rank, world, dev, workload="64k"):
+    """End-to-end training epoch of the node-level Graphormer at sequence length 64K or 870K, timed the
+    way the reference times it (main_sp_sparse_node_level.py:196-221): per iteration from "inputs are on
+    the GPU" to "optimizer step done and device idle", summed over the epoch's two batches (64,000 and
+    37,608 nodes, the sizes of its ogbn-arxiv run; 870,000 and 599,024 nodes with 18.2 M and 9.2 M edges
+    for the ogbn-products shape), averaged over the epochs after the fourth.  The sequence
     is split over the ranks (strong scaling, as in the reference); weights are replicated and their
     gradients averaged with one flat all-reduce."""
     import torch.distributed as dist
@@ -218,18 +231,20 @@ def epoch_benchmark(rank, world, dev, epochs=12):
     # the dense layers around the path are library GEMMs; TF32 is what the reference's PyTorch (1.10) used
     # for them by default on Ampere-class GPUs
     torch.backends.cuda.matmul.allow_tf32 = True
-    model = Graphormer(4, 8, 128, 64, 40, 1, 0.3, 0.1, 0.5, 64, 1).to(dev).train()
+    shape = EPOCH_SHAPES[workload]
+    epochs, n_feat, n_cls = shape["epochs"], shape["features"], shape["classes"]
+    model = Graphormer(4, 8, n_feat, 64, n_cls, 1, 0.3, 0.1, 0.5, 64, 1).to(dev).train()
     if world > 1:
         for p in model.parameters():
             dist.broadcast(p.data, src=0)
     opt = torch.optim.AdamW(model.parameters(), lr=2e-4, weight_decay=0.01, fused=True, capturable=True)
     batches = []
-    for seed, n_nodes, random_edges in ((42, 64000, 334450), (43, 37608, 228357 - 3 * 37608)):
-        ei, n_rows = clustered_edges(seed, n_nodes, 8, random_edges, 0.315)
+    for seed, n_nodes, random_edges, cross, zipf in shape["batches"]:
+        ei, n_rows = clustered_edges(seed, n_nodes, 8, random_edges, cross, zipf_exponent=zipf)
         L = n_nodes // world
         gen = torch.Generator().manual_seed(seed + 100)
-        x = torch.randn(n_nodes, 128, generator=gen)
-        y = torch.randint(0, 40, (n_nodes,), generator=gen)
+        x = torch.randn(n_nodes, n_feat, generator=gen)
+        y = torch.randint(0, n_cls, (n_nodes,), generator=gen)
         ei = adjust_edge_index_nomerge(ei, L) if world > 1 else ei
         graph = SparseGraph(ei.to(dev), world * (L + 1) if world > 1 else n_rows)
         graph.by_src
@@ -277,8 +292,8 @@ def epoch_benchmark(rank, world, dev, epochs=12):
     result = {"epoch_time_s": eager_time, "eager_epoch_time_s": eager_time, "timing": "eager PyTorch step",
               "iterations_per_epoch": len(batches),
               "batches": [{"nodes": b[4], "edges": b[5]} for b in batches],
-              "model": "Graphormer node-level, 4 layers, hidden 64, 8 heads, ffn 64, 128 features -> 40 classes, "
-                       "111,913 parameters, dropout as the reference's defaults",
+              "model": f"Graphormer node-level, 4 layers, hidden 64, 8 heads, ffn 64, {n_feat} features -> {n_cls} "
+                       f"classes, {sum(p.numel() for p in params):,} parameters, dropout as the reference's defaults",
               "includes": "forward, nll_loss, backward, flat gradient all-reduce (N > 1), fused AdamW step; inputs and "
                           "edge layouts resident on the GPU, as the reference times it",
               "dense_layers": "torch.nn (library GEMMs with TF32, LayerNorm, dropout): not part of the hot path; "
@@ -497,9 +512,9 @@ def run_single_gpu(args, dtype):
     step_achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
     cpu, _ = cpu_reference_rate(edge_index, n_rows, steps=5, warmup=2, budget_s=20.0)
     epoch = None
-    if args.workload == "64k" and dtype == torch.float32 and os.environ.get("TGT_BENCH_EPOCH", "1") != "0":
+    if dtype == torch.float32 and os.environ.get("TGT_BENCH_EPOCH", "1") != "0":
         try:
-            epoch = epoch_benchmark(0, 1, dev)
+            epoch = epoch_benchmark(0, 1, dev, args.workload)
         except Exception as exc:          # the headline numbers above do not depend on this leg
             epoch = {"error": repr(exc)[:300]}
     line = {

@@ -18,6 +18,11 @@ Outputs (all small .npz files, committed):
                  merged by mean), around a toy local attention: outputs and gradients, P ranks
   graphormer_node_level.npz  the reference's node-level Graphormer: parameters, log-probabilities, loss and
                  parameter gradients of one training step (3 layers, dropout 0, one rank)
+  gt_node_level.npz   the same for the reference's node-level GT (3 layers, no global token, one rank)
+  gt_graph_level.npz  the reference's graph-level GT on two ranks (3 padded graphs of 40 integer-featured
+                 nodes): output, loss and the gradient of one copy of the loss
+  graphormer_graph_level.npz  the reference's graph-level Graphormer, one rank (3 padded graphs of 40 nodes,
+                 graph token at index 0 of each): output, loss, parameter gradients
 """
 from __future__ import annotations
 
@@ -337,18 +342,198 @@ def make_ulysses_cases(ref_path):
                  nprocs=world, join=True)
 
 
+def _gt_node_worker(rank, world, ref_path, port, out_path):
+    """Reference node-level GT (no global token), one rank, dropout 0, training mode (so the layer
+    goes through its exchange, which is a copy with one rank)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ref_path)
+    install_shims()
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def all_to_all_copy(output_list, input_list, group=None):
+        for o, i in zip(output_list, input_list):
+            o.copy_(i)
+    dist.all_to_all = all_to_all_copy
+    torch.distributed.all_to_all = all_to_all_copy
+    import gt_sp.initialize as init
+    n = 260
+    init.initialize_sequence_parallel(n, 1, 1, 1)
+    from models.gt_dist_node_level import GT
+    torch.manual_seed(21)
+    model = GT(3, 8, 20, 64, 6, 1, 0.0, 0.0, 0.0, 64, 0)
+    with torch.no_grad():                      # std 0.02/sqrt(L) would leave all attention scores ~0
+        for p_ in model.parameters():
+            p_.mul_(8.0)
+    gen = torch.Generator().manual_seed(22)
+    x = torch.randn(n, 20, generator=gen)
+    y = torch.randint(0, 6, (n,), generator=gen)
+    ei = torch.cat([torch.randint(0, n, (2, 5 * n), generator=gen), torch.arange(n).repeat(2, 1)], dim=1)
+    model.train()
+    out = model(x, None, ei, attn_type="sparse")
+    loss = torch.nn.functional.nll_loss(out, y)
+    loss.backward()
+    rec = {"x": x.numpy(), "y": y.numpy(), "edge_index": ei.numpy(), "out": out.detach().numpy(),
+           "loss": np.float64(loss.item())}
+    for name, p_ in model.state_dict().items():
+        rec["param/" + name] = p_.numpy()
+    for name, p_ in model.named_parameters():
+        if p_.grad is not None:
+            rec["grad/" + name] = p_.grad.numpy()
+    np.savez_compressed(out_path, **rec)
+    print("wrote", out_path, "loss", loss.item())
+    dist.destroy_process_group()
+
+
+class _Batch:
+    """The two attributes of the collated batch that the graph-level models read."""
+
+    def __init__(self, x, edge_index):
+        self.x, self.edge_index = x, edge_index
+
+
+def _gt_graph_worker(rank, world, ref_path, port, out_path):
+    """Reference graph-level GT on `world` gloo ranks (its backward does not run with one rank), dropout 0.
+    Recorded: the full inputs, the output (identical on all ranks) and the gradient of ONE copy of the
+    loss: encoder and embedding gradients summed over the ranks (each rank holds the part that flows
+    through its slice of the sequence), read-out gradients from rank 0 (every rank holds all of it)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ref_path)
+    install_shims()
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def all_to_all_via_single(output_list, input_list, group=None):
+        out = torch.empty_like(torch.stack(input_list))
+        dist.all_to_all_single(out, torch.stack(input_list).contiguous(), group=group)
+        for o, chunk in zip(output_list, out):
+            o.copy_(chunk)
+    dist.all_to_all = all_to_all_via_single
+    torch.distributed.all_to_all = all_to_all_via_single
+    import gt_sp.initialize as init
+    b, s, feats, classes = 3, 40, 5, 5
+    L = s // world
+    init.initialize_sequence_parallel(s, 1, 1, world)
+    from models.gt_dist_graph_level import GT
+    torch.manual_seed(31)
+    model = GT(2, 8, 64, 0.0, 0.0, 64, "ZINC", "multi_hop", 5, 0.0, classes)
+    with torch.no_grad():
+        for p_ in model.parameters():
+            p_.mul_(8.0)
+    gen = torch.Generator().manual_seed(32)
+    x = torch.randint(0, 64, (b, s, feats), generator=gen)
+    y = torch.randint(0, classes, (b,), generator=gen)
+    # edges inside each graph, numbered over the b * s flattened rows of the gathered batch
+    per_graph = []
+    for g in range(b):
+        e = torch.cat([torch.randint(0, s, (2, 4 * s), generator=gen), torch.arange(s).repeat(2, 1)], dim=1)
+        per_graph.append(e + g * s)
+    ei = torch.cat(per_graph, dim=1)
+    model.train()
+    out = model(_Batch(x[:, rank * L:(rank + 1) * L].contiguous(), ei), attn_type="sparse")
+    loss = torch.nn.functional.cross_entropy(out, y)
+    loss.backward()
+    grads = {}
+    for name, p_ in model.named_parameters():
+        if p_.grad is None:
+            continue
+        g = p_.grad.clone()
+        if not name.startswith("MLP_layer"):
+            dist.all_reduce(g)
+        grads[name] = g
+    if rank == 0:
+        rec = {"x": x.numpy(), "y": y.numpy(), "edge_index": ei.numpy(), "out": out.detach().numpy(),
+               "loss": np.float64(loss.item()), "world": np.int64(world)}
+        for name, p_ in model.state_dict().items():
+            rec["param/" + name] = p_.numpy()
+        for name, g in grads.items():
+            rec["grad/" + name] = g.numpy()
+        np.savez_compressed(out_path, **rec)
+        print("wrote", out_path, "loss", loss.item())
+    dist.destroy_process_group()
+
+
+def _graphormer_graph_worker(rank, world, ref_path, port, out_path):
+    """Reference graph-level Graphormer, one rank, dropout 0: 3 padded graphs of 40 nodes, one graph token
+    each at local index 0, edges over the 3 * 41 flattened rows."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ref_path)
+    install_shims()
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def all_to_all_copy(output_list, input_list, group=None):
+        for o, i in zip(output_list, input_list):
+            o.copy_(i)
+    dist.all_to_all = all_to_all_copy
+    torch.distributed.all_to_all = all_to_all_copy
+    import gt_sp.initialize as init
+    b, s, feats, classes = 3, 40, 2, 5
+    init._GLOBAL_TOKEN_NUM = 1
+    init.initialize_sequence_parallel(s, 1, 1, 1)
+    init.set_global_token_indices([0])
+    from models.graphormer_dist_graph_level import Graphormer
+    torch.manual_seed(41)
+    model = Graphormer(2, 8, 64, 0.0, 0.0, 64, "ZINC", "multi_hop", 5, 0.0, classes)
+    with torch.no_grad():
+        for p_ in model.parameters():
+            p_.mul_(8.0)
+    gen = torch.Generator().manual_seed(42)
+    batch = _Batch(torch.randint(0, 64, (b, s, feats), generator=gen), None)
+    batch.in_degree = torch.randint(0, 64, (b, s), generator=gen)
+    batch.out_degree = torch.randint(0, 64, (b, s), generator=gen)
+    y = torch.randint(0, classes, (b,), generator=gen)
+    rows = s + 1
+    per_graph = []
+    for g in range(b):
+        nodes = torch.arange(1, rows)
+        e = torch.cat([torch.randint(1, rows, (2, 4 * s), generator=gen), torch.arange(rows).repeat(2, 1),
+                       torch.stack([nodes, torch.zeros_like(nodes)]), torch.stack([torch.zeros_like(nodes), nodes])],
+                      dim=1)
+        per_graph.append(e + g * rows)
+    batch.edge_index = torch.cat(per_graph, dim=1)
+    rec = {"x": batch.x.numpy(), "in_degree": batch.in_degree.numpy(), "out_degree": batch.out_degree.numpy(),
+           "y": y.numpy(), "edge_index": batch.edge_index.numpy()}
+    model.train()
+    out = model(batch, attn_type="sparse")
+    loss = torch.nn.functional.cross_entropy(out, y)
+    loss.backward()
+    rec["out"], rec["loss"] = out.detach().numpy(), np.float64(loss.item())
+    for name, p_ in model.state_dict().items():
+        rec["param/" + name] = p_.numpy()
+    for name, p_ in model.named_parameters():
+        if p_.grad is not None:
+            rec["grad/" + name] = p_.grad.numpy()
+    np.savez_compressed(out_path, **rec)
+    print("wrote", out_path, "loss", loss.item())
+    dist.destroy_process_group()
+
+
+def make_gt_cases(ref_path):
+    import torch.multiprocessing as mp
+    mp.spawn(_gt_node_worker, args=(1, ref_path, 29641, str(OUT_DIR / "gt_node_level.npz")), nprocs=1, join=True)
+    mp.spawn(_gt_graph_worker, args=(2, ref_path, 29642, str(OUT_DIR / "gt_graph_level.npz")), nprocs=2, join=True)
+    mp.spawn(_graphormer_graph_worker, args=(1, ref_path, 29643, str(OUT_DIR / "graphormer_graph_level.npz")),
+             nprocs=1, join=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of zxmeng98/torchgt")
+    ap.add_argument("--only", default="", help="'gt' regenerates the GT and graph-level model files only")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     install_shims()
     torch.set_num_threads(1)
+    if args.only == "gt":
+        make_gt_cases(args.reference)
+        return
     make_attention_cases()
     make_edge_cases()
     make_ulysses_cases(args.reference)
     make_model_case(args.reference)
     make_variant_cases(args.reference)
+    make_gt_cases(args.reference)
 
 
 if __name__ == "__main__":

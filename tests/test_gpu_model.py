@@ -1,4 +1,5 @@
-"""The node-level Graphormer shell against the reference model's own outputs and gradients."""
+"""The model shells (node-level Graphormer, node- and graph-level GT) against the reference models' own
+outputs and gradients."""
 import numpy as np
 import pytest
 import torch
@@ -41,3 +42,87 @@ def test_training_step_matches_the_reference_model():
     # evaluation mode (all heads, no exchange) gives the same numbers when dropout is 0
     with torch.no_grad():
         assert rel_err(model.eval()(x, None, ei, attn_type="sparse"), g["out"]) < TOL_MODEL
+
+
+def _load(model, g):
+    state = {k[len("param/"):]: torch.from_numpy(v) for k, v in g.items() if k.startswith("param/")}
+    model.load_state_dict(state, strict=True)
+    return model.cuda().train()
+
+
+def _check_grads(model, g, at_least):
+    checked = 0
+    for name, p in model.named_parameters():
+        key = "grad/" + name
+        if key in g and float(np.abs(g[key]).max()) < 1e-7:
+            # a gradient that cancels to rounding noise in the reference too (first layer's key bias)
+            assert float(p.grad.abs().max()) < 1e-6, name
+        elif key in g:
+            assert rel_err(p.grad, g[key]) < TOL_MODEL, name
+            checked += 1
+        else:   # parameters the reference declares but never applies
+            assert p.grad is None or float(p.grad.abs().max()) == 0.0, name
+    assert checked >= at_least
+
+
+def test_gt_node_level_training_step_matches_the_reference_model():
+    import torchgt_b200.gt_sp.initialize as init
+    from torchgt_b200.gt import GTNodeLevel
+    init.destroy_sequence_parallel()
+    g = load_golden("gt_node_level.npz")
+    model = _load(GTNodeLevel(3, 8, 20, 64, 6, 1, 0.0, 0.0, 0.0, 64, 0), g)
+    x, y = torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["y"]).cuda()
+    ei = torch.from_numpy(g["edge_index"]).cuda()
+    out = model(x, None, ei, attn_type="sparse")
+    loss = F.nll_loss(out, y)
+    loss.backward()
+    assert rel_err(out, g["out"]) < TOL_MODEL
+    assert abs(float(loss) - float(g["loss"])) < TOL_MODEL * abs(float(g["loss"]))
+    _check_grads(model, g, at_least=40)
+
+
+class _Batch:
+    def __init__(self, x, edge_index):
+        self.x, self.edge_index = x, edge_index
+
+
+def test_gt_graph_level_training_step_matches_the_reference_model_run_on_two_ranks():
+    """The vectors come from the reference on two sequence-parallel ranks (its backward does not run on
+    one); sequence parallelism is exact, so one GPU holding the whole sequence must give the same output
+    and the same gradient of one copy of the loss."""
+    import torchgt_b200.gt_sp.initialize as init
+    from torchgt_b200 import SparseGraph
+    from torchgt_b200.gt import GTGraphLevel
+    init.destroy_sequence_parallel()
+    g = load_golden("gt_graph_level.npz")
+    model = _load(GTGraphLevel(2, 8, 64, 0.0, 0.0, 64, "ZINC", "multi_hop", 5, 0.0, 5), g)
+    x, y = torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["y"]).cuda()
+    ei = torch.from_numpy(g["edge_index"]).cuda()
+    out = model(_Batch(x, ei), attn_type="sparse")
+    loss = F.cross_entropy(out, y)
+    loss.backward()
+    assert rel_err(out, g["out"]) < TOL_MODEL
+    assert abs(float(loss) - float(g["loss"])) < TOL_MODEL * abs(float(g["loss"]))
+    _check_grads(model, g, at_least=30)
+    # the same batch through a prebuilt graph handle
+    with torch.no_grad():
+        handle = SparseGraph(ei, x.shape[0] * x.shape[1])
+        assert rel_err(model(_Batch(x, handle), attn_type="sparse"), g["out"]) < TOL_MODEL
+
+
+def test_graphormer_graph_level_training_step_matches_the_reference_model():
+    import torchgt_b200.gt_sp.initialize as init
+    from torchgt_b200.graphormer import GraphormerGraphLevel
+    init.destroy_sequence_parallel()
+    g = load_golden("graphormer_graph_level.npz")
+    model = _load(GraphormerGraphLevel(2, 8, 64, 0.0, 0.0, 64, "ZINC", "multi_hop", 5, 0.0, 5), g)
+    batch = _Batch(torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["edge_index"]).cuda())
+    batch.in_degree = torch.from_numpy(g["in_degree"]).cuda()
+    batch.out_degree = torch.from_numpy(g["out_degree"]).cuda()
+    y = torch.from_numpy(g["y"]).cuda()
+    out = model(batch, attn_type="sparse")
+    loss = F.cross_entropy(out, y)
+    loss.backward()
+    assert rel_err(out, g["out"]) < TOL_MODEL
+    assert abs(float(loss) - float(g["loss"])) < TOL_MODEL * abs(float(g["loss"]))
+    _check_grads(model, g, at_least=35)

@@ -79,3 +79,63 @@ def test_nomerge_layer_on_real_gpus(world, transport):
             assert errs.pop("used_peer_memory") == (transport == "p2p")
             assert errs["a2a_21"] == 0.0 and errs["a2a_12"] == 0.0, (rank, errs)
             assert max(errs.values()) < 1e-5, (rank, errs)
+
+
+class _Batch:
+    def __init__(self, x, edge_index):
+        self.x, self.edge_index = x, edge_index
+
+
+def _gt_worker(rank, world, port, ret):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TGT_P2P_SPIN_LIMIT="4000000")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import torchgt_b200.gt_sp.initialize as init
+        from torchgt_b200.gt import GTGraphLevel
+        with np.load(GOLDEN / "gt_graph_level.npz") as z:
+            g = {k: z[k] for k in z.files}
+        s_len = g["x"].shape[1]
+        L = s_len // world
+        init.initialize_sequence_parallel(s_len, 1, 1, world)
+        model = GTGraphLevel(2, 8, 64, 0.0, 0.0, 64, "ZINC", "multi_hop", 5, 0.0, 5)
+        model.load_state_dict({k[len("param/"):]: torch.from_numpy(v) for k, v in g.items() if k.startswith("param/")},
+                              strict=True)
+        model = model.to(dev).train()
+        x = torch.from_numpy(g["x"][:, rank * L:(rank + 1) * L]).contiguous().to(dev)
+        out = model(_Batch(x, torch.from_numpy(g["edge_index"]).to(dev)), attn_type="sparse")
+        loss = torch.nn.functional.cross_entropy(out, torch.from_numpy(g["y"]).to(dev))
+        loss.backward()
+        ref = torch.from_numpy(g["out"]).to(dev)
+        errs = {"out": float((out.detach() - ref).abs().max() / ref.abs().max())}
+        worst = 0.0
+        for name, p in model.named_parameters():
+            if "grad/" + name not in g:
+                continue
+            grad = p.grad.clone()
+            if not name.startswith("MLP_layer"):       # each rank holds the part through its slice of the sequence
+                dist.all_reduce(grad)
+            gref = torch.from_numpy(g["grad/" + name]).to(dev)
+            if float(gref.abs().max()) < 1e-7:
+                continue
+            worst = max(worst, float((grad - gref).abs().max() / gref.abs().max()))
+        errs["grads"] = worst
+        torch.cuda.synchronize()
+        ret[rank] = errs
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gt_graph_level_model_on_two_gpus_matches_the_reference_on_two_ranks():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as manager:
+        ret = manager.dict()
+        mp.spawn(_gt_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+        for rank in range(2):
+            assert ret[rank]["out"] < 1e-4 and ret[rank]["grads"] < 1e-4, (rank, dict(ret[rank]))

@@ -137,3 +137,16 @@ def test_graphormer_shell_loads_reference_checkpoints_and_counts_the_same_parame
     readme_model = Graphormer(4, 8, 128, 64, 40, 1, 0.3, 0.1, 0.5, 64, 1)
     n = sum(p.numel() for p in readme_model.parameters())
     assert n == 111913 == int(g["params_of_the_readme_model"])   # the count the reference's README logs
+
+
+def test_gt_and_graph_level_shells_load_reference_checkpoints(sp_state):
+    from torchgt_b200.graphormer import GraphormerGraphLevel
+    from torchgt_b200.gt import GTGraphLevel, GTNodeLevel
+    graph_level = (2, 8, 64, 0.0, 0.0, 64, "ZINC", "multi_hop", 5, 0.0, 5)
+    for model, name in ((GTNodeLevel(3, 8, 20, 64, 6, 1, 0.0, 0.0, 0.0, 64, 0), "gt_node_level.npz"),
+                        (GTGraphLevel(*graph_level), "gt_graph_level.npz"),
+                        (GraphormerGraphLevel(*graph_level), "graphormer_graph_level.npz")):
+        g = load_golden(name)
+        state = {k[len("param/"):]: torch.from_numpy(v) for k, v in g.items() if k.startswith("param/")}
+        assert set(state) == set(model.state_dict())
+        model.load_state_dict(state, strict=True)

@@ -1,7 +1,8 @@
-"""Node-level Graphormer shell around the sparse attention path.
+"""Graphormer shells (node-level and graph-level) around the sparse attention path.
 
-Same constructor arguments, sub-module names and ``state_dict`` keys as the reference model
-(models/graphormer_dist_node_level.py:226-395), so its checkpoints load with ``strict=True``.  The dense
+Same constructor arguments, sub-module names and ``state_dict`` keys as the reference models
+(models/graphormer_dist_node_level.py:226-395, models/graphormer_dist_graph_level.py:28-76,318-505),
+so their checkpoints load with ``strict=True``.  The dense
 layers are ordinary ``torch.nn`` modules (library GEMMs); the attention and its sequence-parallel
 exchange are this library's kernels.  It exists so that end-to-end step and epoch times can be measured
 without the reference's code; the dense-bias branch of the reference model (never taken on the sparse
@@ -21,7 +22,8 @@ from .gt_sp.layer import DistributedAttentionNoMerge
 
 
 def _init_params(module: nn.Module, n_layers: int) -> None:
-    """models/graphormer_dist_node_level.py:18-25: N(0, 0.02/sqrt(L)) linears, N(0, 0.02) embeddings."""
+    """models/graphormer_dist_node_level.py:18-25, models/graphormer_dist_graph_level.py:20-26:
+    N(0, 0.02/sqrt(L)) linears, N(0, 0.02) embeddings."""
     if isinstance(module, nn.Linear):
         module.weight.data.normal_(mean=0.0, std=0.02 / math.sqrt(n_layers))
         if module.bias is not None:
@@ -45,7 +47,7 @@ class MultiHeadAttention(nn.Module):
     """Q/K/V projections, the Ulysses layer around the sparse attention, output projection
     (models/graphormer_dist_node_level.py:226-273)."""
 
-    def __init__(self, hidden_size: int, attention_dropout_rate: float, num_heads: int, attn_bias_dim: int):
+    def __init__(self, hidden_size: int, attention_dropout_rate: float, num_heads: int, attn_bias_dim: int = 1):
         super().__init__()
         self.num_heads = num_heads
         self.att_size = hidden_size // num_heads
@@ -57,7 +59,7 @@ class MultiHeadAttention(nn.Module):
         self.dist_attn = DistributedAttentionNoMerge(core, group)
         self.output_layer = nn.Linear(num_heads * self.att_size, hidden_size)
 
-    def forward(self, x, attn_bias=None, edge_index=None, attn_type=None):
+    def forward(self, x, attn_bias=None, edge_index=None, attn_type=None, mask=None):
         b = x.size(0)
         q = self.linear_q(x).view(b, -1, self.num_heads, self.att_size)
         k = self.linear_k(x).view(b, -1, self.num_heads, self.att_size)
@@ -72,7 +74,7 @@ class MultiHeadAttention(nn.Module):
 class EncoderLayer(nn.Module):
     """Pre-norm attention block + pre-norm feed-forward block (models/graphormer_dist_node_level.py:276-314)."""
 
-    def __init__(self, hidden_size, ffn_size, dropout_rate, attention_dropout_rate, num_heads, attn_bias_dim):
+    def __init__(self, hidden_size, ffn_size, dropout_rate, attention_dropout_rate, num_heads, attn_bias_dim=1):
         super().__init__()
         self.self_attention_norm = nn.LayerNorm(hidden_size)
         self.self_attention = MultiHeadAttention(hidden_size, attention_dropout_rate, num_heads, attn_bias_dim)
@@ -81,7 +83,7 @@ class EncoderLayer(nn.Module):
         self.ffn = FeedForwardNetwork(hidden_size, ffn_size, dropout_rate)
         self.ffn_dropout = nn.Dropout(dropout_rate)
 
-    def forward(self, x, attn_bias=None, edge_index=None, attn_type=None):
+    def forward(self, x, attn_bias=None, edge_index=None, attn_type=None, mask=None):
         y = self.self_attention(self.self_attention_norm(x), attn_bias, edge_index, attn_type=attn_type)
         x = x + self.self_attention_dropout(y)
         y = self.ffn(self.ffn_norm(x))
@@ -125,3 +127,64 @@ class Graphormer(nn.Module):
             h = layer(h, attn_bias=None, edge_index=edge_index, attn_type=attn_type)
         h = self.final_ln(h)
         return F.log_softmax(self.downstream_out_proj(h[0, 1:, :]), dim=1)
+
+
+class GraphNodeFeature(nn.Module):
+    """Summed atom embeddings + in/out-degree embeddings, graph token prepended at index 0
+    (models/graphormer_dist_graph_level.py:28-71)."""
+
+    def __init__(self, num_heads, num_atoms, num_in_degree, num_out_degree, hidden_dim):
+        super().__init__()
+        self.num_heads = num_heads
+        self.num_atoms = num_atoms
+        self.atom_encoder = nn.Embedding(num_atoms, hidden_dim, padding_idx=0)
+        self.in_degree_encoder = nn.Embedding(num_in_degree, hidden_dim, padding_idx=0)
+        self.out_degree_encoder = nn.Embedding(num_out_degree, hidden_dim, padding_idx=0)
+        self.graph_token = nn.Embedding(1, hidden_dim)
+
+    def forward(self, batched_data):
+        x = batched_data.x
+        h = (self.atom_encoder(x).sum(dim=-2) + self.in_degree_encoder(batched_data.in_degree) +
+             self.out_degree_encoder(batched_data.out_degree))
+        token = self.graph_token.weight.unsqueeze(0).expand(x.size(0), -1, -1)
+        return torch.cat([token, h], dim=1)
+
+
+# (atoms, in-degrees, out-degrees) table sizes per dataset family (models/graphormer_dist_graph_level.py:424-445)
+_TABLES = {"ZINC": (64, 64, 64), "MalNet": (560000, 560000, 560000)}
+
+
+class GraphormerGraphLevel(nn.Module):
+    """``Graphormer(n_layers, num_heads, hidden_dim, dropout_rate, intput_dropout_rate, ffn_dim,
+    dataset_name, edge_type, multi_hop_max_dist, attention_dropout_rate, output_dim)`` of
+    models/graphormer_dist_graph_level.py:409-505: one padded graph per sequence, this rank's graph token
+    at local index 0, prediction read from the token.  The reference builds no attention bias on this
+    path (its ``GraphAttnBias`` is commented out), so none is built here."""
+
+    def __init__(self, n_layers, num_heads, hidden_dim, dropout_rate, intput_dropout_rate, ffn_dim, dataset_name,
+                 edge_type, multi_hop_max_dist, attention_dropout_rate, output_dim):
+        super().__init__()
+        atoms, in_deg, out_deg = _TABLES.get(dataset_name, (7000, 7000, 7000))
+        self.graph_node_feature = GraphNodeFeature(num_heads, atoms, in_deg, out_deg, hidden_dim)
+        self.input_dropout = nn.Dropout(intput_dropout_rate)
+        self.layers = nn.ModuleList(
+            [EncoderLayer(hidden_dim, ffn_dim, dropout_rate, attention_dropout_rate, num_heads)
+             for _ in range(n_layers)])
+        self.final_ln = nn.LayerNorm(hidden_dim)
+        if dataset_name == "PCQM4M-LSC":
+            self.out_proj = nn.Linear(hidden_dim, 1)
+        else:
+            self.downstream_out_proj = nn.Linear(hidden_dim, output_dim)
+        self.apply(lambda m: _init_params(m, n_layers))   # embeddings are drawn over their padding row too
+
+    def forward(self, batched_data, perturb=None, attn_type=None):
+        """batched_data: ``x`` int64 [b, s/p, F], ``in_degree`` / ``out_degree`` int64 [b, s/p], ``edge_index``
+        [2, E] over the flattened rows of the gathered batch (or a ``SparseGraph``); returns [b, output_dim]."""
+        h = self.input_dropout(self.graph_node_feature(batched_data))
+        edge_index = batched_data.edge_index
+        for layer in self.layers:
+            h = layer(h, None, edge_index=edge_index, attn_type=attn_type)
+        h = self.final_ln(h)
+        head = self.out_proj if hasattr(self, "out_proj") else self.downstream_out_proj
+        return head(h[:, 0, :])
+
