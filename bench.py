@@ -387,9 +387,9 @@ def capture(fn):
 
 
 def kernels_per_step(graph, with_dbias=True):
-    # forward, dQ pass, dK/dV pass: one walk + one stitch kernel each; the row-statistics pre-pass runs
-    # only when dbias is computed
-    return 3 * 2 + (1 if with_dbias else 0)
+    # forward, dQ pass, dK/dV pass: one kernel each (rows that cross tiles are finished inside it); the
+    # row-statistics pre-pass runs only when dbias is computed
+    return 3 + (1 if with_dbias else 0)
 
 
 def run_single_gpu(args, dtype):
@@ -428,6 +428,25 @@ def run_single_gpu(args, dtype):
     stop.record()
     torch.cuda.synchronize()
     ms_per_step = start.elapsed_time(stop) / args.steps
+
+    # ---- the same step with the bias as a plain input (no dbias: no statistics pre-pass) ----------------
+    import copy
+    plain_sets = []
+    for b in sets:
+        b2 = copy.copy(b)
+        b2.dbias = None
+        plain_sets.append(b2)
+    plain_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 6))) for b in plain_sets]
+    for i in range(args.warmup):
+        plain_graphs[i % ROTATING_SETS].replay()
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(args.steps):
+        plain_graphs[i % ROTATING_SETS].replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms_no_dbias = start.elapsed_time(stop) / args.steps
+    plain_graphs.clear()
 
     # ---- per-phase durations (each phase its own graph, events around every replay) ------------------
     names = ["fwd_kernel", "bwd_dq_kernel", "bwd_dkv_kernel"]
@@ -541,7 +560,12 @@ def run_single_gpu(args, dtype):
                      "phases_ms": phase_ms,
                      "phases_frac": {n: bytes_[n] / (phase_ms[n] * 1e-3) / 1e9 / peak for n in names},
                      "step": {"algorithmic_bytes": step_bytes, "achieved": step_achieved,
-                              "frac": step_achieved / peak, "frac_of_nominal_8TBs": step_achieved / 8000.0}},
+                              "frac": step_achieved / peak, "frac_of_nominal_8TBs": step_achieved / 8000.0},
+                     "step_without_dbias": {
+                         "ms_per_step": ms_no_dbias, "edges_per_s": n_edges / (ms_no_dbias * 1e-3),
+                         "frac": step_bytes / (ms_no_dbias * 1e-3) / 1e9 / peak,
+                         "note": "bias read as an input, its gradient not computed (the byte count has no dbias "
+                                 "term either); the headline step computes dbias as well"}},
         "cpu_baseline": cpu,
         "epoch": epoch,
     }

@@ -14,9 +14,11 @@
 // A row that crosses a range boundary leaves partial sums in shared memory ("head" = the range
 // starts inside the row, "tail" = the row starts here and runs past the range); after a barrier
 // the group that holds the tail adds the heads of the following groups in order.  If the row
-// also crosses the tile boundary the CTA writes its sum to a per-tile carry in global memory and a
-// small second kernel adds those in tile order.  Every sum has a fixed order: no atomics, bitwise
-// reproducible results.  Rows without edges are zero-filled by the group that walks the gap.
+// also crosses the tile boundary the CTA writes its sum to a per-tile carry in global memory and
+// counts itself in on the row's arrival counter; the CTA that arrives last adds the carries in tile
+// order and finishes the row (nobody waits for anybody).  Every sum has a fixed order whichever CTA
+// does it: no floating-point atomics, bitwise reproducible results.  Rows without edges are
+// zero-filled by the group that walks the gap.
 #pragma once
 
 #include <type_traits>
@@ -56,6 +58,8 @@ struct SegWalk {
   int ge;          // edges per lane group per tile (multiple of kUnroll, <= GE_MAX)
   int n_tiles;
   float* gcarry;   // [n_tiles][2][gridDim.y * G * NACC] cross-tile partial sums
+  int* tile_done;  // [gridDim.y][n_tiles] arrivals per row that crosses tiles, indexed by the tile it
+                   // starts in; zero when the kernel starts
   bool need_perm;  // stage perm[] (bias or dbias in original edge order)
 };
 
@@ -123,6 +127,9 @@ __device__ __forceinline__ float fast_exp(float x) {
   return fmaf(e, r * kLn2, e);
 }
 
+template <int G, class Policy>
+__device__ __forceinline__ void finish_row(const SegWalk& w, const Policy& pol, float* s_part, int tile);
+
 // The walk.  Policy supplies:
 //   static constexpr int NACC;                     accumulators per lane
 //   struct Operands;                               what one edge loads
@@ -135,7 +142,7 @@ __device__ __forceinline__ float fast_exp(float x) {
 template <int G, class Policy>
 __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, int32_t* s_other,
                                           int32_t* s_seg, int32_t* s_perm, float* s_carry,
-                                          int32_t* s_carry_row) {
+                                          int32_t* s_carry_row, float* s_part, int32_t* s_finish) {
   constexpr int NG = TileGeom<G>::NG;
   constexpr int NACC = Policy::NACC;
   const int tid = threadIdx.x;
@@ -288,24 +295,48 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
       pol.finalize(r, acc);
     }
   }
+
+  // ---- rows that cross tile boundaries: every tile such a row touches has written one partial
+  // (the tile it starts in a tail carry, the others a head carry) and now counts itself in; the
+  // tile that arrives last finishes the row.  A tile touches at most two such rows.
+  if (w.n_tiles == 1) return;
+  __threadfence();   // this thread's carries are visible device-wide before the arrival is counted
+  __syncthreads();
+  if (tid == 0) {
+    const int first_row = row_of(0);
+    auto arrive = [&](int row) {
+      const int start_tile = __ldg(w.ptr + row) / te;
+      const int end_tile = (__ldg(w.ptr + row + 1) - 1) / te;
+      const int before = atomicAdd(w.tile_done + int64_t(blockIdx.y) * w.n_tiles + start_tile, 1);
+      return before == end_tile - start_tile ? start_tile : -1;
+    };
+    __threadfence();
+    s_finish[0] = s_halo[0] == first_row ? arrive(first_row) : -1;              // a head carry was written
+    s_finish[1] = (tile_cont_out && s_halo[0] != last_row) ? arrive(last_row) : -1;  // a tail carry
+    __threadfence();   // the other tiles' carries are read after their arrivals were seen
+  }
+  __syncthreads();     // from here on the index arrays are dead: s_part may overlay them
+#pragma unroll 1
+  for (int f = 0; f < 2; ++f) {
+    const int start_tile = s_finish[f];
+    if (start_tile >= 0) {
+      finish_row<G, Policy>(w, pol, s_part, start_tile);
+      __syncthreads();
+    }
+  }
 }
 
-// Second kernel: rows that cross tile boundaries.  One CTA per tile; the CTA of the tile in which
-// such a row STARTS adds that tile's tail carry and the head carries of the following tiles and
-// finishes the row.  The partials are dealt round-robin to 128 / G slots, each slot adds its share
-// in tile order, then the slots are combined in a fixed tree: the order never depends on timing.
+// Finishes the row that starts in `tile` and runs past its end, from the partials all its tiles have
+// delivered: that tile's tail carry and the head carries of the following tiles.  The partials are
+// dealt round-robin to 128 / G slots, each slot adds its share in tile order, then the slots are
+// combined in a fixed tree: the order depends neither on timing nor on which CTA runs this.
 template <int G, class Policy>
-__device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol, float* s_part) {
+__device__ __forceinline__ void finish_row(const SegWalk& w, const Policy& pol, float* s_part, int tile) {
   constexpr int NG = TileGeom<G>::NG;
   constexpr int NACC = Policy::NACC;
-  const int tile = blockIdx.x;
   const int te = NG * w.ge;
   const int64_t t1 = int64_t(tile + 1) * te;
-  if (t1 >= w.n_edges) return;                       // last tile: nothing runs past it
   const int r = __ldg(w.seg + t1 - 1);
-  if (__ldg(w.seg + t1) != r) return;                // the tile ends on a row boundary
-  const int row_begin = __ldg(w.ptr + r);
-  if (row_begin < t1 - te) return;                   // the row started in an earlier tile
   const int last_tile = (__ldg(w.ptr + r + 1) - 1) / te;
   const int slot = threadIdx.x / G, c = threadIdx.x % G;
   const int lanes_all = gridDim.y * G;
@@ -320,7 +351,7 @@ __device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol
   for (int i = slot; i < n_part; i += NG) {
     const float* p = base + (int64_t(tile + i) * 2 + (i == 0 ? 1 : 0)) * stride;
 #pragma unroll
-    for (int a = 0; a < NACC; ++a) acc[a] += __ldg(p + a);
+    for (int a = 0; a < NACC; ++a) acc[a] += __ldcg(p + a);   // written by other CTAs of this launch: read at L2
   }
   // combine the NG slots: halving tree through shared memory
   float* mine = s_part + (slot * G + c) * NACC;
@@ -413,11 +444,14 @@ inline int resident_ctas(Kernel kernel, int* cache) {
   return *cache;
 }
 
-// Tiling of one pass: edges per lane group, number of tiles, bytes of cross-tile carry.
+// Tiling of one pass: edges per lane group, number of tiles, bytes of cross-tile carry followed by
+// the arrival counters (scratch_bytes = both).
 struct TilePlan {
   int ge;
   int n_tiles;
   size_t carry_bytes;
+  size_t counter_bytes;
+  size_t scratch_bytes;
 };
 TilePlan plan_tiles(int64_t n_edges, const HeadSplit& hs, int nacc, int ctas_per_sm);
 
@@ -426,11 +460,24 @@ template <int G, int NACC>
 struct TileSmem {
   static constexpr int TE = TileGeom<G>::TE_MAX;
   static constexpr int NG = TileGeom<G>::NG;
-  int32_t other[TE + NG];
-  int32_t seg[TE + NG + 2];   // padded rows + the two halo words
-  int32_t perm[TE + NG];
+  struct Indices {
+    int32_t other[TE + NG];
+    int32_t seg[TE + NG + 2];   // padded rows + the two halo words
+    int32_t perm[TE + NG];
+  };
+  union {
+    Indices idx;                          // while the tile is walked
+    float part[kBlockThreads * NACC];     // afterwards: slots of finish_row
+  };
   float carry[NG * 2 * G * NACC];
   int32_t carry_row[NG * 2];
+  int32_t finish[2];
 };
+
+// The call every walk kernel makes.
+template <int G, class Policy>
+__device__ __forceinline__ void walk_tile_in(TileSmem<G, Policy::NACC>& sm, const SegWalk& w, const Policy& pol) {
+  walk_tile<G, Policy>(w, pol, sm.idx.other, sm.idx.seg, sm.idx.perm, sm.carry, sm.carry_row, sm.part, sm.finish);
+}
 
 }  // namespace tgt

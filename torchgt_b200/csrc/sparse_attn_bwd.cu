@@ -405,15 +405,7 @@ __global__ void TGT_WALK_BOUNDS bwd_dq_fused_kernel(const BwdParams p) {
   using Policy = DqFusedPolicy<T, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
   const Policy pol = make_dq_fused_policy<T, LPH, G>(p);
-  walk_tile<G, Policy>(p.walk, pol, sm.other, sm.seg, sm.perm, sm.carry, sm.carry_row);
-}
-
-template <typename T, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) bwd_dq_fused_stitch_kernel(const BwdParams p) {
-  using Policy = DqFusedPolicy<T, LPH, G>;
-  const Policy pol = make_dq_fused_policy<T, LPH, G>(p);
-  __shared__ float s_part[kBlockThreads * Policy::NACC];
-  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+  walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
 template <typename T, int LPH, int G>
@@ -421,15 +413,7 @@ __global__ void TGT_WALK_BOUNDS bwd_dq_kernel(const BwdParams p) {
   using Policy = DqPolicy<T, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
   const Policy pol = make_dq_policy<T, LPH, G>(p);
-  walk_tile<G, Policy>(p.walk, pol, sm.other, sm.seg, sm.perm, sm.carry, sm.carry_row);
-}
-
-template <typename T, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) bwd_dq_stitch_kernel(const BwdParams p) {
-  using Policy = DqPolicy<T, LPH, G>;
-  const Policy pol = make_dq_policy<T, LPH, G>(p);
-  __shared__ float s_part[kBlockThreads * Policy::NACC];
-  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+  walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
 template <typename T, int LPH, int G>
@@ -437,15 +421,7 @@ __global__ void TGT_WALK_BOUNDS bwd_dkv_kernel(const BwdParams p) {
   using Policy = DkvPolicy<T, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
   const Policy pol = make_dkv_policy<T, LPH, G>(p);
-  walk_tile<G, Policy>(p.walk, pol, sm.other, sm.seg, sm.perm, sm.carry, sm.carry_row);
-}
-
-template <typename T, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const BwdParams p) {
-  using Policy = DkvPolicy<T, LPH, G>;
-  const Policy pol = make_dkv_policy<T, LPH, G>(p);
-  __shared__ float s_part[kBlockThreads * Policy::NACC];
-  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+  walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
 enum { kWalkDq = 0, kWalkDkv = 1, kWalkDqFused = 2 };
@@ -468,7 +444,7 @@ int bwd_resident_ctas(int dtype, const HeadSplit& hs, int which) {
 }
 
 struct BwdScratch {
-  size_t stats, carry_a, carry_b, total;
+  size_t stats, carry_a, carry_b, counters, counter_bytes, total;
   TilePlan plan_a, plan_a_fused, plan_b;
 };
 
@@ -483,15 +459,23 @@ BwdScratch plan_bwd_scratch(const tgt_layout* by_dst, const HeadSplit& hs, int h
   s.carry_a = off;
   off += s.plan_a.carry_bytes > s.plan_a_fused.carry_bytes ? s.plan_a.carry_bytes : s.plan_a_fused.carry_bytes;
   s.carry_b = off; off += s.plan_b.carry_bytes;
+  // arrival counters of both passes side by side (one memset clears them): pass A first
+  s.counters = off;
+  const size_t ca = s.plan_a.counter_bytes > s.plan_a_fused.counter_bytes ? s.plan_a.counter_bytes
+                                                                           : s.plan_a_fused.counter_bytes;
+  s.counter_bytes = ca + s.plan_b.counter_bytes;
+  off += s.counter_bytes;
   s.total = off;
   return s;
 }
 
-void fill_walk(SegWalk* w, const tgt_layout& L, const TilePlan& tp, float* carry, bool need_perm) {
+void fill_walk(SegWalk* w, const tgt_layout& L, const TilePlan& tp, float* carry, int* counters,
+               bool need_perm) {
   w->ptr = L.ptr; w->other = L.other; w->perm = L.perm; w->seg = L.seg;
   w->n_rows = int(L.n_rows); w->n_edges = int(L.n_edges);
   w->ge = tp.ge; w->n_tiles = tp.n_tiles;
   w->gcarry = carry;
+  w->tile_done = counters;
   w->need_perm = need_perm;
 }
 
@@ -611,44 +595,30 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
     TGT_DISPATCH(dtype, hs.lph, hs.lph, TGT_LAUNCH_STATS);
 #undef TGT_LAUNCH_STATS
   }
+  int* counters_a = reinterpret_cast<int*>(base + sc.counters);
+  int* counters_b = reinterpret_cast<int*>(base + sc.counters + sc.counter_bytes - sc.plan_b.counter_bytes);
+  if (passes & 6) TGT_CHECK_CUDA(cudaMemsetAsync(counters_a, 0, sc.counter_bytes, stream));
   if ((passes & 2) && dbias == nullptr) {
     // pass A that derives the row statistics itself (and leaves them in scratch for pass B)
-    fill_walk(&p.walk, *by_dst, sc.plan_a_fused, reinterpret_cast<float*>(base + sc.carry_a),
+    fill_walk(&p.walk, *by_dst, sc.plan_a_fused, reinterpret_cast<float*>(base + sc.carry_a), counters_a,
               bias != nullptr);
     const dim3 grid(sc.plan_a_fused.n_tiles, hs.groups);
-#define TGT_LAUNCH_DQF(T, LPH, G)                                                   \
-  do {                                                                              \
-    bwd_dq_fused_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
-    if (sc.plan_a_fused.n_tiles > 1)                                                \
-      bwd_dq_fused_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
-  } while (0)
+#define TGT_LAUNCH_DQF(T, LPH, G) bwd_dq_fused_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
     TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQF);
 #undef TGT_LAUNCH_DQF
   } else if (passes & 2) {
     // pass A with per-edge dbias: uses the statistics of the pre-pass (stage 1)
-    fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a), true);
+    fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a), counters_a, true);
     const dim3 grid(sc.plan_a.n_tiles, hs.groups);
-    const dim3 sgrid(sc.plan_a.n_tiles, hs.groups);
-#define TGT_LAUNCH_DQ(T, LPH, G)                                               \
-  do {                                                                         \
-    bwd_dq_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);           \
-    if (sc.plan_a.n_tiles > 1)                                                 \
-      bwd_dq_stitch_kernel<T, LPH, G><<<sgrid, kBlockThreads, 0, stream>>>(p); \
-  } while (0)
+#define TGT_LAUNCH_DQ(T, LPH, G) bwd_dq_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
     TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQ);
 #undef TGT_LAUNCH_DQ
   }
   if (passes & 4) {
-    fill_walk(&p.walk, *by_src, sc.plan_b, reinterpret_cast<float*>(base + sc.carry_b),
+    fill_walk(&p.walk, *by_src, sc.plan_b, reinterpret_cast<float*>(base + sc.carry_b), counters_b,
               bias != nullptr);
     const dim3 grid(sc.plan_b.n_tiles, hs.groups);
-    const dim3 sgrid(sc.plan_b.n_tiles, hs.groups);
-#define TGT_LAUNCH_DKV(T, LPH, G)                                               \
-  do {                                                                          \
-    bwd_dkv_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);           \
-    if (sc.plan_b.n_tiles > 1)                                                  \
-      bwd_dkv_stitch_kernel<T, LPH, G><<<sgrid, kBlockThreads, 0, stream>>>(p); \
-  } while (0)
+#define TGT_LAUNCH_DKV(T, LPH, G) bwd_dkv_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
     TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DKV);
 #undef TGT_LAUNCH_DKV
   }

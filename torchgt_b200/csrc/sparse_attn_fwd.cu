@@ -117,16 +117,7 @@ __global__ void TGT_WALK_BOUNDS fwd_kernel(const FwdParams p) {
   using Policy = FwdPolicy<T, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
   const Policy pol = make_policy<T, LPH, G>(p);
-  walk_tile<G, Policy>(p.walk, pol, sm.other, sm.seg, sm.perm, sm.carry, sm.carry_row);
-}
-
-template <typename T, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) fwd_stitch_kernel(const FwdParams p) {
-  using Policy = FwdPolicy<T, LPH, G>;
-  // 32 % G == 0, so threadIdx.x % G is also the column of a lane inside its warp
-  const Policy pol = make_policy<T, LPH, G>(p);
-  __shared__ float s_part[kBlockThreads * Policy::NACC];
-  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+  walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
 // Resident CTAs per SM of fwd_kernel<T, LPH, G> for the run-time triple.
@@ -149,6 +140,8 @@ TilePlan plan_tiles(int64_t n_edges, const HeadSplit& hs, int nacc, int ctas_per
   const int64_t te = int64_t(kBlockThreads / hs.g) * t.ge;
   t.n_tiles = int((n_edges + te - 1) / te);
   t.carry_bytes = round_up(size_t(t.n_tiles) * 2 * size_t(hs.groups) * hs.g * nacc * 4, 256);
+  t.counter_bytes = round_up(size_t(t.n_tiles) * hs.groups * 4, 256);
+  t.scratch_bytes = t.carry_bytes + t.counter_bytes;
   return t;
 }
 
@@ -156,7 +149,7 @@ size_t fwd_scratch_bytes(const tgt_layout* L, int heads, int head_dim, int dtype
   HeadSplit hs;
   if (!split_heads(heads, head_dim, dtype, &hs) || L->n_edges == 0) return 0;
   const int nacc = (dtype == TGT_F32 ? 4 : 8) + 1;
-  return plan_tiles(L->n_edges, hs, nacc, fwd_resident_ctas(dtype, hs)).carry_bytes;
+  return plan_tiles(L->n_edges, hs, nacc, fwd_resident_ctas(dtype, hs)).scratch_bytes;
 }
 
 }  // namespace tgt
@@ -196,9 +189,9 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   }
   const int nacc = (dtype == TGT_F32 ? 4 : 8) + 1;
   const TilePlan tp = plan_tiles(L.n_edges, hs, nacc, fwd_resident_ctas(dtype, hs));
-  if (scratch == nullptr || scratch_bytes < tp.carry_bytes)
+  if (scratch == nullptr || scratch_bytes < tp.scratch_bytes)
     return set_error(TGT_ERR_WORKSPACE, "scratch holds %zu bytes, %zu needed", scratch_bytes,
-                     tp.carry_bytes);
+                     tp.scratch_bytes);
 
   FwdParams p;
   p.q = q; p.k = k; p.v = v; p.bias = bias; p.bias_heads = bias_heads;
@@ -210,16 +203,12 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   p.walk.n_rows = int(L.n_rows); p.walk.n_edges = int(L.n_edges);
   p.walk.ge = tp.ge; p.walk.n_tiles = tp.n_tiles;
   p.walk.gcarry = static_cast<float*>(scratch);
+  p.walk.tile_done = reinterpret_cast<int*>(static_cast<char*>(scratch) + tp.carry_bytes);
   p.walk.need_perm = bias != nullptr;
+  if (tp.n_tiles > 1) TGT_CHECK_CUDA(cudaMemsetAsync(p.walk.tile_done, 0, tp.counter_bytes, stream));
 
   const dim3 grid(tp.n_tiles, hs.groups);
-  const dim3 sgrid(tp.n_tiles, hs.groups);
-#define TGT_LAUNCH_FWD(T, LPH, G)                                     \
-  do {                                                                \
-    fwd_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);     \
-    if (tp.n_tiles > 1)                                               \
-      fwd_stitch_kernel<T, LPH, G><<<sgrid, kBlockThreads, 0, stream>>>(p); \
-  } while (0)
+#define TGT_LAUNCH_FWD(T, LPH, G) fwd_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
   TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_FWD);
 #undef TGT_LAUNCH_FWD
   TGT_CHECK_CUDA(cudaGetLastError());
