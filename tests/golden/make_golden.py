@@ -23,6 +23,8 @@ Outputs (all small .npz files, committed):
                  nodes): output, loss and the gradient of one copy of the loss
   graphormer_graph_level.npz  the reference's graph-level Graphormer, one rank (3 padded graphs of 40 nodes,
                  graph token at index 0 of each): output, loss, parameter gradients
+  graphormer_graph_level_P2.npz  the same model on two ranks (every rank's own graph token in front of its
+                 20 nodes of each graph): per-rank outputs and per-rank parameter gradients
 """
 from __future__ import annotations
 
@@ -509,12 +511,79 @@ def _graphormer_graph_worker(rank, world, ref_path, port, out_path):
     dist.destroy_process_group()
 
 
+def _graphormer_graph_p2_worker(rank, world, ref_path, port, out_path):
+    """Reference graph-level Graphormer on `world` gloo ranks, dropout 0, batch of 3 graphs: every rank
+    holds s/world nodes of each graph behind its own copy of the graph token (local index 0), the
+    gathered sequence has world * (s/world + 1) rows per graph.  Recorded per rank: its input slice, its
+    output (read from its token row), and its parameter gradients before any all-reduce."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ref_path)
+    install_shims()
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def all_to_all_via_single(output_list, input_list, group=None):
+        out = torch.empty_like(torch.stack(input_list))
+        dist.all_to_all_single(out, torch.stack(input_list).contiguous(), group=group)
+        for o, chunk in zip(output_list, out):
+            o.copy_(chunk)
+    dist.all_to_all = all_to_all_via_single
+    torch.distributed.all_to_all = all_to_all_via_single
+    import gt_sp.initialize as init
+    b, s, feats, classes = 3, 40, 2, 5
+    L = s // world
+    rows = world * (L + 1)                       # rows per graph in the gathered sequence
+    init._GLOBAL_TOKEN_NUM = 1
+    init.initialize_sequence_parallel(s, 1, 1, world)
+    init.set_global_token_indices(list(range(0, rows, L + 1)))
+    from models.graphormer_dist_graph_level import Graphormer
+    torch.manual_seed(51)
+    model = Graphormer(2, 8, 64, 0.0, 0.0, 64, "ZINC", "multi_hop", 5, 0.0, classes)
+    with torch.no_grad():
+        for p_ in model.parameters():
+            p_.mul_(8.0)
+    gen = torch.Generator().manual_seed(52)
+    x = torch.randint(0, 64, (b, s, feats), generator=gen)
+    in_deg = torch.randint(0, 64, (b, s), generator=gen)
+    out_deg = torch.randint(0, 64, (b, s), generator=gen)
+    y = torch.randint(0, classes, (b,), generator=gen)
+    per_graph = []
+    for g in range(b):
+        e = torch.cat([torch.randint(0, rows, (2, 4 * rows), generator=gen), torch.arange(rows).repeat(2, 1)], dim=1)
+        per_graph.append(e + g * rows)
+    ei = torch.cat(per_graph, dim=1)
+    sl = slice(rank * L, (rank + 1) * L)
+    batch = _Batch(x[:, sl].contiguous(), ei)
+    batch.in_degree, batch.out_degree = in_deg[:, sl].contiguous(), out_deg[:, sl].contiguous()
+    model.train()
+    out = model(batch, attn_type="sparse")
+    loss = torch.nn.functional.cross_entropy(out, y)
+    loss.backward()
+    rec = {"out": out.detach().numpy(), "loss": np.float64(loss.item())}
+    for name, p_ in model.named_parameters():
+        if p_.grad is not None:
+            rec["grad/" + name] = p_.grad.numpy()
+    gathered = [None] * world
+    dist.all_gather_object(gathered, rec)
+    if rank == 0:
+        flat = {f"r{r}/{name}": val for r, g in enumerate(gathered) for name, val in g.items()}
+        flat.update({"x": x.numpy(), "in_degree": in_deg.numpy(), "out_degree": out_deg.numpy(), "y": y.numpy(),
+                     "edge_index": ei.numpy(), "world": np.int64(world)})
+        for name, p_ in model.state_dict().items():
+            flat["param/" + name] = p_.numpy()
+        np.savez_compressed(out_path, **flat)
+        print("wrote", out_path, "losses", [float(g["loss"]) for g in gathered])
+    dist.destroy_process_group()
+
+
 def make_gt_cases(ref_path):
     import torch.multiprocessing as mp
     mp.spawn(_gt_node_worker, args=(1, ref_path, 29641, str(OUT_DIR / "gt_node_level.npz")), nprocs=1, join=True)
     mp.spawn(_gt_graph_worker, args=(2, ref_path, 29642, str(OUT_DIR / "gt_graph_level.npz")), nprocs=2, join=True)
     mp.spawn(_graphormer_graph_worker, args=(1, ref_path, 29643, str(OUT_DIR / "graphormer_graph_level.npz")),
              nprocs=1, join=True)
+    mp.spawn(_graphormer_graph_p2_worker, args=(2, ref_path, 29644, str(OUT_DIR / "graphormer_graph_level_P2.npz")),
+             nprocs=2, join=True)
 
 
 def main():

@@ -139,3 +139,63 @@ def test_gt_graph_level_model_on_two_gpus_matches_the_reference_on_two_ranks():
         mp.spawn(_gt_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
         for rank in range(2):
             assert ret[rank]["out"] < 1e-4 and ret[rank]["grads"] < 1e-4, (rank, dict(ret[rank]))
+
+
+def _graphormer_graph_worker(rank, world, port, ret):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TGT_P2P_SPIN_LIMIT="4000000")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import torchgt_b200.gt_sp.initialize as init
+        from torchgt_b200.graphormer import GraphormerGraphLevel
+        with np.load(GOLDEN / "graphormer_graph_level_P2.npz") as z:
+            g = {k: z[k] for k in z.files}
+        s_len = g["x"].shape[1]
+        L = s_len // world
+        init.set_global_token_num(1)
+        init.initialize_sequence_parallel(s_len, 1, 1, world)
+        init.set_global_token_indices(list(range(0, world * (L + 1), L + 1)))
+        model = GraphormerGraphLevel(2, 8, 64, 0.0, 0.0, 64, "ZINC", "multi_hop", 5, 0.0, 5)
+        model.load_state_dict({k[len("param/"):]: torch.from_numpy(v) for k, v in g.items() if k.startswith("param/")},
+                              strict=True)
+        model = model.to(dev).train()
+        sl = slice(rank * L, (rank + 1) * L)
+        batch = _Batch(torch.from_numpy(g["x"][:, sl]).contiguous().to(dev), torch.from_numpy(g["edge_index"]).to(dev))
+        batch.in_degree = torch.from_numpy(g["in_degree"][:, sl]).contiguous().to(dev)
+        batch.out_degree = torch.from_numpy(g["out_degree"][:, sl]).contiguous().to(dev)
+        out = model(batch, attn_type="sparse")
+        loss = torch.nn.functional.cross_entropy(out, torch.from_numpy(g["y"]).to(dev))
+        loss.backward()
+        ref = torch.from_numpy(g[f"r{rank}/out"]).to(dev)
+        errs = {"out": float((out.detach() - ref).abs().max() / ref.abs().max())}
+        worst, checked = 0.0, 0
+        for name, p in model.named_parameters():
+            key = f"r{rank}/grad/{name}"
+            if key not in g or float(np.abs(g[key]).max()) < 1e-7:
+                continue
+            gref = torch.from_numpy(g[key]).to(dev)
+            worst = max(worst, float((p.grad - gref).abs().max() / gref.abs().max()))
+            checked += 1
+        errs["grads"], errs["checked"] = worst, checked
+        torch.cuda.synchronize()
+        ret[rank] = errs
+    finally:
+        dist.destroy_process_group()
+
+
+def test_graphormer_graph_level_model_on_two_gpus_matches_the_reference_rank_by_rank():
+    """Batch of three graphs, every rank's own graph token in front of its slice: exercises the exchange and
+    the global-token copy with a batch dimension."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as manager:
+        ret = manager.dict()
+        mp.spawn(_graphormer_graph_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+        for rank in range(2):
+            errs = dict(ret[rank])
+            assert errs["out"] < 1e-4 and errs["grads"] < 1e-4 and errs["checked"] >= 35, (rank, errs)
