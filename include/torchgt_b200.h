@@ -121,7 +121,7 @@ TGT_API int tgt_sparse_attn_scratch_bytes(const tgt_layout* by_dst, const tgt_la
  * the two torch_scatter.scatter(reduce='add') calls.  No per-edge tensor is materialised.
  * q, k, v, out: device [n_rows, heads, head_dim] of `dtype`; z: device fp32 [n_rows, heads]
  * (saved for backward); bias: device fp32 in ORIGINAL edge order or NULL (see bias_heads).
- * Rows without in-edges produce exactly 0.  Deterministic (no atomics).
+ * Rows without in-edges produce exactly 0.  Deterministic (every floating-point sum has a fixed order).
  */
 TGT_API int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, const float* bias,
                         int bias_heads, const tgt_layout* by_dst, void* out, float* z, int heads,
@@ -160,7 +160,7 @@ TGT_API int tgt_sparse_attn_fwd_noalloc(const void* q, const void* k, const void
  *   da = dt * [-5 <= raw <= 5];  dQ_d += da * K_s / sqrt(D);  dK_s += da * Q_d / sqrt(D)
  * Pass A walks by_dst (dQ, dbias, per-row statistics), pass B walks by_src (dK, dV); scores are
  * recomputed, nothing per-edge is read from forward.  dbias is device fp32 in ORIGINAL edge order
- * with the shape bias has, or NULL when not wanted.  Deterministic (no atomics).
+ * with the shape bias has, or NULL when not wanted.  Deterministic (every floating-point sum has a fixed order).
  */
 TGT_API int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
                         const float* bias, int bias_heads, const void* out, const float* z,

@@ -1,4 +1,4 @@
-// Backward of the sparse graph attention: two atomics-free passes that recompute the scores.
+// Backward of the sparse graph attention: two passes without floating-point atomics that recompute the scores.
 //   pass A: edges sorted by destination -> dQ, and the row statistics
 //           stats[d,h] = { inv_d = 1/(Z+1e-6), delta_d = dO_d . O_d } that pass B reads
 //   pass B: edges sorted by source      -> dK and dV

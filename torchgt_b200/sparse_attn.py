@@ -5,7 +5,7 @@
     w_e = exp(clamp(K[s,h] . Q[d,h] / sqrt(D), -5, 5) + bias_e),   out[d,h] = sum_e w_e V[s,h] / (sum_e w_e + 1e-6)
 
 which is CoreAttention.sparse_attention of the reference (attn_module.py:133-189) without its
-per-edge temporaries, and its gradient in two atomics-free passes.
+per-edge temporaries, and its gradient in two passes without floating-point atomics.
 """
 from __future__ import annotations
 
