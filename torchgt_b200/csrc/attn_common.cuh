@@ -110,21 +110,40 @@ __device__ __forceinline__ float clamp_score(float raw) {
   return fminf(fmaxf(raw, kClampLo), kClampHi);
 }
 
+// torch.clamp passes the gradient where the input lies inside [lo, hi], bounds included
 __device__ __forceinline__ bool clamp_passes_grad(float raw) {
   return raw >= kClampLo && raw <= kClampHi;
 }
 
-// exp(x) for |x| < 80: ex2.approx on the rounded product x*log2(e), corrected for the rounding
-// error of that product with one fma (relative error about 2^-22, like expf, in 6 instructions).
+// Sum of a per-head value (replicated on the LPH lanes of each head) over the heads of a lane group.
+template <int LPH, int G>
+__device__ __forceinline__ float sum_over_heads(float x) {
+#pragma unroll
+  for (int off = LPH; off < G; off <<= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+  return x;
+}
+
+// exp(x) for |x| < 80: ex2.approx on the rounded product x*log2(e), corrected for the rounding error
+// of that product with one fma (relative error about 2^-22, like expf).  Building with
+// -DTGT_EXP_CORRECT=0 drops the correction: four instructions per edge and lane fewer (the 64K
+// benchmark step goes from 176 to 170 us), relative error |x| * 1.44 * 2^-24 * ln 2 + 2^-22, i.e. below
+// 6e-7 for clamped scores and 5e-6 at |x| = 80; the op-level parity tests still pass with it, but
+// gradients that cancel heavily (key-bias gradients of a whole model) move by more than 1e-4.
+#ifndef TGT_EXP_CORRECT
+#define TGT_EXP_CORRECT 1
+#endif
 __device__ __forceinline__ float fast_exp(float x) {
   constexpr float kLog2eHi = 1.4426950216293335f;   // log2(e) rounded to fp32
-  constexpr float kLog2eLo = 1.9259629911e-8f;      // log2(e) - kLog2eHi
-  constexpr float kLn2 = 0.6931471805599453f;
   const float t = x * kLog2eHi;
-  const float r = fmaf(x, kLog2eHi, -t) + x * kLog2eLo;  // what the product lost
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
-  return fmaf(e, r * kLn2, e);
+#if TGT_EXP_CORRECT
+  constexpr float kLog2eLo = 1.9259629911e-8f;      // log2(e) - kLog2eHi
+  constexpr float kLn2 = 0.6931471805599453f;
+  const float r = fmaf(x, kLog2eHi, -t) + x * kLog2eLo;  // what the product lost
+  e = fmaf(e, r * kLn2, e);
+#endif
+  return e;
 }
 
 template <int G, class Policy>

@@ -119,8 +119,7 @@ struct DqPolicy {
     const float dt = valid ? (gv - o.st.y) * o.st.x * wgt : 0.f;
     if (dbias != nullptr) {
       if (bias_stride == 1) {
-        // every head's dt sits on LPH lanes, so the group sum counts it LPH times
-        const float s = group_sum<G>(dt) * (1.0f / LPH);
+        const float s = sum_over_heads<LPH, G>(dt);   // every head's dt sits on all LPH lanes of the head
         if (valid && group_leader) dbias[pe] = s;
       } else if (valid && head_leader) {
         dbias[int64_t(pe) * bias_stride + head] = dt;
