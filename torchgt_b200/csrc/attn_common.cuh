@@ -31,6 +31,13 @@ namespace tgt {
 #ifndef TGT_UNROLL
 #define TGT_UNROLL 4
 #endif
+// Lane groups up to this width finish the rows that cross tiles in a second kernel; wider ones do it
+// inside the walk kernel (the last tile to arrive).  Narrow groups have many small tiles (a thread
+// walks 32 edges at G = 2), where the fence and the arrival count of every CTA cost more than one
+// extra launch.
+#ifndef TGT_STITCH_KERNEL_MAX_G
+#define TGT_STITCH_KERNEL_MAX_G 4
+#endif
 #ifdef TGT_MIN_CTAS
 #define TGT_WALK_BOUNDS __launch_bounds__(128, TGT_MIN_CTAS)
 #else
@@ -59,7 +66,7 @@ struct SegWalk {
   int n_tiles;
   float* gcarry;   // [n_tiles][2][gridDim.y * G * NACC] cross-tile partial sums
   int* tile_done;  // [gridDim.y][n_tiles] arrivals per row that crosses tiles, indexed by the tile it
-                   // starts in; zero when the kernel starts
+                   // starts in; zero when the kernel starts.  Null: a second kernel finishes those rows
   bool need_perm;  // stage perm[] (bias or dbias in original edge order)
 };
 
@@ -318,7 +325,7 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
   // ---- rows that cross tile boundaries: every tile such a row touches has written one partial
   // (the tile it starts in a tail carry, the others a head carry) and now counts itself in; the
   // tile that arrives last finishes the row.  A tile touches at most two such rows.
-  if (w.n_tiles == 1) return;
+  if (w.n_tiles == 1 || w.tile_done == nullptr) return;
   __threadfence();   // this thread's carries are visible device-wide before the arrival is counted
   __syncthreads();
   if (tid == 0) {
@@ -391,6 +398,22 @@ __device__ __forceinline__ void finish_row(const SegWalk& w, const Policy& pol, 
     pol.finalize(r, acc);
   }
 }
+
+// Second kernel for narrow lane groups: one CTA per tile; the CTA of the tile in which a row that runs
+// past the tile's end STARTS finishes that row.
+template <int G, class Policy>
+__device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol, float* s_part) {
+  const int tile = blockIdx.x;
+  const int te = TileGeom<G>::NG * w.ge;
+  const int64_t t1 = int64_t(tile + 1) * te;
+  if (t1 >= w.n_edges) return;                       // last tile: nothing runs past it
+  const int r = __ldg(w.seg + t1 - 1);
+  if (__ldg(w.seg + t1) != r) return;                // the tile ends on a row boundary
+  if (__ldg(w.ptr + r) < t1 - te) return;            // the row started in an earlier tile
+  finish_row<G, Policy>(w, pol, s_part, tile);
+}
+
+inline bool stitch_in_second_kernel(int g) { return g <= TGT_STITCH_KERNEL_MAX_G; }
 
 struct HeadSplit {
   int lph;     // lanes per head

@@ -423,6 +423,30 @@ __global__ void TGT_WALK_BOUNDS bwd_dkv_kernel(const BwdParams p) {
   walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
+template <typename T, int LPH, int G>
+__global__ void __launch_bounds__(kBlockThreads) bwd_dq_fused_stitch_kernel(const BwdParams p) {
+  using Policy = DqFusedPolicy<T, LPH, G>;
+  const Policy pol = make_dq_fused_policy<T, LPH, G>(p);
+  __shared__ float s_part[kBlockThreads * Policy::NACC];
+  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+}
+
+template <typename T, int LPH, int G>
+__global__ void __launch_bounds__(kBlockThreads) bwd_dq_stitch_kernel(const BwdParams p) {
+  using Policy = DqPolicy<T, LPH, G>;
+  const Policy pol = make_dq_policy<T, LPH, G>(p);
+  __shared__ float s_part[kBlockThreads * Policy::NACC];
+  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+}
+
+template <typename T, int LPH, int G>
+__global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const BwdParams p) {
+  using Policy = DkvPolicy<T, LPH, G>;
+  const Policy pol = make_dkv_policy<T, LPH, G>(p);
+  __shared__ float s_part[kBlockThreads * Policy::NACC];
+  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+}
+
 enum { kWalkDq = 0, kWalkDkv = 1, kWalkDqFused = 2 };
 
 int bwd_resident_ctas(int dtype, const HeadSplit& hs, int which) {
@@ -594,22 +618,36 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
     TGT_DISPATCH(dtype, hs.lph, hs.lph, TGT_LAUNCH_STATS);
 #undef TGT_LAUNCH_STATS
   }
-  int* counters_a = reinterpret_cast<int*>(base + sc.counters);
-  int* counters_b = reinterpret_cast<int*>(base + sc.counters + sc.counter_bytes - sc.plan_b.counter_bytes);
-  if (passes & 6) TGT_CHECK_CUDA(cudaMemsetAsync(counters_a, 0, sc.counter_bytes, stream));
+  const bool second_kernel = stitch_in_second_kernel(hs.g);
+  int* counters_a = second_kernel ? nullptr : reinterpret_cast<int*>(base + sc.counters);
+  int* counters_b = second_kernel ? nullptr
+                                  : reinterpret_cast<int*>(base + sc.counters + sc.counter_bytes -
+                                                           sc.plan_b.counter_bytes);
+  if ((passes & 6) && !second_kernel)
+    TGT_CHECK_CUDA(cudaMemsetAsync(counters_a, 0, sc.counter_bytes, stream));
   if ((passes & 2) && dbias == nullptr) {
     // pass A that derives the row statistics itself (and leaves them in scratch for pass B)
     fill_walk(&p.walk, *by_dst, sc.plan_a_fused, reinterpret_cast<float*>(base + sc.carry_a), counters_a,
               bias != nullptr);
     const dim3 grid(sc.plan_a_fused.n_tiles, hs.groups);
-#define TGT_LAUNCH_DQF(T, LPH, G) bwd_dq_fused_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
+#define TGT_LAUNCH_DQF(T, LPH, G)                                                   \
+  do {                                                                              \
+    bwd_dq_fused_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
+    if (second_kernel && sc.plan_a_fused.n_tiles > 1)                               \
+      bwd_dq_fused_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
+  } while (0)
     TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQF);
 #undef TGT_LAUNCH_DQF
   } else if (passes & 2) {
     // pass A with per-edge dbias: uses the statistics of the pre-pass (stage 1)
     fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a), counters_a, true);
     const dim3 grid(sc.plan_a.n_tiles, hs.groups);
-#define TGT_LAUNCH_DQ(T, LPH, G) bwd_dq_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
+#define TGT_LAUNCH_DQ(T, LPH, G)                                              \
+  do {                                                                        \
+    bwd_dq_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
+    if (second_kernel && sc.plan_a.n_tiles > 1)                               \
+      bwd_dq_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
+  } while (0)
     TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQ);
 #undef TGT_LAUNCH_DQ
   }
@@ -617,7 +655,12 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
     fill_walk(&p.walk, *by_src, sc.plan_b, reinterpret_cast<float*>(base + sc.carry_b), counters_b,
               bias != nullptr);
     const dim3 grid(sc.plan_b.n_tiles, hs.groups);
-#define TGT_LAUNCH_DKV(T, LPH, G) bwd_dkv_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
+#define TGT_LAUNCH_DKV(T, LPH, G)                                              \
+  do {                                                                         \
+    bwd_dkv_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
+    if (second_kernel && sc.plan_b.n_tiles > 1)                                \
+      bwd_dkv_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
+  } while (0)
     TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DKV);
 #undef TGT_LAUNCH_DKV
   }

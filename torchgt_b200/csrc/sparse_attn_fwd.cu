@@ -120,6 +120,14 @@ __global__ void TGT_WALK_BOUNDS fwd_kernel(const FwdParams p) {
   walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
+template <typename T, int LPH, int G>
+__global__ void __launch_bounds__(kBlockThreads) fwd_stitch_kernel(const FwdParams p) {
+  using Policy = FwdPolicy<T, LPH, G>;
+  const Policy pol = make_policy<T, LPH, G>(p);
+  __shared__ float s_part[kBlockThreads * Policy::NACC];
+  stitch_tiles<G, Policy>(p.walk, pol, s_part);
+}
+
 // Resident CTAs per SM of fwd_kernel<T, LPH, G> for the run-time triple.
 int fwd_resident_ctas(int dtype, const HeadSplit& hs) {
   static int cache[2][6][6] = {};
@@ -203,12 +211,19 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   p.walk.n_rows = int(L.n_rows); p.walk.n_edges = int(L.n_edges);
   p.walk.ge = tp.ge; p.walk.n_tiles = tp.n_tiles;
   p.walk.gcarry = static_cast<float*>(scratch);
-  p.walk.tile_done = reinterpret_cast<int*>(static_cast<char*>(scratch) + tp.carry_bytes);
+  const bool second_kernel = stitch_in_second_kernel(hs.g);
+  p.walk.tile_done = second_kernel ? nullptr : reinterpret_cast<int*>(static_cast<char*>(scratch) + tp.carry_bytes);
   p.walk.need_perm = bias != nullptr;
-  if (tp.n_tiles > 1) TGT_CHECK_CUDA(cudaMemsetAsync(p.walk.tile_done, 0, tp.counter_bytes, stream));
+  if (tp.n_tiles > 1 && !second_kernel)
+    TGT_CHECK_CUDA(cudaMemsetAsync(p.walk.tile_done, 0, tp.counter_bytes, stream));
 
   const dim3 grid(tp.n_tiles, hs.groups);
-#define TGT_LAUNCH_FWD(T, LPH, G) fwd_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p)
+#define TGT_LAUNCH_FWD(T, LPH, G)                                          \
+  do {                                                                     \
+    fwd_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
+    if (second_kernel && tp.n_tiles > 1)                                   \
+      fwd_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
+  } while (0)
   TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_FWD);
 #undef TGT_LAUNCH_FWD
   TGT_CHECK_CUDA(cudaGetLastError());
