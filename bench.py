@@ -386,11 +386,11 @@ def capture(fn):
     return g
 
 
-def kernels_per_step(graph, with_dbias=True, ranks=1):
+def kernels_per_step(graph, with_dbias=True, ranks=1, elem=4):
     # forward, dQ pass, dK/dV pass: one kernel each, plus a second small kernel each where rows are at most
     # 64 bytes wide (there the rows that cross tiles are finished separately); the row-statistics pre-pass
     # runs only when dbias is computed
-    row_bytes = HEADS // max(1, ranks) * HEAD_DIM * 4   # the fp32 default; bf16 rows are half as wide
+    row_bytes = HEADS // max(1, ranks) * HEAD_DIM * elem
     return 3 * (2 if row_bytes <= 64 else 1) + (1 if with_dbias else 0)
 
 
@@ -554,7 +554,7 @@ def run_single_gpu(args, dtype):
                 "one_step_at_a_time_ms": results["full"] * 1e3,
                 "graph_resident_value": n_edges / results["graph_resident"],
                 "graph_resident_ms_per_step": results["graph_resident"] * 1e3},
-        "gpu_launches": kernels_per_step(graph) * args.steps,
+        "gpu_launches": kernels_per_step(graph, elem=elem) * args.steps,
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                      "traffic": NCU_TRAFFIC_BYTES.get(dominant) if (dtype == torch.float32 and args.workload == "64k") else None,
@@ -721,7 +721,7 @@ def run_multi_gpu(args, dtype, rank, world):
         step_bytes = sum(bytes_.values())
         per_rank_io = 4 * (L + 1) * HEADS * HEAD_DIM * elem
         # kernels: the attention phases and, per exchange, push + barrier + fetch (or pack + unpack + NCCL)
-        launches = kernels_per_step(graph, with_dbias=False, ranks=world) + 4 * 3
+        launches = kernels_per_step(graph, with_dbias=False, ranks=world, elem=elem) + 4 * 3
         line = {
             "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": n_edges / (ms_per_step * 1e-3),
             "unit": "edges/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
