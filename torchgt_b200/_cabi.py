@@ -11,6 +11,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtorchgt_b200.so"
 
 TGT_OK = 0
+TGT_ERR_INDEX_RANGE = 5
 TGT_F32 = 0
 TGT_BF16 = 1
 

@@ -80,7 +80,7 @@ class SparseGraph:
         """Raise if a deferred build saw a node id outside [0, n_rows) (synchronises)."""
         for lay in (self.by_dst, self._by_src):
             if lay is not None and lay.bad_index is not None and int(lay.bad_index.item()) != 0:
-                raise _cabi.TgtError(5, f"edge_index holds a node id outside [0, {self.n_rows})")
+                raise _cabi.TgtError(_cabi.TGT_ERR_INDEX_RANGE, f"edge_index holds a node id outside [0, {self.n_rows})")
 
 
 # ---- cache: the reference passes a raw edge_index tensor to every layer ---------------------------
