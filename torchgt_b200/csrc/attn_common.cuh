@@ -46,6 +46,17 @@ namespace tgt {
 
 constexpr int kBlockThreads = 128;
 constexpr int kUnroll = TGT_UNROLL;  // edges per lane group whose gathers are in flight together
+constexpr int kGeStep = 4;           // ge is a multiple of this (and of every batch size below)
+
+// Batch size of the walk for element type T and lane-group width G.  Measured on B200 (fp32, 8-byte to
+// 256-byte rows; bf16 128-byte rows): batches of 4 edges are best everywhere except for fp32 rows of
+// 16 lanes (the 8 heads x 8 case, two lane groups per warp), where batches of 2 are 9-10 % faster
+// (64K benchmark step 176 -> 158 us, 870K step 5.11 -> 4.67 ms); narrower groups lose 20-70 % with 2.
+template <typename T, int G>
+constexpr int walk_unroll() {
+  return (std::is_same<T, float>::value && G == 16 && TGT_UNROLL == 4) ? 2 : TGT_UNROLL;
+}
+static_assert(kGeStep % TGT_UNROLL == 0, "ge must stay a multiple of the batch size");
 
 template <int G>
 struct TileGeom {
@@ -62,7 +73,7 @@ struct SegWalk {
   const int32_t* seg;
   int n_rows;
   int n_edges;
-  int ge;          // edges per lane group per tile (multiple of kUnroll, <= GE_MAX)
+  int ge;          // edges per lane group per tile (multiple of kGeStep, <= GE_MAX)
   int n_tiles;
   float* gcarry;   // [n_tiles][2][gridDim.y * G * NACC] cross-tile partial sums
   int* tile_done;  // [gridDim.y][n_tiles] arrivals per row that crosses tiles, indexed by the tile it
@@ -84,7 +95,7 @@ inline int choose_ge(int64_t n_edges, int g, int ctas_per_sm) {
   const int ng = kBlockThreads / g;
   const int ge_max = host_ge_max(g);
   if (forced_ge() > 0) {
-    int f = (forced_ge() + kUnroll - 1) / kUnroll * kUnroll;
+    int f = (forced_ge() + kGeStep - 1) / kGeStep * kGeStep;
     return f > ge_max ? ge_max : f;
   }
   // Time is roughly (number of CTA waves) x (work of one tile); a tile costs its ge edges per lane
@@ -93,7 +104,7 @@ inline int choose_ge(int64_t n_edges, int g, int ctas_per_sm) {
   const int64_t capacity = int64_t(kSmCount) * ctas_per_sm;
   int best = ge_max;
   double best_cost = 1e300;
-  for (int ge = (ge_max < 16 ? ge_max : 16); ge <= ge_max; ge += kUnroll) {
+  for (int ge = (ge_max < 16 ? ge_max : 16); ge <= ge_max; ge += kGeStep) {
     const int64_t tiles = (n_edges + int64_t(ng) * ge - 1) / (int64_t(ng) * ge);
     const int64_t waves = (tiles + capacity - 1) / capacity;
     const double cost = double(waves) * (ge + 8);
@@ -158,6 +169,7 @@ __device__ __forceinline__ void finish_row(const SegWalk& w, const Policy& pol, 
 
 // The walk.  Policy supplies:
 //   static constexpr int NACC;                     accumulators per lane
+//   static constexpr int kUnroll;                  edges per batch (walk_unroll<T, G>())
 //   struct Operands;                               what one edge loads
 //   void load(Operands&, int row, int other, int perm_e) const;      issue the gathers of one edge
 //   void clear(Operands&) const;                                     operands of a padding slot
@@ -171,6 +183,7 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
                                           int32_t* s_carry_row, float* s_part, int32_t* s_finish) {
   constexpr int NG = TileGeom<G>::NG;
   constexpr int NACC = Policy::NACC;
+  constexpr int kUnroll = Policy::kUnroll;   // edges per batch (shadows the default)
   const int tid = threadIdx.x;
   const int g = tid / G;        // lane group inside the CTA
   const int c = tid % G;        // 16-byte column inside the group
@@ -255,7 +268,7 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
     }
   };
   if (n == te) {
-    // ge is a multiple of kUnroll, so every batch of every group is full
+    // ge is a multiple of the batch size, so every batch of every group is full
     for (int first = gb; first < gend; first += kUnroll) batch(first, std::true_type{});
   } else {
     // last tile: all groups of a warp run the same number of batches (the shuffles inside need

@@ -67,6 +67,7 @@ template <typename T, int LPH, int G>
 struct DqPolicy {
   static constexpr int VEC = Vec16<T>::kElems;
   static constexpr int NACC = VEC;
+  static constexpr int kUnroll = walk_unroll<T, G>();
 
   const T* __restrict__ q;
   const T* __restrict__ k;
@@ -155,6 +156,7 @@ template <typename T, int LPH, int G>
 struct DqFusedPolicy {
   static constexpr int VEC = Vec16<T>::kElems;
   static constexpr int NACC = 2 * VEC + 1;  // A1, A2, S
+  static constexpr int kUnroll = walk_unroll<T, G>();
 
   const T* __restrict__ q;
   const T* __restrict__ k;
@@ -240,6 +242,7 @@ template <typename T, int LPH, int G>
 struct DkvPolicy {
   static constexpr int VEC = Vec16<T>::kElems;
   static constexpr int NACC = 2 * VEC;  // dK then dV
+  static constexpr int kUnroll = walk_unroll<T, G>();
 
   const T* __restrict__ q;
   const T* __restrict__ k;

@@ -10,6 +10,7 @@ template <typename T, int LPH, int G>
 struct FwdPolicy {
   static constexpr int VEC = Vec16<T>::kElems;
   static constexpr int NACC = VEC + 1;  // w*V and, last, the sum of w
+  static constexpr int kUnroll = walk_unroll<T, G>();
 
   const T* __restrict__ q;
   const T* __restrict__ k;
