@@ -42,7 +42,7 @@ ROTATING_SETS = 4
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
 # summarised in profiles/sparse_attn_64k_fp32_kernels.md (fp32 workload; the dQ phase includes the
 # row-statistics kernel).
-NCU_TRAFFIC_BYTES = {"fwd_kernel": 63.4e6, "bwd_dq_kernel": 88.8e6 + 34.8e6, "bwd_dkv_kernel": 99.3e6}
+NCU_TRAFFIC_BYTES = {"fwd_kernel": 62.7e6, "bwd_dq_kernel": 89.8e6 + 34.8e6, "bwd_dkv_kernel": 101.1e6}
 
 
 def measured_hbm_peak():
