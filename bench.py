@@ -398,11 +398,21 @@ def run_single_gpu(args, dtype):
     from torchgt_b200 import SparseGraph, sparse_graph_attention
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    edge_index, n_rows = load_workload(args.workload)
+    if args.profile and args.slice_of > 1:
+        # the head slice one rank of an N-rank sequence-parallel run sees: N x 64,000 nodes, 8 / N heads
+        global HEADS
+        from torchgt_b200.gt_sp.utils import adjust_edge_index_nomerge
+        edge_index, _ = load_workload("64k", ranks=args.slice_of)
+        edge_index = adjust_edge_index_nomerge(edge_index, NODES_PER_RANK)
+        n_rows = args.slice_of * (NODES_PER_RANK + 1)
+        HEADS = HEADS // args.slice_of
+    else:
+        edge_index, n_rows = load_workload(args.workload)
     n_edges = edge_index.shape[1]
     graph = SparseGraph(edge_index.to(dev), n_rows)
     graph.by_src  # build both layouts before timing
-    sets = [OpBuffers(graph, dtype, 1234 + i) for i in range(ROTATING_SETS)]
+    sets = [OpBuffers(graph, dtype, 1234 + i, with_bias=not (args.profile and args.no_bias))
+            for i in range(ROTATING_SETS)]
     if args.profile:
         # plain launches of a few steps for ncu (no CUDA graph, no end-to-end or CPU legs)
         stream = torch.cuda.current_stream().cuda_stream
@@ -410,8 +420,8 @@ def run_single_gpu(args, dtype):
             sets[i % ROTATING_SETS].fwd(stream)
             sets[i % ROTATING_SETS].bwd(stream, 7 if sets[i % ROTATING_SETS].dbias is not None else 6)
         torch.cuda.synchronize()
-        print(json.dumps({"profile_run": True, "steps": args.steps, "warmup": args.warmup,
-                          "kernels_per_step": kernels_per_step(graph)}), flush=True)
+        print(json.dumps({"profile_run": True, "steps": args.steps, "warmup": args.warmup, "rows": n_rows,
+                          "edges": n_edges, "heads": HEADS, "bias": not args.no_bias}), flush=True)
         return
     step_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 7 if b.dbias is not None else 6))) for b in sets]
     phase_graphs = [[capture(lambda s, b=b: b.fwd(s)), capture(lambda s, b=b: b.bwd(s, 3 if b.dbias is not None else 2)),
@@ -769,6 +779,9 @@ def main():
                     help="N=1 only: 64k (default, the headline) or 870k (long-sequence batch)")
     ap.add_argument("--profile", action="store_true",
                     help="N=1 only: launch warmup+steps plain forward+backward steps and exit (for ncu)")
+    ap.add_argument("--slice-of", type=int, default=1, choices=[1, 2, 4, 8],
+                    help="with --profile: run the head slice one rank of an N-rank run sees (N x 64,000 nodes, 8/N heads)")
+    ap.add_argument("--no-bias", action="store_true", help="with --profile: no edge bias (the layer's own call form)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

@@ -13,7 +13,7 @@ worker processes ``torch.distributed.all_to_all`` is routed through ``all_to_all
 Outputs (all small .npz files, committed):
   attn_*.npz     CoreAttention.sparse_attention_bias forward + autograd gradients
   edges.npz      fix_edge_index / adjust_edge_index_nomerge / flatten_edge_index_nopad known answers
-  ulysses_P*.npz _SeqAllToAll both directions and the DistributedAttentionNoMerge layer, P ranks
+  ulysses_P*.npz _SeqAllToAll both directions and the DistributedAttentionNoMerge layer, P = 2, 4, 8 ranks
   layer_variants_P*.npz  the four Ulysses layer variants no reference model instantiates (global tokens
                  merged by mean), around a toy local attention: outputs and gradients, P ranks
   graphormer_node_level.npz  the reference's node-level Graphormer: parameters, log-probabilities, loss and
@@ -276,10 +276,10 @@ def _variants_worker(rank, world, ref_path, port, out_path):
     dist.destroy_process_group()
 
 
-def make_variant_cases(ref_path):
+def make_variant_cases(ref_path, worlds=(2, 4, 8)):
     import torch.multiprocessing as mp
-    for i, world in enumerate((2, 4)):
-        mp.spawn(_variants_worker, args=(world, ref_path, 29631 + i, str(OUT_DIR / f"layer_variants_P{world}.npz")),
+    for world in worlds:
+        mp.spawn(_variants_worker, args=(world, ref_path, 29631 + world, str(OUT_DIR / f"layer_variants_P{world}.npz")),
                  nprocs=world, join=True)
 
 
@@ -337,10 +337,10 @@ def make_model_case(ref_path):
     mp.spawn(_model_worker, args=(1, ref_path, 29621, str(OUT_DIR / "graphormer_node_level.npz")), nprocs=1, join=True)
 
 
-def make_ulysses_cases(ref_path):
+def make_ulysses_cases(ref_path, worlds=(2, 4, 8)):
     import torch.multiprocessing as mp
-    for i, world in enumerate((2, 4)):
-        mp.spawn(_ulysses_worker, args=(world, ref_path, 29611 + i, str(OUT_DIR / f"ulysses_P{world}.npz")),
+    for world in worlds:
+        mp.spawn(_ulysses_worker, args=(world, ref_path, 29611 + world, str(OUT_DIR / f"ulysses_P{world}.npz")),
                  nprocs=world, join=True)
 
 
@@ -589,13 +589,18 @@ def make_gt_cases(ref_path):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of zxmeng98/torchgt")
-    ap.add_argument("--only", default="", help="'gt' regenerates the GT and graph-level model files only")
+    ap.add_argument("--only", default="", help="'gt' regenerates the GT and graph-level model files only, "
+                                               "'p8' the eight-rank exchange and layer files only")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     install_shims()
     torch.set_num_threads(1)
     if args.only == "gt":
         make_gt_cases(args.reference)
+        return
+    if args.only == "p8":
+        make_ulysses_cases(args.reference, worlds=(8,))
+        make_variant_cases(args.reference, worlds=(8,))
         return
     make_attention_cases()
     make_edge_cases()

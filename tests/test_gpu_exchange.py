@@ -69,7 +69,7 @@ def test_named_entry_points_for_the_two_directions():
     from torchgt_b200 import _cabi
     lib = _cabi.load()
     stream = torch.cuda.current_stream().cuda_stream
-    for world in (2, 4):
+    for world in (2, 4, 8):
         g = load_golden(f"ulysses_P{world}.npz")
         L1, H, D = int(g["L"]) + 1, int(g["H"]), int(g["D"])
         W = (H // world) * D

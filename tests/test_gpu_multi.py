@@ -64,7 +64,7 @@ def _worker(rank, world, port, transport, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("transport", ["p2p", "nccl"])
 def test_nomerge_layer_on_real_gpus(world, transport):
     """transport = p2p: the library's own NVLink peer-memory exchange; nccl: one all_to_all_single."""

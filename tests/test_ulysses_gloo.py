@@ -1,4 +1,4 @@
-"""The Ulysses layers on CPU ranks (gloo, world size 2 and 4): exchange index maps, global-token
+"""The Ulysses layers on CPU ranks (gloo, world size 2, 4 and 8): exchange index maps, global-token
 handling and autograd, against vectors produced by the reference's own layers.  The attention inside
 is the CPU oracle (passed in as ``local_attention``), so these tests cover the multi-rank host logic."""
 import os
@@ -151,13 +151,13 @@ def _run(world, case):
         return {r: dict(ret[r]) for r in range(world)}
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_exchange_maps_and_gather_scatter(world):
     for rank, errs in _run(world, "maps").items():
         assert all(v == 0.0 for v in errs.values()), (rank, errs)
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_nomerge_layer_matches_reference_outputs_and_gradients(world):
     for rank, errs in _run(world, "nomerge").items():
         assert max(errs.values()) < 1e-5, (rank, errs)
@@ -169,7 +169,7 @@ def test_gt_layers_match_single_process_attention(world):
         assert max(errs.values()) < 1e-5, (rank, errs)
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_layer_variants_with_merged_global_tokens_match_the_reference(world):
     """DistributedAttention, ...Global0, ...LocalBias, ...All2all of the reference (no model uses them):
     same outputs and gradients around the same toy local attention, bias paths included."""
