@@ -103,6 +103,37 @@ TGT_API int tgt_edge_layout_build(const int64_t* edge_index, int64_t n_edges, in
                                   int32_t* deferred_status, void* stream);
 
 /*
+ * The same build for an int32 [2, n_edges] device edge list (what tgt_edge_prepare writes): half the
+ * bytes of the reference's int64 list (main_sp_sparse_node_level.py:178-182 uploads int64 every
+ * iteration).  All other arguments and the result are those of tgt_edge_layout_build.
+ */
+TGT_API int tgt_edge_layout_build_i32(const int32_t* edge_index, int64_t n_edges, int64_t n_rows,
+                                      int group_by, int32_t* ptr, int32_t* other, int32_t* perm,
+                                      int32_t* seg, void* workspace, size_t workspace_bytes,
+                                      int32_t* deferred_status, void* stream);
+
+/*
+ * Batch edge construction on the device: the reference's host-side helpers applied in one pass to the
+ * RAW edges of a batch of `graphs` graphs (node ids 0..n_g-1 inside each graph), writing an int32
+ * [2, out_total] edge list for tgt_edge_layout_build_i32.
+ *   add_global_token = 1 : fix_edge_index (gt_sp/utils.py:34-50, data/collator_sp_sparse.py:107-123):
+ *                          ids + 1, then per graph the edges (i -> 0), i = 1..n_g, then (0 -> i);
+ *   sub_seq_len > 0      : adjust_edge_index_nomerge (gt_sp/utils.py:53-58): id x > 0 becomes
+ *                          x + (x - 1) / sub_seq_len (integer division);
+ *   rows_per_graph       : flatten_edge_index_nopad (data/collator_sp_sparse.py:126-133): graph g's ids
+ *                          are offset by g * rows_per_graph (pass 0 for a single graph).
+ * raw_edges: device int64 [2, raw_total], the graphs' raw lists concatenated; raw_ptr: device int64
+ * [graphs + 1] edge range of every graph; node_ptr: device int64 [graphs + 1] prefix sums of the node
+ * counts (only read with add_global_token).  out_total must equal raw_total (+ 2 * total nodes with
+ * add_global_token).  Per graph the output order is [raw | node -> token | token -> node], i.e. the
+ * order the reference's helpers produce, so per-edge biases keep their meaning.
+ */
+TGT_API int tgt_edge_prepare(const int64_t* raw_edges, int64_t raw_total, const int64_t* raw_ptr,
+                             const int64_t* node_ptr, int graphs, int add_global_token,
+                             int64_t sub_seq_len, int64_t rows_per_graph, int32_t* out,
+                             int64_t out_total, void* stream);
+
+/*
  * Bytes of scratch tgt_sparse_attn_fwd (phase 0) / tgt_sparse_attn_bwd (phase 1) need for these
  * layouts (partial sums of rows that cross a tile boundary; row statistics of the backward).
  * by_src may be NULL for phase 0.
@@ -160,7 +191,8 @@ TGT_API int tgt_sparse_attn_fwd_noalloc(const void* q, const void* k, const void
  *   da = dt * [-5 <= raw <= 5];  dQ_d += da * K_s / sqrt(D);  dK_s += da * Q_d / sqrt(D)
  * Pass A walks by_dst (dQ, dbias, per-row statistics), pass B walks by_src (dK, dV); scores are
  * recomputed, nothing per-edge is read from forward.  dbias is device fp32 in ORIGINAL edge order
- * with the shape bias has, or NULL when not wanted.  Deterministic (every floating-point sum has a fixed order).
+ * with the shape bias has, or NULL when not wanted.  `out` (the forward result) is read only when
+ * dbias is wanted and may be NULL otherwise.  Deterministic (every floating-point sum has a fixed order).
  */
 TGT_API int tgt_sparse_attn_bwd(const void* dout, const void* q, const void* k, const void* v,
                         const float* bias, int bias_heads, const void* out, const float* z,
@@ -236,40 +268,56 @@ TGT_API int tgt_global_rows_reduce(void* dx, const int32_t* global_rows, int n_g
 
 /*
  * Ulysses exchange over NVLink peer memory: the same head<->sequence all-to-all as above, done by this
- * library's kernels storing straight into the destination ranks' memory instead of by a collective
+ * library's kernels reading and writing the other ranks' memory directly instead of by a collective
  * library plus pack / unpack passes.  Replaces _SeqAllToAll.forward (gt_sp/layer.py:30-45) and, with
  * alias rows, copy_global_token0 (gt_sp/utils.py:817-838) in the same pass.
  *
- * Every rank owns one peer-visible "landing" area of tgt_p2p_control_bytes() + 2 * half_bytes bytes,
- * zero-filled once before first use; peer_landing[i] is the address of rank i's area AS SEEN FROM
- * THIS GPU (peer mapping), a host array of `world` pointers, world <= 16.  One exchange is
- * tgt_p2p_push -> tgt_p2p_barrier -> tgt_p2p_fetch on one stream, called by every rank in the same
- * order with the same sizes.  The two halves alternate on the device (the barrier advances a counter
- * kept in the area), so the sequence may be replayed from a CUDA graph.
+ * Peer-visible memory is the caller's: every rank owns one zero-filled control block of
+ * tgt_p2p_control_bytes() bytes and any number of "slots".  A peer table is a host array of `world`
+ * pointers (world <= 16), entry i being rank i's block or slot AS SEEN FROM THIS GPU (peer mapping).
+ * All ranks make the same calls in the same order with the same sizes.  A slot may be written again
+ * only after a tgt_p2p_barrier that follows, in stream order on every rank, the last read of its
+ * old content; the barrier counts on the device, so a sequence may be replayed from a CUDA graph.
  *
- * tgt_p2p_push: tensor t is [outer_s][world][width_s_bytes] (what _SeqAllToAll splits along
- * scatter_idx); on every destination it lands as [outer_g][world][width_g_bytes] (what cat along
- * gather_idx produces) with this rank's piece in column block `rank`.  If n_alias > 0, source rows
+ * tgt_p2p_push (sequence -> heads: q, k, v, dO): tensor t is [outer_s][world][width_s_bytes] (what
+ * _SeqAllToAll splits along scatter_idx); on every destination it lands as
+ * [outer_g][world][width_g_bytes] (what cat along gather_idx produces) with this rank's piece in
+ * column block `rank`, tensors back to back in the destination's slot.  If n_alias > 0, source rows
  * (of alias_row_bytes each, counted inside one outer row) listed in the device array alias_rows are
- * read from row 0 instead.  staged = 0 stores every piece at its final position on the destination;
- * staged = 1 stores this rank's whole chunk as one contiguous block and leaves the concatenation to
- * tgt_p2p_fetch (use it when width_g_bytes is small: NVLink stores of less than 128 bytes are slow).
- * tgt_p2p_barrier: all ranks' pushes are complete and visible when the kernel ends.  Waits are
- * bounded: after spin_limit polls it gives up, writes 1 + (rank it waited for) to *status (a
- * host-readable, device-writable int32, e.g. pinned memory) and returns; the context stays usable.
- * tgt_p2p_fetch: copies the n_tensors landed tensors (bytes_per_tensor each) out of the landing
- * half the last barrier completed, into ordinary device tensors; `staged`, `world` and
- * `width_g_bytes` must repeat what the push was given.
+ * read from row 0 instead.  mode:
+ *   TGT_PUSH_FINAL   every piece is stored at its final position on the destination;
+ *   TGT_PUSH_STAGED  this rank's whole chunk is stored as one contiguous block and the concatenation
+ *                    is left to tgt_p2p_fetch (for small width_g_bytes: NVLink stores of less than
+ *                    128 bytes are slow);
+ *   TGT_PUSH_WOVEN   as FINAL, but the n_tensors tensors arrive as ONE tensor whose rows hold the
+ *                    sources' pieces side by side ([.., n_tensors * width_s_bytes]): K and V of a row
+ *                    next to each other, so that one gather serves both.
+ * tgt_p2p_pull (heads -> sequence: attention output, dQ, dK, dV; call it after a barrier): every
+ * peer's slot holds n_tensors tensors [outer][world * rows][width_bytes] back to back; this rank
+ * reads its rows from all of them, y_t[o][l][r * width_bytes + c] = slot_r_t[o][rank * rows + l][c],
+ * into ordinary device tensors.  Source rows listed in alias_rows are read from row 0 of the same o.
+ * tgt_p2p_barrier: everything every rank enqueued before it is complete and visible when the kernel
+ * ends.  Waits are bounded: after spin_limit polls it gives up, writes 1 + (rank it waited for) to
+ * *status (a host-readable, device-writable int32, e.g. pinned memory) and returns; the context
+ * stays usable, the data of that step is not.
+ * tgt_p2p_fetch: copies n_tensors landed tensors (bytes_per_tensor each) out of this rank's slot into
+ * ordinary device tensors; `staged`, `world` and `width_g_bytes` must repeat what the push was given.
  */
+#define TGT_PUSH_FINAL 0
+#define TGT_PUSH_STAGED 1
+#define TGT_PUSH_WOVEN 2
 TGT_API size_t tgt_p2p_control_bytes(void);
 TGT_API int tgt_p2p_push(const void* x0, const void* x1, const void* x2, int n_tensors,
-                         void* const* peer_landing, size_t half_bytes, int64_t outer_s,
+                         void* const* peer_slots, size_t slot_bytes, int64_t outer_s,
                          int64_t width_s_bytes, int64_t width_g_bytes, int world, int rank,
                          const int32_t* alias_rows, int n_alias, int64_t alias_row_bytes,
-                         int staged, void* stream);
-TGT_API int tgt_p2p_barrier(void* const* peer_landing, int world, int rank, uint32_t spin_limit,
+                         int mode, void* stream);
+TGT_API int tgt_p2p_pull(void* const* peer_slots, size_t slot_bytes, int n_tensors, void* y0,
+                         void* y1, void* y2, int64_t outer, int64_t rows, int64_t width_bytes,
+                         int world, int rank, const int32_t* alias_rows, int n_alias, void* stream);
+TGT_API int tgt_p2p_barrier(void* const* peer_control, int world, int rank, uint32_t spin_limit,
                             int32_t* status, void* stream);
-TGT_API int tgt_p2p_fetch(const void* landing_mine, size_t half_bytes, int n_tensors, void* y0,
+TGT_API int tgt_p2p_fetch(const void* slot_mine, size_t slot_bytes, int n_tensors, void* y0,
                           void* y1, void* y2, int64_t bytes_per_tensor, int staged, int world,
                           int64_t width_g_bytes, void* stream);
 

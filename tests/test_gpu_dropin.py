@@ -37,6 +37,12 @@ def test_model_call_form_and_constructor_variants():
         assert o3.shape == (n, h, d) and rel_err(o3.reshape(1, n, -1), ref) < TOL_F32
     with pytest.raises(NotImplementedError):
         core(q.cuda(), k.cuda(), v.cuda(), None, ei.cuda(), "full")
+    # GT argument order (q, k, v): models/gt_dist_node_level.py:83, models/gt_graph_level.py:83
+    from torchgt_b200.attn_module import CoreAttentionQKV
+    from torchgt_b200.gt import CoreAttention as GtCoreAttention
+    assert GtCoreAttention is CoreAttentionQKV
+    o4 = CoreAttentionQKV(h * d, 0.1, h).sparse_attention_bias(q.cuda(), k.cuda(), v.cuda(), ei.cuda(), None)
+    assert o4.shape == (n, h, d) and rel_err(o4.reshape(1, n, -1), ref) < TOL_F32
 
 
 def test_flattened_batch_with_dense_bias_graph_level_form():

@@ -149,9 +149,9 @@ def _peer_table(areas):
                                                  ((1, 32, 64), 1, 2, 1, False), ((2, 16, 32), 1, 2, 1, True),
                                                  ((1, 64, 8), 1, 2, 3, False)])
 def test_peer_push_and_fetch_match_all_to_all_semantics(world, staged, shape, s, g, n_t, alias):
-    """The peer-memory transport on one GPU: every rank's landing area is an ordinary local buffer, the
-    ranks push one after the other, and the per-area epoch is advanced by a one-rank barrier (a real
-    multi-rank barrier needs one GPU per rank and is covered by the multi-GPU test)."""
+    """The peer-memory transport on one GPU: every rank's slot is an ordinary local buffer and the ranks
+    push one after the other (a real multi-rank barrier needs one GPU per rank and is covered by the
+    multi-GPU tests)."""
     import math
     from torchgt_b200 import _cabi
     lib = _cabi.load()
@@ -160,11 +160,9 @@ def test_peer_push_and_fetch_match_all_to_all_semantics(world, staged, shape, s,
     gen = torch.Generator().manual_seed(world + n_t)
     xs = [[torch.randn(shape, generator=gen).cuda() for _ in range(n_t)] for _ in range(world)]
     nbytes = xs[0][0].numel() * 4
-    half = ((n_t * nbytes + 255) // 256) * 256
-    ctl = int(lib.tgt_p2p_control_bytes())
-    areas = [torch.zeros(ctl + 2 * half, dtype=torch.uint8, device="cuda") for _ in range(world)]
-    table = _peer_table(areas)
-    status = torch.zeros(1, dtype=torch.int32).pin_memory()
+    slot_bytes = ((n_t * nbytes + 255) // 256) * 256
+    slots = [torch.zeros(slot_bytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = _peer_table(slots)
     stream = torch.cuda.current_stream().cuda_stream
     chunk = list(shape); chunk[s] //= world
     out_shape = list(chunk); out_shape[g] *= world
@@ -172,31 +170,92 @@ def test_peer_push_and_fetch_match_all_to_all_semantics(world, staged, shape, s,
     ws_bytes = chunk[s] * math.prod(shape[s + 1:]) * 4
     wg_bytes = math.prod(chunk[g:]) * 4
     rows = torch.tensor([0, 4, 12], dtype=torch.int32, device="cuda") if alias else None
-    for step in range(3):          # three exchanges in a row: both landing halves get reused
+    for step in range(2):          # the slot is reused
         for r in range(world):
             ptrs = [t.data_ptr() for t in xs[r]] + [None] * (3 - n_t)
-            _cabi.check(lib.tgt_p2p_push(ptrs[0], ptrs[1], ptrs[2], n_t, table, half, outer_s, ws_bytes, wg_bytes,
+            _cabi.check(lib.tgt_p2p_push(ptrs[0], ptrs[1], ptrs[2], n_t, table, slot_bytes, outer_s, ws_bytes, wg_bytes,
                                          world, r, rows.data_ptr() if alias else None, 3 if alias else 0,
                                          shape[-1] * 4 if alias else 0, staged, stream))
         outs = []
         for r in range(world):
-            one = _peer_table([areas[r]])
-            _cabi.check(lib.tgt_p2p_barrier(one, 1, 0, 10, status.data_ptr(), stream))
             ys = [torch.empty(out_shape, device="cuda") for _ in range(n_t)]
             optrs = [t.data_ptr() for t in ys] + [None] * (3 - n_t)
-            _cabi.check(lib.tgt_p2p_fetch(areas[r].data_ptr(), half, n_t, optrs[0], optrs[1], optrs[2], nbytes, staged,
-                                          world, wg_bytes, stream))
+            _cabi.check(lib.tgt_p2p_fetch(slots[r].data_ptr(), slot_bytes, n_t, optrs[0], optrs[1], optrs[2], nbytes,
+                                          staged, world, wg_bytes, stream))
             outs.append(ys)
         torch.cuda.synchronize()
-        assert int(status[0]) == 0
         for t in range(n_t):
             srcs = [xs[r][t].cpu().numpy() for r in range(world)]
             if alias:
                 srcs = [uo.copy_global_token0(x, [0, 4, 12]) for x in srcs]
             ref = uo.seq_all_to_all(srcs, s, g)
             for r in range(world):
-                assert np.array_equal(outs[r][t].cpu().numpy(), ref[r]), (step, t, r)
+                got = outs[r][t].cpu().numpy()
+                assert np.array_equal(got, ref[r]), (step, t, r)
+                if not staged:       # final-position pushes can be read in place, without the fetch
+                    in_place = slots[r][t * nbytes:(t + 1) * nbytes].view(torch.float32).view(*out_shape)
+                    assert np.array_equal(in_place.cpu().numpy(), ref[r]), (step, t, r)
         xs = [[x + 1.0 for x in row] for row in xs]      # new values for the next exchange
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("batch,rows_local", [(1, 9), (2, 5), (1, 301)])
+def test_woven_push_puts_k_and_v_of_a_row_side_by_side(world, batch, rows_local):
+    """TGT_PUSH_WOVEN: the tensors pushed together arrive as one tensor [b, P * rows, n_t, H_l * D]."""
+    from torchgt_b200 import _cabi
+    lib = _cabi.load()
+    H, D = 8, 8
+    gen = torch.Generator().manual_seed(3 * world + rows_local)
+    xs = [[torch.randn(batch, rows_local, H, D, generator=gen).cuda() for _ in range(2)] for _ in range(world)]
+    nbytes = xs[0][0].numel() * 4
+    slots = [torch.zeros(2 * nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = _peer_table(slots)
+    stream = torch.cuda.current_stream().cuda_stream
+    row_bytes = (H // world) * D * 4
+    for r in range(world):
+        _cabi.check(lib.tgt_p2p_push(xs[r][0].data_ptr(), xs[r][1].data_ptr(), None, 2, table, 2 * nbytes,
+                                     batch * rows_local, row_bytes, rows_local * row_bytes, world, r, None, 0, 0,
+                                     _cabi.TGT_PUSH_WOVEN, stream))
+    torch.cuda.synchronize()
+    refs = [uo.seq_all_to_all([xs[r][t].cpu().numpy() for r in range(world)], 2, 1) for t in range(2)]
+    for r in range(world):
+        woven = slots[r].view(torch.float32).view(batch, world * rows_local, 2, H // world, D).cpu().numpy()
+        for t in range(2):
+            assert np.array_equal(woven[:, :, t], refs[t][r]), (r, t)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("batch,rows_local,n_t,alias", [(1, 9, 1, False), (2, 5, 3, False), (1, 301, 1, True),
+                                                        (3, 4, 1, True)])
+def test_peer_pull_matches_all_to_all_semantics(world, batch, rows_local, n_t, alias):
+    """Heads -> sequence by reading the peers' slots: y[b, l, r * W + c] = slot_r[b, rank * rows + l, c]
+    (gt_sp/layer.py:30-49 with scatter_idx=1, gather_idx=2), global-token rows taken from row 0."""
+    from torchgt_b200 import _cabi
+    lib = _cabi.load()
+    H, D = 8, 8
+    W = (H // world) * D
+    gen = torch.Generator().manual_seed(7 * world + n_t)
+    # rank r holds n_t tensors [b, world * rows, W] back to back in its slot
+    held = [[torch.randn(batch, world * rows_local, W, generator=gen) for _ in range(n_t)] for _ in range(world)]
+    slots = [torch.cat([t.reshape(-1) for t in held[r]]).cuda() for r in range(world)]
+    table = _peer_table(slots)
+    slot_bytes = slots[0].numel() * 4
+    stream = torch.cuda.current_stream().cuda_stream
+    alias_list = list(range(0, world * rows_local, rows_local))
+    rows_dev = torch.tensor(alias_list, dtype=torch.int32, device="cuda") if alias else None
+    for r in range(world):
+        ys = [torch.full((batch, rows_local, world * W), float("nan"), device="cuda") for _ in range(n_t)]
+        ptrs = [t.data_ptr() for t in ys] + [None] * (3 - n_t)
+        _cabi.check(lib.tgt_p2p_pull(table, slot_bytes, n_t, ptrs[0], ptrs[1], ptrs[2], batch, rows_local, W * 4,
+                                     world, r, rows_dev.data_ptr() if alias else None, len(alias_list) if alias else 0,
+                                     stream))
+        torch.cuda.synchronize()
+        for t in range(n_t):
+            srcs = [held[p][t].numpy() for p in range(world)]
+            if alias:
+                srcs = [uo.copy_global_token0(x, alias_list) for x in srcs]
+            ref = uo.seq_all_to_all(srcs, 1, 2)
+            assert np.array_equal(ys[t].cpu().numpy(), ref[r]), (r, t)
 
 
 def test_peer_barrier_gives_up_after_its_poll_limit_and_reports_the_rank():
@@ -205,7 +264,7 @@ def test_peer_barrier_gives_up_after_its_poll_limit_and_reports_the_rank():
     from torchgt_b200 import _cabi
     lib = _cabi.load()
     ctl = int(lib.tgt_p2p_control_bytes())
-    areas = [torch.zeros(ctl + 512, dtype=torch.uint8, device="cuda") for _ in range(3)]
+    areas = [torch.zeros(ctl, dtype=torch.uint8, device="cuda") for _ in range(3)]
     status = torch.zeros(1, dtype=torch.int32).pin_memory()
     stream = torch.cuda.current_stream().cuda_stream
     _cabi.check(lib.tgt_p2p_barrier(_peer_table(areas), 3, 1, 2000, status.data_ptr(), stream))
@@ -216,4 +275,4 @@ def test_peer_barrier_gives_up_after_its_poll_limit_and_reports_the_rank():
     assert lib.tgt_p2p_barrier(_peer_table(areas), 3, 5, 10, status.data_ptr(), stream) == 1
     assert lib.tgt_p2p_barrier(_peer_table(areas), 3, 1, 10, None, stream) == 1
     assert lib.tgt_p2p_push(areas[0].data_ptr(), None, None, 1, _peer_table(areas), 32, 1, 16, 16, 3, 0, None, 0, 0,
-                            0, stream) == 1   # 48 bytes do not fit a 32-byte landing half
+                            0, stream) == 1   # 48 bytes do not fit a 32-byte slot

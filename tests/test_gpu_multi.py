@@ -26,7 +26,8 @@ def _free_port() -> int:
 def _worker(rank, world, port, transport, ret):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
-                      TGT_EXCHANGE=transport, TGT_P2P_SPIN_LIMIT="4000000")
+                      TGT_EXCHANGE=transport.split("-")[0], TGT_P2P_SPIN_LIMIT="4000000",
+                      TGT_FUSED_LAYER="0" if transport.endswith("-unfused") else "1")
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -53,21 +54,30 @@ def _worker(rank, world, port, transport, ret):
         for name, mine in (("out", out.detach()), ("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
             ref = t(name)
             errs[name] = float((mine - ref).abs().max() / ref.abs().max())
+        # a second step through the same slots (their reuse is the delicate part of the transport)
+        q2, k2, v2 = (t(n).clone().requires_grad_() for n in "qkv")
+        out2 = layer(q2, k2, v2, None, torch.from_numpy(g["r0_edge_index"]).to(dev), "sparse")
+        (out2 * t("dout")).sum().backward()
+        errs["out_again"] = float((out2.detach() - t("out")).abs().max() / t("out").abs().max())
+        errs["dk_again"] = float((k2.grad - t("dk")).abs().max() / t("dk").abs().max())
         torch.cuda.synchronize()
         from torchgt_b200.gt_sp import p2p
         px = p2p.peer_exchange_for(group, dev)
         errs["used_peer_memory"] = px is not None
-        if px is not None:
-            px.check()
+        p2p.check_peer_exchanges()
         ret[rank] = errs
     finally:
+        from torchgt_b200.gt_sp import p2p
+        p2p.reset_peer_exchanges()
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("transport", ["p2p", "nccl"])
+@pytest.mark.parametrize("transport", ["p2p", "p2p-unfused", "nccl"])
 def test_nomerge_layer_on_real_gpus(world, transport):
-    """transport = p2p: the library's own NVLink peer-memory exchange; nccl: one all_to_all_single."""
+    """transport = p2p: the library's own NVLink peer-memory exchange with the layer as one autograd node
+    (attention reads the landed q, k, v in place); p2p-unfused: the same transport behind the general
+    _SeqAllToAll; nccl: one all_to_all_single."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
@@ -76,7 +86,7 @@ def test_nomerge_layer_on_real_gpus(world, transport):
         mp.spawn(_worker, args=(world, _free_port(), transport, ret), nprocs=world, join=True)
         for rank in range(world):
             errs = dict(ret[rank])
-            assert errs.pop("used_peer_memory") == (transport == "p2p")
+            assert errs.pop("used_peer_memory") == transport.startswith("p2p")
             assert errs["a2a_21"] == 0.0 and errs["a2a_12"] == 0.0, (rank, errs)
             assert max(errs.values()) < 1e-5, (rank, errs)
 
@@ -127,6 +137,8 @@ def _gt_worker(rank, world, port, ret):
         torch.cuda.synchronize()
         ret[rank] = errs
     finally:
+        from torchgt_b200.gt_sp import p2p
+        p2p.reset_peer_exchanges()
         dist.destroy_process_group()
 
 
@@ -184,6 +196,8 @@ def _graphormer_graph_worker(rank, world, port, ret):
         torch.cuda.synchronize()
         ret[rank] = errs
     finally:
+        from torchgt_b200.gt_sp import p2p
+        p2p.reset_peer_exchanges()
         dist.destroy_process_group()
 
 

@@ -102,6 +102,12 @@ def test_dense_bias_lookup_matches_the_reference_indexing():
     assert torch.equal(edge_bias_from_dense(node_level, ei1, 1, n, h), node_level[0][ei1[0], ei1[1]])
     with pytest.raises(ValueError):
         edge_bias_from_dense(torch.zeros(1, h, n + 1, n + 1), ei1, 1, n, h)
+    # heads == nodes: the shape fits both forms; it is never guessed, the caller names the form
+    square = torch.randn(1, n, n, n, generator=gen)
+    with pytest.raises(ValueError, match="fits both"):
+        edge_bias_from_dense(square, ei1, 1, n, n)
+    assert torch.equal(edge_bias_from_dense(square, ei1, 1, n, n, "node"), square[0][ei1[0], ei1[1]])
+    assert torch.equal(edge_bias_from_dense(square, ei1, 1, n, n, "graph"), square[0][:, ei1[0], ei1[1]].t())
 
 
 def test_the_op_refuses_host_tensors():

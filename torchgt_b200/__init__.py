@@ -10,8 +10,9 @@ All compute runs in hand-written CUDA kernels for sm_100a behind a C ABI (``incl
 loaded with ctypes; there is no CPU fallback.
 """
 from .attn_module import CoreAttention
-from .graph import SparseGraph, clear_graph_cache, graph_for
+from .graph import SparseGraph, clear_graph_cache, graph_for, prepare_edges
 from .sparse_attn import sparse_graph_attention
 
-__all__ = ["CoreAttention", "SparseGraph", "sparse_graph_attention", "graph_for", "clear_graph_cache"]
+__all__ = ["CoreAttention", "SparseGraph", "sparse_graph_attention", "graph_for", "clear_graph_cache",
+           "prepare_edges"]
 __version__ = "1.0"

@@ -14,6 +14,7 @@ TGT_OK = 0
 TGT_ERR_INDEX_RANGE = 5
 TGT_F32 = 0
 TGT_BF16 = 1
+TGT_PUSH_FINAL, TGT_PUSH_STAGED, TGT_PUSH_WOVEN = 0, 1, 2
 
 ERROR_NAMES = {
     1: "TGT_ERR_INVALID",
@@ -55,6 +56,10 @@ SIGNATURES = {
     "tgt_edge_layout_sizes": (c_int, [c_int64, c_int64, POINTER(c_size_t)]),
     "tgt_edge_layout_build": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "tgt_edge_layout_build_i32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "tgt_edge_prepare": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
+                                 c_void_p, c_int64, c_void_p]),
     "tgt_sparse_attn_scratch_bytes": (c_int, [_PL, _PL, c_int, c_int, c_int, c_int, POINTER(c_size_t)]),
     "tgt_sparse_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, _PL, c_void_p,
                                     c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
@@ -82,6 +87,8 @@ SIGNATURES = {
     "tgt_p2p_control_bytes": (c_size_t, []),
     "tgt_p2p_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), c_size_t, c_int64, c_int64,
                              c_int64, c_int, c_int, c_void_p, c_int, c_int64, c_int, c_void_p]),
+    "tgt_p2p_pull": (c_int, [POINTER(c_void_p), c_size_t, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                             c_int64, c_int, c_int, c_void_p, c_int, c_void_p]),
     "tgt_p2p_barrier": (c_int, [POINTER(c_void_p), c_int, c_int, c_uint32, c_void_p, c_void_p]),
     "tgt_p2p_fetch": (c_int, [c_void_p, c_size_t, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int64,
                               c_void_p]),

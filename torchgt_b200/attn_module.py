@@ -27,30 +27,49 @@ def _is_edge_argument(x) -> bool:
 
 
 def edge_bias_from_dense(attn_bias: torch.Tensor, edge_index: torch.Tensor, batch: int, nodes: int,
-                         heads: int) -> torch.Tensor:
+                         heads: int, layout: Optional[str] = None) -> torch.Tensor:
     """Per-edge [E, heads] bias from the reference's dense forms.
 
-    Graph-level form [b, heads, N, N] (models/graphormer_dist_graph_level.py:262-267): edge (s, d) in
-    flattened row numbering reads ``attn_bias[s // N, :, s % N, d % N]``.  Node-level form
+    ``layout="graph"``: [b, heads, N, N] (models/graphormer_dist_graph_level.py:262-267): edge (s, d) in
+    flattened row numbering reads ``attn_bias[s // N, :, s % N, d % N]``.  ``layout="node"``:
     [b, N, N, heads] (models/graphormer_dist_node_level.py:100-106) reads ``attn_bias[s // N, s % N,
-    d % N, :]``.
+    d % N, :]``.  ``layout=None`` tells the form from the shape and raises when the shape fits both
+    (heads == N), instead of guessing.
     """
     src, dst = edge_index[0].long(), edge_index[1].long()
     if attn_bias.dim() != 4 or attn_bias.shape[0] != batch:
         raise ValueError(f"dense attn_bias must be 4-D with batch {batch}; got {tuple(attn_bias.shape)}")
-    if attn_bias.shape[1] == nodes and attn_bias.shape[2] == nodes:
+    fits_node = attn_bias.shape[1] == nodes and attn_bias.shape[2] == nodes
+    fits_graph = attn_bias.shape[2] == nodes and attn_bias.shape[3] == nodes
+    if layout is None:
+        if fits_node and fits_graph:
+            raise ValueError(f"dense attn_bias {tuple(attn_bias.shape)} fits both [b, N, N, heads] and "
+                             "[b, heads, N, N]; set dense_bias_layout ('node' or 'graph') on the module")
+        layout = "node" if fits_node else "graph"
+    if layout not in ("node", "graph"):
+        raise ValueError("layout must be 'node', 'graph' or None")
+    if layout == "node" and fits_node:
         e = attn_bias[src // nodes, src % nodes, dst % nodes, :]
-    elif attn_bias.shape[2] == nodes and attn_bias.shape[3] == nodes:
+    elif layout == "graph" and fits_graph:
         e = attn_bias[src // nodes, :, src % nodes, dst % nodes]
     else:
-        raise ValueError(f"dense attn_bias {tuple(attn_bias.shape)} does not match {nodes} nodes")
+        raise ValueError(f"dense attn_bias {tuple(attn_bias.shape)} does not match {nodes} nodes in the "
+                         f"'{layout}' form")
     if e.shape[1] not in (1, heads):
         raise ValueError(f"dense attn_bias carries {e.shape[1]} heads, the call has {heads}")
     return e
 
 
 class CoreAttention(nn.Module):
-    """``CoreAttention(hidden_size, attention_dropout_rate, num_heads[, attn_bias_dim | device])``."""
+    """``CoreAttention(hidden_size, attention_dropout_rate, num_heads[, attn_bias_dim | device])``.
+
+    ``sparse_attention_bias`` takes (k, q, v, ...), the order of models/graphormer_dist_node_level.py:69,
+    models/graphormer_dist_graph_level.py:238 and models/gt_dist_graph_level.py:83;
+    :class:`CoreAttentionQKV` is the same module with the (q, k, v, ...) order of
+    models/gt_dist_node_level.py:83 and models/gt_graph_level.py:83.  ``dense_bias_layout`` ("node",
+    "graph" or None = told from the shape) names the form of a dense 4-D ``attn_bias``."""
+
+    dense_bias_layout: Optional[str] = None
 
     def __init__(self, hidden_size: int, attention_dropout_rate: float, num_heads: int,
                  attn_bias_dim_or_device=None):
@@ -81,7 +100,7 @@ class CoreAttention(nn.Module):
         if bias is not None and bias.dim() == 4:
             if isinstance(edge_index, SparseGraph):
                 raise ValueError("a dense attn_bias needs the COO edge_index, not a SparseGraph")
-            bias = edge_bias_from_dense(bias, edge_index, batch, nodes, heads)
+            bias = edge_bias_from_dense(bias, edge_index, batch, nodes, heads, self.dense_bias_layout)
         return sparse_graph_attention(q3, k3, v3, edge_index, bias)
 
     def sparse_attention(self, q, k, v, edge_index, attn_bias=None):
@@ -91,8 +110,7 @@ class CoreAttention(nn.Module):
 
     def sparse_attention_bias(self, k, q, v, edge_index, attn_bias=None):
         """models/graphormer_dist_node_level.py:69-127 (argument order k, q, v) -> [b*N, H, D].
-
-        The GT copies (models/gt_dist_node_level.py:83) take (q, k, v): call those by keyword."""
+        Code written against the (q, k, v) copies uses :class:`CoreAttentionQKV`."""
         return self._sparse(q, k, v, edge_index, attn_bias)
 
     def full_attention(self, *args, **kwargs):
@@ -118,3 +136,12 @@ class CoreAttention(nn.Module):
         if edge_index is None:
             raise ValueError("attn_type='sparse' needs edge_index")
         return self._sparse(q, k, v, edge_index, attn_bias).view(batch, s_len, -1)
+
+
+class CoreAttentionQKV(CoreAttention):
+    """The copies whose ``sparse_attention_bias`` takes (q, k, v, edge_index, attn_bias):
+    models/gt_dist_node_level.py:83-142 and models/gt_graph_level.py:83-137.  Everything else is
+    :class:`CoreAttention`."""
+
+    def sparse_attention_bias(self, q, k, v, edge_index, attn_bias=None):
+        return self._sparse(q, k, v, edge_index, attn_bias)

@@ -101,7 +101,7 @@ inline int choose_ge(int64_t n_edges, int g, int ctas_per_sm) {
   // Time is roughly (number of CTA waves) x (work of one tile); a tile costs its ge edges per lane
   // group plus a fixed part (index staging, barriers, stitching) worth about 8 edges.  Few, full
   // waves win; with many waves the tail does not matter and larger tiles amortise the fixed part.
-  const int64_t capacity = int64_t(kSmCount) * ctas_per_sm;
+  const int64_t capacity = int64_t(sm_count()) * ctas_per_sm;
   int best = ge_max;
   double best_cost = 1e300;
   for (int ge = (ge_max < 16 ? ge_max : 16); ge <= ge_max; ge += kGeStep) {

@@ -22,6 +22,31 @@ int set_error(int code, const char* fmt, ...) {
 
 int forced_ge() { return g_forced_ge.load(std::memory_order_relaxed); }
 
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    set_error(TGT_ERR_UNSUPPORTED, "no current CUDA device with an ordinal below %d", kMaxDevices);
+    return -1;
+  }
+  return dev;
+}
+
+int sm_count() {
+  static std::atomic<int> cache[kMaxDevices] = {};
+  const int dev = current_device();
+  if (dev < 0) return 148;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 148;
+    }
+    cache[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
 int check_layout(const tgt_layout* L, const char* name) {
   if (L == nullptr) return set_error(TGT_ERR_INVALID, "%s is null", name);
   if (L->n_rows < 0 || L->n_edges < 0 || L->n_rows >= (int64_t(1) << 31) - 1 ||

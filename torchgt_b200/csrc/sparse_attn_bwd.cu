@@ -453,9 +453,10 @@ __global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const Bwd
 enum { kWalkDq = 0, kWalkDkv = 1, kWalkDqFused = 2 };
 
 int bwd_resident_ctas(int dtype, const HeadSplit& hs, int which) {
-  static int cache[3][2][6][6] = {};
+  static int cache[kMaxDevices][3][2][6][6] = {};   // occupancy is a property of the device
   auto log2i = [](int x) { int l = 0; while ((1 << l) < x) ++l; return l; };
-  int* slot = &cache[which][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
+  const int dev = current_device();
+  int* slot = &cache[dev < 0 ? 0 : dev][which][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
   int result = 4;
 #define TGT_OCC_DQ(T, LPH, G) result = resident_ctas(bwd_dq_kernel<T, LPH, G>, slot)
 #define TGT_OCC_DKV(T, LPH, G) result = resident_ctas(bwd_dkv_kernel<T, LPH, G>, slot)
@@ -580,7 +581,8 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
                      "<= 512 bytes, heads a power of two); pass a per-head bias instead");
   const int64_t n_rows = by_dst->n_rows, n_edges = by_dst->n_edges;
   if (n_rows == 0) return TGT_OK;
-  TGT_CHECK_ARG(dout && q && k && v && out && z && dq && dk && dv, "tensor pointers must not be null");
+  TGT_CHECK_ARG(dout && q && k && v && z && dq && dk && dv, "tensor pointers must not be null");
+  TGT_CHECK_ARG(out != nullptr || !(passes & 1), "out is needed by the row-statistics pre-pass (dbias)");
   TGT_CHECK_ARG(uint64_t(n_rows) * uint64_t(heads) * head_dim * (dtype == TGT_F32 ? 4 : 2) / 16 <
                     (uint64_t(1) << 32),
                 "tensors larger than 64 GiB are not supported");

@@ -131,9 +131,10 @@ __global__ void __launch_bounds__(kBlockThreads) fwd_stitch_kernel(const FwdPara
 
 // Resident CTAs per SM of fwd_kernel<T, LPH, G> for the run-time triple.
 int fwd_resident_ctas(int dtype, const HeadSplit& hs) {
-  static int cache[2][6][6] = {};
+  static int cache[kMaxDevices][2][6][6] = {};   // occupancy is a property of the device
   auto log2i = [](int x) { int l = 0; while ((1 << l) < x) ++l; return l; };
-  int* slot = &cache[dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
+  const int dev = current_device();
+  int* slot = &cache[dev < 0 ? 0 : dev][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
   int result = 4;
 #define TGT_OCC_FWD(T, LPH, G) result = resident_ctas(fwd_kernel<T, LPH, G>, slot)
   TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_FWD);
@@ -242,7 +243,6 @@ namespace {
 constexpr size_t kStaticScratchBytes = size_t(4) << 20;  // 4 MiB per GPU that loads the library
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 void* g_static_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
 
 // The array's name is only a handle on the host; the address the kernels need comes from the

@@ -30,7 +30,13 @@ int set_error(int code, const char* fmt, ...);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-constexpr int kSmCount = 148;  // B200: 2 dies x 74 SMs
+constexpr int kMaxDevices = 64;  // device ordinals the per-device caches cover
+
+// Ordinal of the current device, or -1 (error set) when it cannot be asked or lies outside the caches.
+int current_device();
+// Streaming multiprocessors of the current device (asked from the runtime once per device; 148 on a
+// B200).  Grids and tile plans are sized from it.
+int sm_count();
 
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 

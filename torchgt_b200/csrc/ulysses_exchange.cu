@@ -47,7 +47,7 @@ __global__ void relayout_kernel(Ptrs3 tensors, U* __restrict__ stage, int n_tens
 
 int grid_for(int64_t n) {
   int64_t b = (n + kThreads - 1) / kThreads;
-  const int64_t cap = int64_t(kSmCount) * 16;
+  const int64_t cap = int64_t(sm_count()) * 16;
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return int(b);

@@ -14,13 +14,36 @@ import torch
 
 from . import _cabi
 
+class _StatusRing:
+    """Pinned host words that receive the range-check result of layout builds (one small pinned
+    allocation per process instead of one per layout)."""
+
+    SLOTS = 256
+
+    def __init__(self):
+        self.words = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        self.next = 0
+
+    def take(self) -> torch.Tensor:
+        slot = self.words[self.next:self.next + 1]
+        self.next = (self.next + 1) % self.SLOTS
+        return slot
+
+
+_status_ring: Optional[_StatusRing] = None
+
+
 class EdgeLayout:
     """One orientation of the graph: edges sorted by destination (``group_by=1``) or source (0).
 
     ``perm`` is the stable argsort of the grouping endpoint, ``seg`` that endpoint in sorted order,
-    ``other`` the opposite endpoint in sorted order, ``ptr`` the row pointers (all int32, on the GPU)."""
+    ``other`` the opposite endpoint in sorted order, ``ptr`` the row pointers (all int32, on the GPU).
 
-    def __init__(self, edge_index: torch.Tensor, n_rows: int, group_by: int, defer_check: bool = False):
+    The build never synchronises: the result of its index-range check is copied to pinned host memory
+    behind an event, and :meth:`poll` / :meth:`verify` read it later."""
+
+    def __init__(self, edge_index: torch.Tensor, n_rows: int, group_by: int):
+        global _status_ring
         lib = _cabi.load()
         dev = edge_index.device
         n_edges = int(edge_index.shape[1])
@@ -34,102 +57,199 @@ class EdgeLayout:
         workspace = torch.empty(max(ws.value, 16), dtype=torch.uint8, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
         nz = lambda t: t.data_ptr() if t.numel() else None
-        # deferred check: the build does not synchronise; `bad_index` is read by SparseGraph.check()
-        self.bad_index = torch.zeros(1, **i32) if defer_check else None
-        _cabi.check(lib.tgt_edge_layout_build(
-            nz(edge_index), n_edges, n_rows, group_by, self.ptr.data_ptr(), nz(self.other), nz(self.perm),
-            nz(self.seg), workspace.data_ptr(), workspace.numel(),
-            self.bad_index.data_ptr() if defer_check else None, stream))
+        self.bad_index = torch.empty(1, **i32)     # written by the build: 1 if a node id was out of range
+        wide = edge_index.dtype == torch.int64
+        build = lib.tgt_edge_layout_build if wide else lib.tgt_edge_layout_build_i32
+        _cabi.check(build(nz(edge_index), n_edges, n_rows, group_by, self.ptr.data_ptr(), nz(self.other),
+                          nz(self.perm), nz(self.seg), workspace.data_ptr(), workspace.numel(),
+                          self.bad_index.data_ptr(), stream))
         self.n_rows, self.n_edges, self.group_by = n_rows, n_edges, group_by
         self.c = _cabi.TgtLayout(n_rows=n_rows, n_edges=n_edges, ptr=self.ptr.data_ptr(), other=nz(self.other),
                                  perm=nz(self.perm), seg=nz(self.seg))
+        self.verified = False
+        self._host_flag: Optional[torch.Tensor] = None
+        self._flag_ready: Optional[torch.cuda.Event] = None
+        if not torch.cuda.is_current_stream_capturing():
+            if _status_ring is None:
+                _status_ring = _StatusRing()
+            self._host_flag = _status_ring.take()
+            self._host_flag.copy_(self.bad_index, non_blocking=True)
+            self._flag_ready = torch.cuda.Event()
+            self._flag_ready.record(torch.cuda.current_stream(dev))
 
     def byref(self):
         return ctypes.byref(self.c)
 
+    def _raise_if_bad(self, flag: int) -> None:
+        self.verified = True
+        self._host_flag = self._flag_ready = None
+        if flag != 0:
+            self.verified = False
+            self._failed = True
+            raise _cabi.TgtError(_cabi.TGT_ERR_INDEX_RANGE,
+                                 f"edge_index holds a node id outside [0, {self.n_rows})")
+
+    def poll(self) -> None:
+        """Raise if the build is known to have seen a bad node id; never waits for the GPU."""
+        if getattr(self, "_failed", False):
+            self._raise_if_bad(1)
+        if self.verified or self._flag_ready is None or torch.cuda.is_current_stream_capturing():
+            return
+        if self._flag_ready.query():
+            self._raise_if_bad(int(self._host_flag[0]))
+
+    def verify(self) -> None:
+        """As :meth:`poll`, but waits for the build to finish."""
+        if getattr(self, "_failed", False):
+            self._raise_if_bad(1)
+        if self.verified:
+            return
+        if self._flag_ready is not None:
+            self._flag_ready.synchronize()
+            self._raise_if_bad(int(self._host_flag[0]))
+        else:
+            self._raise_if_bad(int(self.bad_index.item()))
+
 
 class SparseGraph:
-    """Handle holding both layouts of one batch graph.  Build once, pass in place of ``edge_index``."""
+    """Handle holding both layouts of one batch graph.  Build once, pass in place of ``edge_index``.
 
-    def __init__(self, edge_index: torch.Tensor, n_rows: int, defer_check: bool = False):
-        """``defer_check=True`` builds without synchronising the stream (for pipelined input loops): node
-        ids outside [0, n_rows) are then not raised here but by a later :meth:`check` (they are replaced by
-        0 in the layout, so kernels stay in bounds)."""
+    Building enqueues kernels on the current stream and returns without waiting for them.  A node id
+    outside [0, n_rows) is replaced by 0 inside the layouts (so the attention kernels stay in bounds)
+    and reported as a ``TgtError`` by the first later use of the graph that finds the build finished
+    (every attention call polls), or at once by :meth:`check`."""
+
+    def __init__(self, edge_index: torch.Tensor, n_rows: int, defer_check: bool = True):
+        """``edge_index``: [2, E] int64 or int32 on a CUDA device.  ``defer_check=False`` waits for the
+        build and raises on a bad node id before returning."""
         if edge_index.dim() != 2 or edge_index.shape[0] != 2:
             raise ValueError("edge_index must be [2, E]")
         if not edge_index.is_cuda:
             raise RuntimeError("torchgt_b200 runs on CUDA only: edge_index must be a CUDA tensor")
-        edge_index = edge_index.to(torch.int64).contiguous()
+        if edge_index.dtype != torch.int32:
+            edge_index = edge_index.to(torch.int64)
+        edge_index = edge_index.contiguous()
         self.n_rows = int(n_rows)
         self.n_edges = int(edge_index.shape[1])
         self.device = edge_index.device
-        self._defer = bool(defer_check)
-        self.by_dst = EdgeLayout(edge_index, self.n_rows, 1, self._defer)
+        self.by_dst = EdgeLayout(edge_index, self.n_rows, 1)
         self._edge_index = edge_index  # kept until by_src is built
         self._by_src: Optional[EdgeLayout] = None
+        self.scratch_bytes: dict = {}  # (heads, head_dim, dtype, phase) -> bytes the attention kernels need
+        if not defer_check:
+            self.check()
 
     @property
     def by_src(self) -> EdgeLayout:
         """Built on first backward (inference never needs it)."""
         if self._by_src is None:
-            self._by_src = EdgeLayout(self._edge_index, self.n_rows, 0, self._defer)
+            self._by_src = EdgeLayout(self._edge_index, self.n_rows, 0)
             self._edge_index = None
         return self._by_src
 
+    def poll(self) -> None:
+        """Raise a pending index-range error without waiting for the GPU."""
+        self.by_dst.poll()
+        if self._by_src is not None:
+            self._by_src.poll()
+
     def check(self) -> None:
-        """Raise if a deferred build saw a node id outside [0, n_rows) (synchronises)."""
-        for lay in (self.by_dst, self._by_src):
-            if lay is not None and lay.bad_index is not None and int(lay.bad_index.item()) != 0:
-                raise _cabi.TgtError(_cabi.TGT_ERR_INDEX_RANGE, f"edge_index holds a node id outside [0, {self.n_rows})")
+        """Raise if a build saw a node id outside [0, n_rows) (waits for the builds to finish)."""
+        self.by_dst.verify()
+        if self._by_src is not None:
+            self._by_src.verify()
+
+    def same_edges(self, edge_index: torch.Tensor) -> torch.Tensor:
+        """0-d bool tensor on the device: is ``edge_index`` ([2, E], same E) exactly the list this graph was
+        built from?  ``perm`` is a permutation, so equality of both sorted endpoint arrays is equality of
+        the lists, column by column."""
+        lay = self.by_dst
+        if lay.n_edges == 0:
+            return torch.ones((), dtype=torch.bool, device=self.device)
+        dst = edge_index[1].index_select(0, lay.perm)
+        src = edge_index[0].index_select(0, lay.perm)
+        return ((dst == lay.seg) & (src == lay.other)).all()
+
+
+def prepare_edges(raw_edges: torch.Tensor, node_counts, raw_counts=None, add_global_token: bool = True,
+                  sub_seq_len: int = 0, rows_per_graph: int = 0) -> torch.Tensor:
+    """Batch edge construction on the GPU: ``fix_edge_index`` (``add_global_token``), then
+    ``adjust_edge_index_nomerge`` (``sub_seq_len`` > 0), then ``flatten_edge_index_nopad``
+    (``rows_per_graph`` > 0 and several graphs) of the reference (gt_sp/utils.py:34-58,
+    data/collator_sp_sparse.py:107-149,290-309) in one kernel.
+
+    ``raw_edges``: CUDA int64 [2, E] — the raw edges of all graphs of the batch concatenated, node ids
+    local to each graph; ``node_counts`` / ``raw_counts``: nodes and raw edges per graph (ints or
+    sequences; ``raw_counts`` defaults to all edges in one graph).  Returns int32 [2, E_out] in the
+    column order the reference's helpers give, ready for :class:`SparseGraph`."""
+    if not raw_edges.is_cuda or raw_edges.dtype != torch.int64 or raw_edges.dim() != 2 or raw_edges.shape[0] != 2:
+        raise ValueError("raw_edges must be a CUDA int64 [2, E] tensor")
+    raw_edges = raw_edges.contiguous()
+    nodes = [int(node_counts)] if isinstance(node_counts, int) else [int(n) for n in node_counts]
+    total = int(raw_edges.shape[1])
+    counts = [total] if raw_counts is None else [int(c) for c in raw_counts]
+    if len(counts) != len(nodes) or sum(counts) != total:
+        raise ValueError("raw_counts must list every graph and add up to the number of raw edges")
+    dev = raw_edges.device
+    host = torch.tensor([[0] + counts, [0] + nodes], dtype=torch.int64).cumsum(dim=1)
+    ptrs = host.to(dev, non_blocking=True)
+    out_total = total + (2 * sum(nodes) if add_global_token else 0)
+    out = torch.empty((2, out_total), dtype=torch.int32, device=dev)
+    lib = _cabi.load()
+    _cabi.check(lib.tgt_edge_prepare(raw_edges.data_ptr() if total else None, total, ptrs[0].data_ptr(),
+                                     ptrs[1].data_ptr(), len(nodes), 1 if add_global_token else 0,
+                                     int(sub_seq_len), int(rows_per_graph),
+                                     out.data_ptr() if out_total else None, out_total,
+                                     torch.cuda.current_stream(dev).cuda_stream))
+    return out
 
 
 # ---- cache: the reference passes a raw edge_index tensor to every layer ---------------------------
 _CACHE_CAPACITY = 16
-_IDENTITY_CAPACITY = 4  # entries pin their edge_index tensor
+_SAME_SIZE_CAPACITY = 4  # graphs kept per (E, n_rows, device)
+_IDENTITY_CAPACITY = 4   # entries pin their edge_index tensor
 _by_identity: "OrderedDict[tuple, tuple]" = OrderedDict()
-_by_content: "OrderedDict[tuple, SparseGraph]" = OrderedDict()
-_mixers = {}
-
-
-def _fingerprint(edge_index: torch.Tensor) -> tuple:
-    """Content hash computed on the device (wrapping int64 arithmetic), one small sync."""
-    flat = edge_index.reshape(-1)
-    key = (flat.device, )
-    mix = _mixers.get(key)
-    if mix is None:
-        g = torch.Generator(device="cpu").manual_seed(0x7067)
-        mix = (torch.randint(1, 2**62, (4099,), generator=g, dtype=torch.int64) * 2 + 1).to(flat.device)
-        _mixers[key] = mix
-    idx = torch.arange(flat.numel(), device=flat.device) % mix.numel()
-    h = ((flat + 0x9E3779B1) * mix[idx]).sum()
-    return (int(h.item()), int(flat.numel()))
+_by_size: "OrderedDict[tuple, list]" = OrderedDict()
 
 
 def graph_for(edge_index: Union[torch.Tensor, SparseGraph], n_rows: int) -> SparseGraph:
     """Return the cached ``SparseGraph`` of ``edge_index`` (building it on first sight).
 
     Lookup is by tensor identity first (same object, unmodified: the 4 layers of one step), then by
-    device-side content hash (the reference's loops upload a fresh copy of the same edges on every
-    iteration, main_sp_sparse_node_level.py:178-182).
+    content: the reference's loops upload a fresh copy of the same edges on every iteration
+    (main_sp_sparse_node_level.py:178-182), so graphs of the same size on the same device are compared
+    with the new list exactly, element by element on the GPU (one small synchronisation); a graph is
+    reused only when every column matches.
     """
     if isinstance(edge_index, SparseGraph):
         if edge_index.n_rows != n_rows:
             raise ValueError(f"graph has {edge_index.n_rows} rows, tensors have {n_rows}")
         return edge_index
+    if edge_index.dim() != 2 or edge_index.shape[0] != 2:
+        raise ValueError("edge_index must be [2, E]")
     ident = (id(edge_index), edge_index.data_ptr(), edge_index._version, tuple(edge_index.shape), n_rows)
     hit = _by_identity.get(ident)
     if hit is not None and hit[0] is edge_index:
         _by_identity.move_to_end(ident)
         return hit[1]
-    content = (_fingerprint(edge_index), n_rows, edge_index.device)
-    graph = _by_content.get(content)
+    size_key = (int(edge_index.shape[1]), n_rows, edge_index.device)
+    candidates = _by_size.get(size_key, [])
+    graph = None
+    if candidates and edge_index.is_cuda and not torch.cuda.is_current_stream_capturing():
+        same = torch.stack([g.same_edges(edge_index) for g in candidates]).tolist()
+        for g, eq in zip(candidates, same):
+            if eq:
+                graph = g
+                candidates.remove(g)
+                candidates.insert(0, g)
+                break
     if graph is None:
         graph = SparseGraph(edge_index, n_rows)
-        _by_content[content] = graph
-        while len(_by_content) > _CACHE_CAPACITY:
-            _by_content.popitem(last=False)
-    else:
-        _by_content.move_to_end(content)
+        candidates = [graph] + candidates[:_SAME_SIZE_CAPACITY - 1]
+    _by_size[size_key] = candidates
+    _by_size.move_to_end(size_key)
+    while len(_by_size) > _CACHE_CAPACITY:
+        _by_size.popitem(last=False)
     _by_identity[ident] = (edge_index, graph)
     while len(_by_identity) > _IDENTITY_CAPACITY:
         _by_identity.popitem(last=False)
@@ -138,4 +258,4 @@ def graph_for(edge_index: Union[torch.Tensor, SparseGraph], n_rows: int) -> Spar
 
 def clear_graph_cache() -> None:
     _by_identity.clear()
-    _by_content.clear()
+    _by_size.clear()

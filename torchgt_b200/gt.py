@@ -16,7 +16,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .attn_module import CoreAttention
+from .attn_module import CoreAttentionQKV as CoreAttention  # (q, k, v) order, as models/gt_dist_node_level.py:83
 from .gt_sp.gt_layer import DistributedAttention, DistributedAttentionNodeLevel, _SeqGather
 from .gt_sp.initialize import get_sequence_parallel_group, sequence_parallel_is_initialized
 

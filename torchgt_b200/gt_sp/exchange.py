@@ -149,6 +149,11 @@ class _SeqAllToAllMany(torch.autograd.Function):
             # gradient of "listed rows := row 0": row 0 collects the listed rows' gradients, they get 0
             lib = _cabi.load()
             dx = back[0]
+            if any(dx.data_ptr() == g.data_ptr() for g in grads):
+                # the exchange was the identity (one rank): the reduction below edits in place, and
+                # autograd's gradient buffer may be shared with other branches
+                dx = dx.clone()
+                back = (dx,) + tuple(back[1:])
             if dx.dtype not in (torch.float32, torch.bfloat16):
                 raise TypeError("alias rows support float32 and bfloat16 gradients")
             b, rows, w = dx.shape

@@ -1,0 +1,135 @@
+"""The Ulysses layer as ONE autograd node when the transport is peer memory: exchange, attention and
+exchange back without any intermediate copy.
+
+What the reference does per layer call (gt_sp/layer.py:502-550, gt_sp/gt_layer.py:153-206): three
+``_SeqAllToAll`` on q, k, v (each: split, ``contiguous`` per chunk, all-to-all, ``cat``), the attention,
+``copy_global_token0``, one more ``_SeqAllToAll``; and the same again, reversed, in backward.  Here:
+
+  forward   push q, k, v straight into their final rows of the peers' slot -> barrier -> the attention
+            kernel reads the slot in place and writes its output into this rank's own slot -> barrier
+            -> every rank pulls its rows of all peers' outputs into an ordinary tensor (the global-token
+            copy folded into the pull)
+  backward  push dO -> barrier -> (global-token gradient folded into row 0) -> both backward passes read
+            the two slots in place and write dQ, dK, dV into this rank's own slot -> barrier -> pull
+
+The slot that holds q, k, v stays reserved from forward to backward; everything else is given back at
+once (see ``p2p.PeerExchange`` for when a slot may be reused).
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from .. import _cabi
+from ..graph import SparseGraph, graph_for
+from ..sparse_attn import _DTYPES, _scratch, _stream
+from . import p2p
+
+
+def fused_layer_enabled() -> bool:
+    return os.environ.get("TGT_FUSED_LAYER", "1") != "0"
+
+
+def eligible(query: Tensor, attn_bias, edge_index, attn_type, world: int) -> bool:
+    """Can this call take the single-node path?  (CUDA fp32/bf16 [b, rows, H, D] tensors, sparse
+    attention without a bias, heads divisible by the ranks, head slices that are whole 16-byte units.)"""
+    if not fused_layer_enabled() or world < 2 or attn_type != "sparse" or attn_bias is not None:
+        return False
+    if not (isinstance(query, Tensor) and query.is_cuda and query.dim() == 4 and query.dtype in _DTYPES):
+        return False
+    if edge_index is None:
+        return False
+    heads, head_dim = query.shape[2], query.shape[3]
+    if heads % world != 0 or query.numel() == 0:
+        return False
+    row_bytes = (heads // world) * head_dim * query.element_size()
+    return row_bytes % 16 == 0 and (head_dim * query.element_size()) % 16 == 0
+
+
+class _UlyssesSparseAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, graph: SparseGraph, px: "p2p.PeerExchange",
+                alias_rows: Optional[Tensor]):
+        lib = _cabi.load()
+        b, rows, heads, head_dim = q.shape
+        world = px.world
+        heads_l = heads // world
+        row_bytes = heads_l * head_dim * q.element_size()
+        n_rows = b * world * rows
+        tensor_bytes = n_rows * row_bytes
+        code = _DTYPES[q.dtype]
+        px.check()
+        # q, k, v -> peers: rank r' receives heads r' * heads_l .. of every row, at rows rank * rows + l
+        qkv = px.acquire(3 * tensor_bytes)
+        px.push([q, k, v], qkv, b * rows, row_bytes, rows * row_bytes)
+        px.barrier()
+        qg, kg, vg = (qkv.view(t * tensor_bytes, (n_rows, heads_l, head_dim), q.dtype) for t in range(3))
+        landing = px.acquire(tensor_bytes)
+        out_g = landing.view(0, (n_rows, heads_l, head_dim), q.dtype)
+        z = torch.empty((n_rows, heads_l), dtype=torch.float32, device=q.device)
+        scratch = _scratch(graph, heads_l, head_dim, code, 0, q.device)
+        _cabi.check(lib.tgt_sparse_attn_fwd(qg.data_ptr(), kg.data_ptr(), vg.data_ptr(), None, 0,
+                                            graph.by_dst.byref(), out_g.data_ptr(), z.data_ptr(), heads_l, head_dim,
+                                            code, scratch.data_ptr(), scratch.numel(), _stream(q)))
+        px.barrier()
+        out = torch.empty((b, rows, heads * head_dim), dtype=q.dtype, device=q.device)
+        px.pull(landing, [out], b, rows, row_bytes, alias_rows)
+        px.release(landing)
+        ctx.graph, ctx.px, ctx.qkv, ctx.alias_rows = graph, px, qkv, alias_rows
+        ctx.dims = (b, rows, heads, head_dim, heads_l, row_bytes, n_rows, tensor_bytes, code)
+        ctx.io_dtype = q.dtype
+        ctx.save_for_backward(z)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout: Tensor):
+        lib = _cabi.load()
+        (z,) = ctx.saved_tensors
+        px, graph, qkv = ctx.px, ctx.graph, ctx.qkv
+        b, rows, heads, head_dim, heads_l, row_bytes, n_rows, tensor_bytes, code = ctx.dims
+        dtype, dev = ctx.io_dtype, z.device
+        world = px.world
+        dout = dout.contiguous()
+        if dout.dtype != dtype:
+            dout = dout.to(dtype)
+        px.check()
+        landing = px.acquire(tensor_bytes)
+        px.push([dout], landing, b * rows, row_bytes, rows * row_bytes)
+        px.barrier()
+        dog = landing.view(0, (n_rows, heads_l, head_dim), dtype)
+        if ctx.alias_rows is not None:
+            # gradient of "listed rows := row 0": row 0 collects the listed rows' gradients
+            _cabi.check(lib.tgt_global_rows_reduce(dog.data_ptr(), ctx.alias_rows.data_ptr(), ctx.alias_rows.numel(),
+                                                   b, world * rows, heads_l * head_dim, code, _stream(dog)))
+        qg, kg, vg = (qkv.view(t * tensor_bytes, (n_rows, heads_l, head_dim), dtype) for t in range(3))
+        grads = px.acquire(3 * tensor_bytes)
+        dqg, dkg, dvg = (grads.view(t * tensor_bytes, (n_rows, heads_l, head_dim), dtype) for t in range(3))
+        scratch = _scratch(graph, heads_l, head_dim, code, 1, dev)
+        _cabi.check(lib.tgt_sparse_attn_bwd(
+            dog.data_ptr(), qg.data_ptr(), kg.data_ptr(), vg.data_ptr(), None, 0, None, z.data_ptr(),
+            graph.by_dst.byref(), graph.by_src.byref(), dqg.data_ptr(), dkg.data_ptr(), dvg.data_ptr(), None,
+            heads_l, head_dim, code, scratch.data_ptr(), scratch.numel(), _stream(dog)))
+        px.release(qkv)
+        px.release(landing)
+        ctx.qkv = None
+        px.barrier()
+        dq, dk, dv = (torch.empty((b, rows, heads, head_dim), dtype=dtype, device=dev) for _ in range(3))
+        px.pull(grads, [dq, dk, dv], b, rows, row_bytes)
+        px.release(grads)
+        px.check()
+        return dq, dk, dv, None, None, None
+
+
+def ulysses_sparse_attention(px: "p2p.PeerExchange", query: Tensor, key: Tensor, value: Tensor, edge_index,
+                             alias_rows: Optional[Tensor] = None) -> Tensor:
+    """[b, rows, H, D] x3 on every rank -> [b, rows, H*D]: sparse attention over the gathered sequence
+    (``world * rows`` rows per batch entry, numbered rank-major) with the heads sharded over the ranks.
+    ``alias_rows`` (device int32): rows of the gathered sequence whose output is row 0's output."""
+    b, rows = query.shape[0], query.shape[1]
+    graph = graph_for(edge_index, b * px.world * rows)
+    graph.poll()
+    q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
+    return _UlyssesSparseAttention.apply(q, k, v, graph, px, alias_rows)

@@ -18,6 +18,9 @@ class DistributedAttention(_UlyssesBase):
 
     def forward(self, query: Tensor, key: Tensor, value: Tensor, attn_bias: Tensor, edge_index: Tensor,
                 attn_type, *args: Any) -> Tensor:
+        out = self._single_node(query, key, value, attn_bias, edge_index, attn_type, alias=False)
+        if out is not None:
+            return out
         q, k, v = self._gather_sequence(query, key, value)
         bias = attn_bias
         if bias is not None:

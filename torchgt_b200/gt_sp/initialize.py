@@ -83,6 +83,8 @@ def initialize_sequence_parallel(seq_length: int, tensor_model_parallel_size: in
 def destroy_sequence_parallel() -> None:
     """Forget all sequence-parallel state (tests create and tear down groups repeatedly)."""
     global _state
+    from . import p2p
+    p2p.reset_peer_exchanges()    # their symmetric memory and counters belong to the group being forgotten
     _state = _SequenceParallelState()
 
 

@@ -14,6 +14,7 @@ import torch.distributed as dist
 from torch import Tensor
 from torch.nn import Module
 
+from . import fused, p2p
 from .exchange import _exchange, seq_all_to_all_many
 from .initialize import (get_global_token_rows_on, get_last_batch_flag, get_sequence_parallel_group,
                          get_sequence_parallel_rank, get_sequence_parallel_world_size)
@@ -90,6 +91,22 @@ class _UlyssesBase(Module):
         self.scatter_idx = scatter_idx  # heads
         self.gather_idx = gather_idx    # sequence
 
+    def _single_node(self, query: Tensor, key: Tensor, value: Tensor, attn_bias, edge_index, attn_type,
+                     alias: bool):
+        """Exchange + sparse attention + exchange back as one autograd node over peer memory, when the
+        call qualifies (our CoreAttention, CUDA, no bias, transport available); else None."""
+        from ..attn_module import CoreAttention
+        if not isinstance(self.local_attn, CoreAttention):
+            return None
+        world = get_sequence_parallel_world_size()
+        if not fused.eligible(query, attn_bias, edge_index, attn_type, world):
+            return None
+        px = p2p.peer_exchange_for(self.spg, query.device)
+        if px is None:
+            return None
+        rows = get_global_token_rows_on(query.device, get_last_batch_flag()) if alias else None
+        return fused.ulysses_sparse_attention(px, query, key, value, edge_index, rows)
+
     def _gather_sequence(self, query: Tensor, key: Tensor, value: Tensor):
         """[b, s/p(+1), H, D] x3 -> [b, s(+p), H/p, D] x3 in one collective."""
         return seq_all_to_all_many(self.spg, [query, key, value], self.scatter_idx, self.gather_idx)
@@ -162,6 +179,9 @@ class DistributedAttentionNoMerge(_UlyssesBase):
                 attn_type, *args: Any) -> Tensor:
         if not self.training:
             return self.local_attn(query, key, value, attn_bias, edge_index, attn_type, *args)
+        out = self._single_node(query, key, value, attn_bias, edge_index, attn_type, alias=True)
+        if out is not None:
+            return out
         q, k, v = self._gather_sequence(query, key, value)
         bias = attn_bias
         if bias is not None:  # [b, s/p+1, s+1, H] -> [b, s+p, s+1, H/p] -> [b, s+p, s+p, H/p]

@@ -29,12 +29,17 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _scratch(graph: SparseGraph, heads: int, head_dim: int, dtype: int, phase: int, device) -> torch.Tensor:
-    lib = _cabi.load()
-    n = ctypes.c_size_t()
-    by_src = graph.by_src.byref() if phase == 1 else None
-    _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), by_src, heads, head_dim, dtype, phase,
-                                                  ctypes.byref(n)))
-    return torch.empty(max(n.value, 16), dtype=torch.uint8, device=device)
+    """Scratch of one call; its size is asked from the library once per (graph, shape, phase)."""
+    key = (heads, head_dim, dtype, phase)
+    nbytes = graph.scratch_bytes.get(key)
+    if nbytes is None:
+        lib = _cabi.load()
+        n = ctypes.c_size_t()
+        by_src = graph.by_src.byref() if phase == 1 else None
+        _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), by_src, heads, head_dim, dtype, phase,
+                                                      ctypes.byref(n)))
+        nbytes = graph.scratch_bytes[key] = max(n.value, 16)
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
 
 class _SparseGraphAttention(torch.autograd.Function):
@@ -97,6 +102,7 @@ def sparse_graph_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         raise TypeError("q, k, v must all be float32 or all bfloat16")
     n_rows, heads, head_dim = q.shape
     graph = graph_for(edge_index, n_rows)
+    graph.poll()   # a node id outside [0, N) found by the (asynchronous) layout build is raised here
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     if bias is not None:
         if bias.dim() == 2 and bias.shape[1] == 1 and heads != 1:
