@@ -39,10 +39,17 @@ sys.path.insert(0, str(ROOT))
 HEADS, HEAD_DIM = 8, 8
 NODES_PER_RANK = 64000
 ROTATING_SETS = 4
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
-# summarised in profiles/sparse_attn_64k_fp32_kernels.md (fp32 workload; the dQ phase includes the
-# row-statistics kernel).
-NCU_TRAFFIC_BYTES = {"fwd_kernel": 62.7e6, "bwd_dq_kernel": 89.8e6 + 34.8e6, "bwd_dkv_kernel": 101.1e6}
+
+
+def ncu_traffic(workload, dtype_name):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of each phase, as recorded next to the ncu
+    summary of that workload under profiles/ (the dQ phase includes the row-statistics kernel); None when
+    no capture of this workload is on file."""
+    path = ROOT / "profiles" / f"sparse_attn_{workload}_{dtype_name}_traffic.json"
+    try:
+        return {k: float(v) for k, v in json.loads(path.read_text())["dram_bytes_per_launch"].items()}
+    except Exception:
+        return None
 
 
 def measured_hbm_peak():
@@ -119,7 +126,7 @@ def make_inputs(n_rows, n_edges, dtype, seed, device):
     return cast(q), cast(k), cast(v), cast(dout), (bias.to(device) if device is not None else bias)
 
 
-def cpu_reference_rate(edge_index, n_rows, steps, warmup, budget_s=20.0, seed=1234):
+def cpu_reference_rate(edge_index, n_rows, steps, warmup, budget_s=20.0, seed=1234, with_bias=True):
     """Edges/s of the reference's CPU operation sequence (oracle/sparse_attn_oracle.sparse_attention_ops,
     float32, autograd backward) with all host threads, on a bounded edge sample of the workload."""
     from oracle.sparse_attn_oracle import sparse_attention_ops
@@ -130,7 +137,7 @@ def cpu_reference_rate(edge_index, n_rows, steps, warmup, budget_s=20.0, seed=12
     def one(ei, b):
         qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
         t0 = time.perf_counter()
-        out = sparse_attention_ops(qq, kk, vv, ei, b)
+        out = sparse_attention_ops(qq, kk, vv, ei, b if with_bias else None)
         out.backward(dout)
         return time.perf_counter() - t0
 
@@ -159,13 +166,19 @@ def run_reference_arm(args, rank):
     if rank != 0:
         return
     edge_index, n_rows = load_workload(args.workload, ranks=args.gpus)
-    base, mean = cpu_reference_rate(edge_index, n_rows, args.steps, max(args.warmup, 1), budget_s=150.0)
+    if args.gpus > 1:   # the row numbering of the sequence-parallel layer (one global-token slot per rank)
+        from torchgt_b200.gt_sp.utils import adjust_edge_index_nomerge
+        edge_index = adjust_edge_index_nomerge(edge_index, NODES_PER_RANK)
+        n_rows = args.gpus * (NODES_PER_RANK + 1)
+    # N = 1 times the op with a scalar edge bias (gradient included), N > 1 the layer's own call: no bias
+    base, mean = cpu_reference_rate(edge_index, n_rows, args.steps, max(args.warmup, 1), budget_s=150.0,
+                                    with_bias=args.gpus == 1)
     line = {
         "impl": "reference", "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": base["value"],
         "unit": "edges/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus, n_rows, edge_index.shape[1], "fp32", args.workload) | {"device": "host CPU"},
+        "config": workload_config(args.gpus, n_rows, edge_index.shape[1], "fp32", args.workload),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -223,10 +236,9 @@ def epoch_benchmark(rank, world, dev, workload="64k"):
     from torchgt_b200 import SparseGraph
     from torchgt_b200.graphormer import Graphormer
     from torchgt_b200.gt_sp import initialize as sp
+    from torchgt_b200.gt_sp.reducer import Reducer
     from torchgt_b200.gt_sp.utils import adjust_edge_index_nomerge
     from torchgt_b200.synthetic import clustered_edges
-    if world == 1 and not sp.sequence_parallel_is_initialized():
-        pass  # the model then calls the attention directly
     torch.manual_seed(42)
     # the dense layers around the path are library GEMMs; TF32 is what the reference's PyTorch (1.10) used
     # for them by default on Ampere-class GPUs
@@ -252,21 +264,20 @@ def epoch_benchmark(rank, world, dev, workload="64k"):
         batches.append((x[rank * L:(rank + 1) * L].to(dev), y[rank * L:(rank + 1) * L].to(dev), graph, rows,
                         n_nodes, ei.shape[1]))
     params = [p for p in model.parameters()]
+    reducer = Reducer().init(model) if world > 1 else None
 
     def iteration(x, y, graph, rows):
         if world > 1:
             sp.set_global_token_indices(rows)
         out = model(x, None, graph, attn_type="sparse")
         loss = F.nll_loss(out, y)
-        opt.zero_grad(set_to_none=True)
-        loss.backward()
-        if world > 1:
-            grads = [p.grad for p in params if p.grad is not None]
-            flat = torch._utils._flatten_dense_tensors(grads)
-            flat.div_(world)
-            dist.all_reduce(flat)
-            for g, synced in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
-                g.copy_(synced)
+        if reducer is not None:
+            reducer.prepare()                   # gradients accumulate straight into one flat buffer
+            loss.backward()                     # its all-reduce starts when the last gradient has arrived
+            reducer.synchronize()
+        else:
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
         opt.step()
         return loss
 
@@ -325,7 +336,111 @@ def epoch_benchmark(rank, world, dev, workload="64k"):
         result.update({"epoch_time_s": graph_time, "timing": "each training iteration replayed from a CUDA graph",
                        "last_loss": glosses[-1]})
         graphs.clear()
+    if reducer is not None:
+        reducer.remove_hooks()
     return result
+
+
+def training_step_ms(rank, world, dev, sequence_parallel, iters=30):
+    """Milliseconds of one full training iteration of the node-level Graphormer (4 layers, hidden 64, 8
+    heads, 128 features, 40 classes; forward, nll_loss, backward, gradient averaging, fused AdamW) with
+    64,000 nodes on every rank, replayed from a CUDA graph and timed with CUDA events, max over ranks.
+    ``sequence_parallel=True``: the ranks share one graph of world x 64,000 nodes (Ulysses layer, weights
+    replicated, gradients averaged); False: every rank trains its own 64,000-node graph with all heads and
+    no communication — the single-GPU iteration measured in the same job on the same GPUs."""
+    import torch.distributed as dist
+    from torch.nn import functional as F
+    from torchgt_b200 import SparseGraph
+    from torchgt_b200.graphormer import Graphormer
+    from torchgt_b200.gt_sp import initialize as sp
+    from torchgt_b200.gt_sp.reducer import Reducer
+    from torchgt_b200.gt_sp.utils import adjust_edge_index_nomerge
+    from torchgt_b200.synthetic import benchmark_64k
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.manual_seed(42)
+    L = NODES_PER_RANK
+    shared = sequence_parallel and world > 1
+    model = Graphormer(4, 8, 128, 64, 40, 1, 0.3, 0.1, 0.5, 64, 1).to(dev).train()
+    if not shared:
+        for layer in model.layers:
+            layer.self_attention.sequence_parallel = False
+    elif world > 1:
+        for p in model.parameters():
+            dist.broadcast(p.data, src=0)
+    opt = torch.optim.AdamW(model.parameters(), lr=2e-4, weight_decay=0.01, fused=True, capturable=True)
+    reducer = Reducer().init(model) if shared else None
+    ei, n_rows = benchmark_64k(ranks=world if shared else 1)
+    if shared:
+        ei = adjust_edge_index_nomerge(ei, L)
+        n_rows = world * (L + 1)
+        sp.set_global_token_indices(list(range(0, n_rows, L + 1)))
+    graph = SparseGraph(ei.to(dev), n_rows)
+    graph.by_src
+    gen = torch.Generator().manual_seed(7 + rank)
+    x = torch.randn(L, 128, generator=gen).to(dev)
+    y = torch.randint(0, 40, (L,), generator=gen).to(dev)
+
+    def iteration():
+        loss = F.nll_loss(model(x, None, graph, attn_type="sparse"), y)
+        if reducer is not None:
+            reducer.prepare()
+            loss.backward()
+            reducer.synchronize()
+        else:
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+        opt.step()
+        return loss
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            iteration()
+    side.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        loss = iteration()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    for _ in range(5):
+        g.replay()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        g.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([start.elapsed_time(stop) / iters], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    last = float(loss.detach())
+    del g
+    if reducer is not None:
+        reducer.remove_hooks()
+    return float(ms.item()), last
+
+
+def weak_scaling_step(rank, world, dev):
+    """The end-to-end training step under weak scaling: 64,000 nodes per rank, the whole model around the
+    layer.  Efficiency = single-GPU iteration time / N-GPU iteration time, both measured in this job."""
+    single_ms, _ = training_step_ms(rank, world, dev, sequence_parallel=False)
+    if world == 1:
+        return {"nodes_per_rank": NODES_PER_RANK, "ms_per_iteration": single_ms, "single_gpu_ms_per_iteration": single_ms,
+                "efficiency": 1.0, "target_efficiency": 0.85}
+    multi_ms, loss = training_step_ms(rank, world, dev, sequence_parallel=True)
+    return {"nodes_per_rank": NODES_PER_RANK, "n_gpus": world, "ms_per_iteration": multi_ms,
+            "single_gpu_ms_per_iteration": single_ms, "efficiency": single_ms / multi_ms, "target_efficiency": 0.85,
+            "last_loss": loss,
+            "what": "node-level Graphormer (4 layers, hidden 64, 8 heads, 128 features, 40 classes) forward + loss + "
+                    "backward + flat gradient all-reduce + fused AdamW per iteration, CUDA-graph replay, CUDA-event "
+                    "time, max over ranks; the single-GPU figure is the same iteration on 64,000 nodes with all 8 "
+                    "heads and no exchange, run on every GPU of this job at the same time"}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -394,6 +509,90 @@ def kernels_per_step(graph, with_dbias=True, ranks=1, elem=4):
     return 3 * (2 if row_bytes <= 64 else 1) + (1 if with_dbias else 0)
 
 
+def measure_device_resident(sets, steps, warmup):
+    """CUDA-event timings of forward+backward through the C ABI on device-resident input sets: the whole
+    step (with dbias), the step with the bias as a plain input, and each phase on its own."""
+    import copy
+    n_sets = len(sets)
+    step_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 7 if b.dbias is not None else 6))) for b in sets]
+    phase_graphs = [[capture(lambda s, b=b: b.fwd(s)), capture(lambda s, b=b: b.bwd(s, 3 if b.dbias is not None else 2)),
+                     capture(lambda s, b=b: b.bwd(s, 4))] for b in sets]
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(graphs):
+        for i in range(warmup):
+            graphs[i % n_sets].replay()
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(steps):
+            graphs[i % n_sets].replay()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps
+
+    # ---- device-resident throughput: K back-to-back steps over rotating input sets -------------------
+    ms_per_step = timed(step_graphs)
+    # ---- the same step with the bias as a plain input (no dbias: no statistics pre-pass) ---------------
+    plain_sets = []
+    for b in sets:
+        b2 = copy.copy(b)
+        b2.dbias = None
+        plain_sets.append(b2)
+    plain_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 6))) for b in plain_sets]
+    ms_no_dbias = timed(plain_graphs)
+    plain_graphs.clear()
+    # ---- per-phase durations (each phase its own graph, events around every replay) ------------------
+    names = ["fwd_kernel", "bwd_dq_kernel", "bwd_dkv_kernel"]
+    phase_steps = min(steps, 200)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(phase_steps)]
+    for i in range(phase_steps):
+        for j in range(3):
+            evs[i][j].record()
+            phase_graphs[i % n_sets][j].replay()
+        evs[i][3].record()
+    torch.cuda.synchronize()
+    phase_ms = {n: statistics.mean(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(phase_steps))
+                for j, n in enumerate(names)}
+    return {"ms_per_step": ms_per_step, "ms_no_dbias": ms_no_dbias, "phase_ms": phase_ms, "names": names}
+
+
+def extra_workload(name, dtype, steps, warmup, zipf=None):
+    """One more single-GPU workload of the metric, timed like the headline (device-resident, CUDA graph,
+    rotating input sets) with fewer steps: returns a small record for the bench line."""
+    from torchgt_b200 import SparseGraph
+    from torchgt_b200.synthetic import benchmark_64k, benchmark_870k
+    dev = torch.device("cuda", 0)
+    if name == "870k":
+        edge_index, n_rows = benchmark_870k() if zipf is None else benchmark_870k(zipf_exponent=zipf)
+    else:
+        edge_index, n_rows = benchmark_64k()
+    n_edges = edge_index.shape[1]
+    graph = SparseGraph(edge_index.to(dev), n_rows)
+    graph.by_src
+    del edge_index
+    n_sets = 3 if name == "870k" else ROTATING_SETS
+    sets = [OpBuffers(graph, dtype, 1234 + i) for i in range(n_sets)]
+    sampler = ClockSampler(0)
+    m = measure_device_resident(sets, steps, warmup)
+    clocks = sampler.stop()
+    elem = 4 if dtype == torch.float32 else 2
+    peak, peak_kind = measured_hbm_peak()
+    bytes_ = algorithmic_bytes(n_rows, n_edges, HEADS, HEAD_DIM, elem, 4)
+    dominant = max(m["names"], key=lambda n: m["phase_ms"][n])
+    step_bytes = sum(bytes_.values())
+    del sets, graph
+    torch.cuda.empty_cache()
+    return {"rows": n_rows, "edges": n_edges, "io_dtype": "fp32" if elem == 4 else "bf16", "steps": steps,
+            "ms_per_step": m["ms_per_step"], "edges_per_s": n_edges / (m["ms_per_step"] * 1e-3),
+            "frac": step_bytes / (m["ms_per_step"] * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
+            "dominant_phase": dominant,
+            "dominant_phase_frac": bytes_[dominant] / (m["phase_ms"][dominant] * 1e-3) / 1e9 / peak,
+            "phases_ms": m["phase_ms"],
+            "phases_frac": {n: bytes_[n] / (m["phase_ms"][n] * 1e-3) / 1e9 / peak for n in m["names"]},
+            "ms_per_step_without_dbias": m["ms_no_dbias"], "clocks": clocks}
+
+
 def run_single_gpu(args, dtype):
     from torchgt_b200 import SparseGraph, sparse_graph_attention
     dev = torch.device("cuda", 0)
@@ -423,55 +622,9 @@ def run_single_gpu(args, dtype):
         print(json.dumps({"profile_run": True, "steps": args.steps, "warmup": args.warmup, "rows": n_rows,
                           "edges": n_edges, "heads": HEADS, "bias": not args.no_bias}), flush=True)
         return
-    step_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 7 if b.dbias is not None else 6))) for b in sets]
-    phase_graphs = [[capture(lambda s, b=b: b.fwd(s)), capture(lambda s, b=b: b.bwd(s, 3 if b.dbias is not None else 2)),
-                     capture(lambda s, b=b: b.bwd(s, 4))] for b in sets]
-    torch.cuda.synchronize()
-
     sampler = ClockSampler(0)
-    # ---- device-resident throughput: K back-to-back steps over rotating input sets -------------------
-    for i in range(args.warmup):
-        step_graphs[i % ROTATING_SETS].replay()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(args.steps):
-        step_graphs[i % ROTATING_SETS].replay()
-    stop.record()
-    torch.cuda.synchronize()
-    ms_per_step = start.elapsed_time(stop) / args.steps
-
-    # ---- the same step with the bias as a plain input (no dbias: no statistics pre-pass) ----------------
-    import copy
-    plain_sets = []
-    for b in sets:
-        b2 = copy.copy(b)
-        b2.dbias = None
-        plain_sets.append(b2)
-    plain_graphs = [capture(lambda s, b=b: (b.fwd(s), b.bwd(s, 6))) for b in plain_sets]
-    for i in range(args.warmup):
-        plain_graphs[i % ROTATING_SETS].replay()
-    torch.cuda.synchronize()
-    start.record()
-    for i in range(args.steps):
-        plain_graphs[i % ROTATING_SETS].replay()
-    stop.record()
-    torch.cuda.synchronize()
-    ms_no_dbias = start.elapsed_time(stop) / args.steps
-    plain_graphs.clear()
-
-    # ---- per-phase durations (each phase its own graph, events around every replay) ------------------
-    names = ["fwd_kernel", "bwd_dq_kernel", "bwd_dkv_kernel"]
-    phase_steps = min(args.steps, 200)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(phase_steps)]
-    for i in range(phase_steps):
-        for j in range(3):
-            evs[i][j].record()
-            phase_graphs[i % ROTATING_SETS][j].replay()
-        evs[i][3].record()
-    torch.cuda.synchronize()
-    phase_ms = {n: statistics.mean(evs[i][j].elapsed_time(evs[i][j + 1]) for i in range(phase_steps))
-                for j, n in enumerate(names)}
+    m = measure_device_resident(sets, args.steps, args.warmup)
+    ms_per_step, ms_no_dbias, phase_ms, names = m["ms_per_step"], m["ms_no_dbias"], m["phase_ms"], m["names"]
 
     # ---- end to end through the public API from pinned host memory -----------------------------------
     hq, hk, hv, hdout, hbias = (t.pin_memory() for t in make_inputs(n_rows, n_edges, dtype, 99, None))
@@ -548,6 +701,23 @@ def run_single_gpu(args, dtype):
             epoch = epoch_benchmark(0, 1, dev, args.workload)
         except Exception as exc:          # the headline numbers above do not depend on this leg
             epoch = {"error": repr(exc)[:300]}
+    # the rest of the metric (870K sequence length, bf16), timed the same way with fewer steps
+    more = None
+    if args.workload == "64k" and dtype == torch.float32 and os.environ.get("TGT_BENCH_MORE", "1") != "0":
+        del sets
+        torch.cuda.empty_cache()
+        more = {}
+        for key, wl, dt, zipf in (("64k_bf16", "64k", torch.bfloat16, None), ("870k_fp32", "870k", torch.float32, None),
+                                  ("870k_fp32_uniform_sources", "870k", torch.float32, 0.0),
+                                  ("870k_bf16", "870k", torch.bfloat16, None)):
+            try:
+                more[key] = extra_workload(wl, dt, 40 if wl == "870k" else 200, 5, zipf)
+            except Exception as exc:
+                more[key] = {"error": repr(exc)[:300]}
+        more["note"] = ("same timing as the headline (device-resident forward+backward with dbias through the C ABI, "
+                        "CUDA graph, rotating input sets larger than L2); 870k = 870,001 rows, 18,214,272 edges; "
+                        "uniform_sources draws the random edges' sources uniformly instead of from the power law, "
+                        "so no K/V row is hot in L2")
     line = {
         "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": n_edges / (ms_per_step * 1e-3),
         "unit": "edges/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
@@ -567,7 +737,7 @@ def run_single_gpu(args, dtype):
         "gpu_launches": kernels_per_step(graph, elem=elem) * args.steps,
         "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                     "traffic": NCU_TRAFFIC_BYTES.get(dominant) if (dtype == torch.float32 and args.workload == "64k") else None,
+                     "traffic": (ncu_traffic(args.workload, args.dtype) or {}).get(dominant),
                      "algorithmic_bytes_per_launch": bytes_[dominant],
                      "phases_ms": phase_ms,
                      "phases_frac": {n: bytes_[n] / (phase_ms[n] * 1e-3) / 1e9 / peak for n in names},
@@ -580,15 +750,96 @@ def run_single_gpu(args, dtype):
                                  "term either); the headline step computes dbias as well"}},
         "cpu_baseline": cpu,
         "epoch": epoch,
+        "more_workloads": more,
     }
     print(json.dumps(line), flush=True)
 
 
 # ---------------------------------------------------------------------------------------------------
+def rank_inputs(rank, i, L, dtype):
+    """The seeded q, k, v [1, L+1, H, D] and dO [1, L+1, H*D] of rank ``rank``, input set ``i`` (host)."""
+    gen = torch.Generator().manual_seed(4321 + 17 * rank + i)
+    q, k, v = (torch.randn(1, L + 1, HEADS, HEAD_DIM, generator=gen).to(dtype) for _ in range(3))
+    dout = torch.randn(1, L + 1, HEADS * HEAD_DIM, generator=gen).to(dtype)
+    return q, k, v, dout
+
+
+def layer_parity(layer, graph, edge_index, rank, world, L, dev, dtype):
+    """One forward+backward of the layer on every rank, compared with the float64 CPU oracle (outside any
+    timed region).  Every output row depends only on its in-edges and every dK/dV row on its out-edges and
+    on the statistics of their destinations, so a sample of rows is checked EXACTLY against the oracle
+    evaluated on the sub-problem that holds all those edges; the global-token row 0 (in- and out-degree
+    world x 64,000) is always in the sample.  Each rank checks its own rows for two of the eight heads
+    (rank r: heads r mod 8 and (r + 3) mod 8, so every rank's attention kernels are covered).
+    Returns the largest error relative to max |reference| of each compared tensor."""
+    import numpy as np
+    import torch.distributed as dist
+    from oracle.sparse_attn_oracle import backward_closed_form, forward_closed_form
+    heads = sorted({rank % HEADS, (rank + 3) % HEADS})
+    full = [rank_inputs(r, 0, L, dtype) for r in range(world)]
+    cat = lambda j: torch.cat([f[j][0].float() for f in full], dim=0)
+    q_all, k_all, v_all = (cat(j)[:, heads].contiguous() for j in range(3))                # [N, 2, D]
+    do_all = cat(3).view(-1, HEADS, HEAD_DIM)[:, heads].contiguous()
+    slots = [r * (L + 1) for r in range(world)]
+    # copy_global_token0: every rank's slot of the global token reads row 0's output, so row 0 collects
+    # their gradients and the slots' own rows get none
+    do_eff = do_all.clone()
+    do_eff[0] = do_all[slots].sum(dim=0)
+    do_eff[slots[1:]] = 0
+
+    q, k, v, dout = (t.to(dev) for t in full[rank])
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    out = layer(q, k, v, None, graph, "sparse")
+    out.backward(dout)
+    torch.cuda.synchronize()
+    mine = {"out": out.detach(), "dq": q.grad, "dk": k.grad, "dv": v.grad}
+    mine = {n: t.float().cpu().view(L + 1, HEADS, HEAD_DIM)[:, heads].double().numpy() for n, t in mine.items()}
+
+    gen = torch.Generator().manual_seed(99 + rank)
+    base = rank * (L + 1)
+    local_dst = torch.randint(1, L + 1, (192,), generator=gen).unique()
+    local_src = torch.randint(1, L + 1, (64,), generator=gen).unique()
+    n_total = world * (L + 1)
+    is_src = torch.zeros(n_total, dtype=torch.bool); is_src[base + local_src] = True
+    dests = edge_index[1][is_src[edge_index[0]]].unique()
+    is_dst = torch.zeros(n_total, dtype=torch.bool)
+    is_dst[base + local_dst] = True; is_dst[dests] = True; is_dst[0] = True
+    sub = edge_index[:, is_dst[edge_index[1]]]
+    ref_out, _ = forward_closed_form(q_all, k_all, v_all, sub)
+    ref_dq, ref_dk, ref_dv, _ = backward_closed_form(q_all, k_all, v_all, sub, do_eff)
+
+    def err(x, ref):
+        return float(np.abs(x - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+    errs = {}
+    d_rows = local_dst.numpy()
+    errs["out"] = max(err(mine["out"][d_rows], ref_out[base + d_rows]),
+                      err(mine["out"][0], ref_out[0]))               # this rank's token slot = row 0's output
+    errs["dq"] = err(mine["dq"][d_rows], ref_dq[base + d_rows])
+    if rank == 0:
+        errs["dq"] = max(errs["dq"], err(mine["dq"][0], ref_dq[0]))
+    else:
+        errs["dq"] = max(errs["dq"], float(np.abs(mine["dq"][0]).max()))   # the other slots have no edges
+    s_rows = local_src.numpy()
+    errs["dk"] = err(mine["dk"][s_rows], ref_dk[base + s_rows])
+    errs["dv"] = err(mine["dv"][s_rows], ref_dv[base + s_rows])
+    if rank == 0:   # row 0's out-edges reach every node: their destinations are not all in the sample; its
+        pass        # in-edge side (out, dq) is checked above
+    worst = torch.tensor([errs["out"], errs["dq"], errs["dk"], errs["dv"]], device=dev, dtype=torch.float64)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    worst = worst.tolist()
+    return {"max_rel_err": max(worst), "out": worst[0], "dq": worst[1], "dk": worst[2], "dv": worst[3],
+            "rows": int(local_dst.numel() + 1), "source_rows": int(local_src.numel()), "edges_in_subproblem": int(sub.shape[1]),
+            "heads_checked_per_rank": 2, "tolerance": 1e-5 if dtype == torch.float32 else 1e-2,
+            "oracle": "float64 closed form of the reference's op sequence (oracle/sparse_attn_oracle.py)"}
+
+
 def run_multi_gpu(args, dtype, rank, world):
+    import gc
     import torch.distributed as dist
     from torchgt_b200 import CoreAttention, SparseGraph
     from torchgt_b200.gt_sp import initialize as sp
+    from torchgt_b200.gt_sp import p2p
     from torchgt_b200.gt_sp.layer import DistributedAttentionNoMerge
     from torchgt_b200.gt_sp.utils import adjust_edge_index_nomerge
     from torchgt_b200.synthetic import benchmark_64k
@@ -607,13 +858,28 @@ def run_multi_gpu(args, dtype, rank, world):
     graph.by_src
     core = CoreAttention(HEADS * HEAD_DIM, 0.0, HEADS, 1)
     layer = DistributedAttentionNoMerge(core, sp.get_sequence_parallel_group()).train()
+
+    def note(msg):
+        if os.environ.get("TGT_BENCH_TRACE"):
+            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+
+    # ---- parity first: the numbers below are only worth something if the layer is right -----------------
+    parity = layer_parity(layer, graph, edge_index, rank, world, L, dev, dtype)
+    px = p2p.peer_exchange_for(sp.get_sequence_parallel_group(), dev)
+    parity["transport"] = "p2p" if px is not None else "nccl"
+    note(f"parity {parity['max_rel_err']:.2e}")
+    if parity["max_rel_err"] > parity["tolerance"]:
+        if rank == 0:
+            print(json.dumps({"error": "multi-GPU parity failed", "parity": parity}), flush=True)
+        dist.barrier()
+        p2p.reset_peer_exchanges()
+        dist.destroy_process_group()
+        raise SystemExit(3)
+
     sets = []
     for i in range(ROTATING_SETS):
-        gen = torch.Generator().manual_seed(4321 + 17 * rank + i)
-        q, k, v = (torch.randn(1, L + 1, HEADS, HEAD_DIM, generator=gen).to(dtype).to(dev).requires_grad_()
-                   for _ in range(3))
-        dout = torch.randn(1, L + 1, HEADS * HEAD_DIM, generator=gen).to(dtype).to(dev)
-        sets.append((q, k, v, dout))
+        q, k, v, dout = (t.to(dev) for t in rank_inputs(rank, i, L, dtype))
+        sets.append((q.requires_grad_(), k.requires_grad_(), v.requires_grad_(), dout))
 
     def step(i):
         q, k, v, dout = sets[i % ROTATING_SETS]
@@ -635,15 +901,11 @@ def run_multi_gpu(args, dtype, rank, world):
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    def note(msg):
-        if os.environ.get("TGT_BENCH_TRACE"):
-            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
-
     sampler = ClockSampler(local) if rank == 0 else None
     eager_ms = timed(step)
     note(f"eager {eager_ms:.3f} ms")
     # The same step (layer forward, backward, both exchanges) captured once per input set in a CUDA
-    # graph: the NCCL all-to-alls and every kernel replay without host work in between.
+    # graph: every kernel of the exchange and of the attention replays without host work in between.
     graphs = []
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -651,16 +913,14 @@ def run_multi_gpu(args, dtype, rank, world):
         for i in range(ROTATING_SETS):
             step(i)
     side.synchronize(); dist.barrier()
-    note("side-stream warm-up done")
     for i in range(ROTATING_SETS):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=side):
             step(i)
         graphs.append(g)
-        note(f"captured step graph {i}")
     torch.cuda.synchronize(); dist.barrier()
-    note("replaying")
     ms_per_step = timed(lambda i: graphs[i % ROTATING_SETS].replay())
+    p2p.check_peer_exchanges()           # a barrier that gave up on a peer invalidates the timing
     note(f"graph {ms_per_step:.3f} ms")
 
     # the attention alone (no exchange) on this rank's head slice of the same graph, for reference
@@ -690,6 +950,7 @@ def run_multi_gpu(args, dtype, rank, world):
         op_graphs.append(g)
     torch.cuda.synchronize(); dist.barrier()
     op_ms = timed(lambda i: op_graphs[i % ROTATING_SETS].replay())
+    del op_sets
 
     # end to end: this rank's q, k, v, dO come from pinned host memory, the result goes back
     host = [t.detach().cpu().pin_memory() for t in sets[0]]
@@ -716,12 +977,16 @@ def run_multi_gpu(args, dtype, rank, world):
     e2e_s = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=dev)
     dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     clocks = sampler.stop() if sampler else None
-    epoch = None
+    epoch = weak = None
     if dtype == torch.float32 and os.environ.get("TGT_BENCH_EPOCH", "1") != "0":
         try:
             epoch = epoch_benchmark(rank, world, dev)
         except Exception as exc:
             epoch = {"error": repr(exc)[:300]}
+        try:
+            weak = weak_scaling_step(rank, world, dev)
+        except Exception as exc:
+            weak = {"error": repr(exc)[:300]}
         sp.set_global_token_indices(list(range(0, world * (L + 1), L + 1)))
 
     if rank == 0:
@@ -730,18 +995,19 @@ def run_multi_gpu(args, dtype, rank, world):
         bytes_ = algorithmic_bytes(n_rows, n_edges, heads_local, HEAD_DIM, elem, 0)
         step_bytes = sum(bytes_.values())
         per_rank_io = 4 * (L + 1) * HEADS * HEAD_DIM * elem
-        # kernels: the attention phases and, per exchange, push + barrier + fetch (or pack + unpack + NCCL)
-        launches = kernels_per_step(graph, with_dbias=False, ranks=world, elem=elem) + 4 * 3
+        # kernels: the attention phases; per step two pushes, two pulls, four barriers, one global-row kernel
+        launches = kernels_per_step(graph, with_dbias=False, ranks=world, elem=elem) + (9 if px is not None else 12)
         line = {
             "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": n_edges / (ms_per_step * 1e-3),
             "unit": "edges/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32" if dtype == torch.float32 else "bf16 i/o, f32 math", "data": "synthetic",
-            "config": workload_config(world, n_rows, n_edges, args.dtype) |
-                      {"timing": "step captured in a CUDA graph per input set (NCCL inside), replayed",
-                       "step": "DistributedAttentionNoMerge fwd+bwd: all-to-all(q,k,v) -> attention with "
-                               f"{heads_local} head(s) over all rows -> all-to-all(out), reversed in backward",
-                       "bias": "none (the models pass attn_bias=None on this path)"},
+            "config": workload_config(world, n_rows, n_edges, args.dtype),
+            "step": {"timing": "step captured in a CUDA graph per input set, replayed",
+                     "what": "DistributedAttentionNoMerge fwd+bwd: exchange(q,k,v) -> attention with "
+                             f"{heads_local} head(s) over all rows -> exchange(out), reversed in backward",
+                     "bias": "none (the models pass attn_bias=None on this path)"},
+            "parity": parity,
             "clocks": clocks,
             "e2e": {"value": n_edges / float(e2e_s.item()), "unit": "edges/s", "h2d_bytes_per_step": per_rank_io,
                     "d2h_bytes_per_step": per_rank_io, "ms_per_step": float(e2e_s.item()) * 1e3,
@@ -750,6 +1016,7 @@ def run_multi_gpu(args, dtype, rank, world):
             "gpu_launches": launches * args.steps,
             "eager_ms_per_step": eager_ms,
             "epoch": epoch,
+            "weak_scaling_training_step": weak,
             "attention_only": {"ms_per_step": op_ms, "value": n_edges / (op_ms * 1e-3), "unit": "edges/s",
                                "note": "same graph, this rank's head slice, no exchange (CUDA graph)",
                                "frac_of_hbm_peak": step_bytes / (op_ms * 1e-3) / 1e9 / peak},
@@ -759,13 +1026,16 @@ def run_multi_gpu(args, dtype, rank, world):
                          "traffic": None, "algorithmic_bytes_per_launch": step_bytes},
         }
         print(json.dumps(line), flush=True)
-    # graphs that hold NCCL nodes must be gone, and the device idle, before the communicator is torn down
+    # Orderly exit.  Communicator teardown waits for every CUDA graph that captured one of its collectives,
+    # so all graphs go first; then the symmetric-memory slots, then the process group.
     graphs.clear(); op_graphs.clear()
-    import gc
+    del layer, sets
     gc.collect()
     torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    p2p.reset_peer_exchanges()
+    gc.collect()
     sys.stdout.flush(); sys.stderr.flush()
-    os._exit(0)   # every rank is past its last collective; skip the communicator teardown
+    dist.destroy_process_group()
 
 
 def main():

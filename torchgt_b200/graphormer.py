@@ -58,13 +58,17 @@ class MultiHeadAttention(nn.Module):
         group = get_sequence_parallel_group() if sequence_parallel_is_initialized() else None
         self.dist_attn = DistributedAttentionNoMerge(core, group)
         self.output_layer = nn.Linear(num_heads * self.att_size, hidden_size)
+        # None: go through the sequence-parallel layer whenever a group exists; False: always attend
+        # locally over the rows given (a single-GPU model inside a multi-rank job)
+        self.sequence_parallel = None
 
     def forward(self, x, attn_bias=None, edge_index=None, attn_type=None, mask=None):
         b = x.size(0)
         q = self.linear_q(x).view(b, -1, self.num_heads, self.att_size)
         k = self.linear_k(x).view(b, -1, self.num_heads, self.att_size)
         v = self.linear_v(x).view(b, -1, self.num_heads, self.att_size)
-        if sequence_parallel_is_initialized():
+        use_sp = sequence_parallel_is_initialized() if self.sequence_parallel is None else self.sequence_parallel
+        if use_sp:
             ctx = self.dist_attn(q, k, v, attn_bias, edge_index, attn_type)
         else:  # single process without a sequence-parallel group: the layer would only pass through
             ctx = self.dist_attn.local_attn(q, k, v, attn_bias, edge_index, attn_type)

@@ -67,7 +67,7 @@ class _UlyssesSparseAttention(torch.autograd.Function):
         px.push([q, k, v], qkv, b * rows, row_bytes, rows * row_bytes)
         px.barrier()
         qg, kg, vg = (qkv.view(t * tensor_bytes, (n_rows, heads_l, head_dim), q.dtype) for t in range(3))
-        landing = px.acquire(tensor_bytes)
+        landing = px.acquire(tensor_bytes, p2p.SOURCE)
         out_g = landing.view(0, (n_rows, heads_l, head_dim), q.dtype)
         z = torch.empty((n_rows, heads_l), dtype=torch.float32, device=q.device)
         scratch = _scratch(graph, heads_l, head_dim, code, 0, q.device)
@@ -105,7 +105,7 @@ class _UlyssesSparseAttention(torch.autograd.Function):
             _cabi.check(lib.tgt_global_rows_reduce(dog.data_ptr(), ctx.alias_rows.data_ptr(), ctx.alias_rows.numel(),
                                                    b, world * rows, heads_l * head_dim, code, _stream(dog)))
         qg, kg, vg = (qkv.view(t * tensor_bytes, (n_rows, heads_l, head_dim), dtype) for t in range(3))
-        grads = px.acquire(3 * tensor_bytes)
+        grads = px.acquire(3 * tensor_bytes, p2p.SOURCE)
         dqg, dkg, dvg = (grads.view(t * tensor_bytes, (n_rows, heads_l, head_dim), dtype) for t in range(3))
         scratch = _scratch(graph, heads_l, head_dim, code, 1, dev)
         _cabi.check(lib.tgt_sparse_attn_bwd(

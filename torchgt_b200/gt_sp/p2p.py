@@ -14,6 +14,16 @@ out again only after one more barrier has been enqueued: by then every rank has 
 writing) its old content, because a rank announces a barrier only after everything it enqueued before.
 New slots are created on demand (a collective set-up step); that cannot happen while a CUDA graph is
 being captured, so run one eager step first.
+
+Slots keep the role they were created for: LANDING slots are written by the peers' pushes and read by
+their owner; SOURCE slots are written by their owner's kernels and read by the peers' pulls.  With the
+roles apart, the first write a training iteration makes to any slot is ordered behind a barrier that
+every reader of the old content has already announced (a push at the start of an iteration follows the
+previous iteration's last barrier, which the owner announced after its last read; the owner's kernels
+write a SOURCE slot only after the first barrier of their own iteration, which every peer announces
+after its last pull).  So CUDA graphs that each hold whole iterations of the fused layer can be replayed
+in any order.  Graphs that hold bare ``_SeqAllToAll`` exchanges must be replayed in the order they were
+captured.
 """
 from __future__ import annotations
 
@@ -32,6 +42,9 @@ _GRANULE = 2 << 20
 DEFAULT_SPIN_LIMIT = 60_000_000  # polls of the barrier before it gives up (about a minute)
 
 
+LANDING, SOURCE = "landing", "source"   # who writes a slot: the peers' pushes / its owner's kernels
+
+
 class PeerExchangeTimeout(RuntimeError):
     pass
 
@@ -39,9 +52,10 @@ class PeerExchangeTimeout(RuntimeError):
 class Slot:
     """One peer-visible buffer of ``nbytes`` on every rank of the group."""
 
-    def __init__(self, buffer: Tensor, handle, world: int):
+    def __init__(self, buffer: Tensor, handle, world: int, role: str = LANDING):
         self.buffer = buffer
         self.handle = handle
+        self.role = role
         self.nbytes = buffer.numel()
         self.peers = (ctypes.c_void_p * world)(*[int(p) for p in handle.buffer_ptrs])
         self.free_epoch = -1          # barrier count at the moment it was last given back
@@ -75,7 +89,7 @@ class PeerExchange:
         self.control = self._new_symmetric(control_bytes)
 
     # -- memory ------------------------------------------------------------------------------------
-    def _new_symmetric(self, nbytes: int) -> Slot:
+    def _new_symmetric(self, nbytes: int, role: str = LANDING) -> Slot:
         """Collective: every rank of the group allocates ``nbytes`` and learns the peers' addresses."""
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("the peer exchange needs a new slot while a CUDA graph is being captured; "
@@ -86,18 +100,19 @@ class PeerExchange:
         buf.zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)               # every rank's memory is zeroed before anyone uses it
-        return Slot(buf, handle, self.world)
+        return Slot(buf, handle, self.world, role)
 
-    def acquire(self, nbytes: int) -> Slot:
-        """A slot of at least ``nbytes`` that no rank is still using (same choice on every rank)."""
+    def acquire(self, nbytes: int, role: str = LANDING) -> Slot:
+        """A slot of at least ``nbytes`` and of this role that no rank is still using (same choice on
+        every rank)."""
         want = (max(int(nbytes), 16) + _GRANULE - 1) // _GRANULE * _GRANULE
         best = None
         for slot in self.slots:
-            if not slot.in_use and slot.free_epoch < self.epoch and slot.nbytes >= want:
+            if slot.role == role and not slot.in_use and slot.free_epoch < self.epoch and slot.nbytes >= want:
                 if best is None or slot.nbytes < best.nbytes:
                     best = slot
         if best is None:
-            best = self._new_symmetric(want)
+            best = self._new_symmetric(want, role)
             self.slots.append(best)
         best.in_use = True
         return best

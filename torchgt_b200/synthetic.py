@@ -45,13 +45,13 @@ def benchmark_64k(seed: int = 1234, ranks: int = 1):
     return clustered_edges(seed, 64000 * ranks, 8 * ranks, 334450 * ranks, 0.315)
 
 
-def benchmark_870k(seed: int = 1234):
+def benchmark_870k(seed: int = 1234, zipf_exponent: float = 2.1):
     """The long-sequence batch: 870,000 nodes + global node, 18,214,272 directed edges (the sizes the
     reference logs for its 870K-token ogbn-products batch), power-law out-degrees (exponent 2.1), 8 clusters
-    with 7.1 % of all edges cut."""
+    with 7.1 % of all edges cut.  ``zipf_exponent=0`` draws the sources uniformly instead (no hot rows)."""
     n = 870000
     random_edges = 18214272 - 3 * n
-    return clustered_edges(seed, n, 8, random_edges, 1293861 / random_edges / 0.875, zipf_exponent=2.1)
+    return clustered_edges(seed, n, 8, random_edges, 1293861 / random_edges / 0.875, zipf_exponent=zipf_exponent)
 
 
 def power_law_edges(seed: int, n_nodes: int, n_edges: int, exponent: float = 2.1):
