@@ -447,11 +447,17 @@ def weak_scaling_step(rank, world, dev):
 class OpBuffers:
     """Device tensors of one input set for direct C-ABI calls (nothing allocated inside the timing)."""
 
-    def __init__(self, graph, dtype, seed, with_bias=True, want_dbias=True):
+    def __init__(self, graph, dtype, seed, with_bias=True, want_dbias=True, woven_kv=False):
         from torchgt_b200 import _cabi
         dev = graph.device
         n, e = graph.n_rows, graph.n_edges
         self.q, self.k, self.v, self.dout, bias = make_inputs(n, e, dtype, seed, dev)
+        self.row_bytes = HEADS * HEAD_DIM * self.q.element_size()
+        self.kv_row_bytes = self.row_bytes
+        if woven_kv:   # K and V of a row side by side, as the sequence-parallel exchange can deliver them
+            self.kv = torch.stack([self.k, self.v], dim=1).contiguous()        # [n, 2, H, D]
+            self.k, self.v = self.kv[:, 0], self.kv[:, 1]
+            self.kv_row_bytes = 2 * self.row_bytes
         self.bias = bias if with_bias else None
         self.out = torch.empty_like(self.q)
         self.z = torch.empty(n, HEADS, dtype=torch.float32, device=dev)
@@ -473,19 +479,20 @@ class OpBuffers:
         from torchgt_b200 import _cabi
         lib = _cabi.load()
         p = lambda t: None if t is None else t.data_ptr()
-        _cabi.check(lib.tgt_sparse_attn_fwd(p(self.q), p(self.k), p(self.v), p(self.bias), 1 if self.bias is not None else 0,
-                                            self.graph.by_dst.byref(), p(self.out), p(self.z), HEADS, HEAD_DIM,
-                                            self.code, p(self.scratch_f), self.scratch_f.numel(), stream))
+        _cabi.check(lib.tgt_sparse_attn_fwd_strided(
+            p(self.q), self.row_bytes, p(self.k), p(self.v), self.kv_row_bytes, p(self.bias),
+            1 if self.bias is not None else 0, self.graph.by_dst.byref(), p(self.out), p(self.z), HEADS, HEAD_DIM,
+            self.code, p(self.scratch_f), self.scratch_f.numel(), stream))
 
     def bwd(self, stream, passes):
         from torchgt_b200 import _cabi
         lib = _cabi.load()
         p = lambda t: None if t is None else t.data_ptr()
-        _cabi.check(lib.tgt_sparse_attn_bwd_passes(
-            p(self.dout), p(self.q), p(self.k), p(self.v), p(self.bias), 1 if self.bias is not None else 0,
-            p(self.out), p(self.z), self.graph.by_dst.byref(), self.graph.by_src.byref(), p(self.dq), p(self.dk),
-            p(self.dv), p(self.dbias), HEADS, HEAD_DIM, self.code, p(self.scratch_b), self.scratch_b.numel(),
-            stream, passes))
+        _cabi.check(lib.tgt_sparse_attn_bwd_strided(
+            p(self.dout), self.row_bytes, p(self.q), self.row_bytes, p(self.k), p(self.v), self.kv_row_bytes,
+            p(self.bias), 1 if self.bias is not None else 0, p(self.out), p(self.z), self.graph.by_dst.byref(),
+            self.graph.by_src.byref(), p(self.dq), p(self.dk), p(self.dv), p(self.dbias), HEADS, HEAD_DIM, self.code,
+            p(self.scratch_b), self.scratch_b.numel(), stream, passes))
 
 
 def capture(fn):

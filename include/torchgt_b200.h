@@ -79,6 +79,16 @@ TGT_API const char* tgt_last_error(void);
 TGT_API int tgt_debug_set_tile_edges(int edges_per_lane_group);
 
 /*
+ * Tuning / test knob with no counterpart in the reference: how many bytes of a row one lane of the
+ * attention kernels moves.  0 (default): the library chooses per head size; 1: 16 bytes (one 128-bit
+ * load per piece); 2: 32 bytes wherever it applies — fp32 heads of 32, 64 or 128 bytes in 32-byte
+ * aligned tensors — using the 256-bit global loads and stores of sm_100, so that a head of 8 fp32
+ * values is one lane and one load.  Results agree to rounding (the order of sums inside a head
+ * differs).  Process-wide.
+ */
+TGT_API int tgt_debug_set_lane_mode(int mode);
+
+/*
  * Bytes of device workspace tgt_edge_layout_build needs.
  * Replaces nothing in the reference (the reference keeps edges as an unsorted COO list).
  */
@@ -159,6 +169,20 @@ TGT_API int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, con
                         int head_dim, int dtype, void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * The same forward for q, k, v whose rows are not densely packed: q_row_bytes and kv_row_bytes are
+ * the distances between consecutive rows of q and of k / v (multiples of 16, at least heads *
+ * head_dim elements).  With k and v stored side by side per row ([n_rows, 2, heads * head_dim]:
+ * v = k + one row width, kv_row_bytes = two row widths — what TGT_PUSH_WOVEN delivers) the K and V
+ * pieces of an edge share their cache lines.  out and z are dense.  No counterpart in the reference
+ * (its tensors are always contiguous copies: gt_sp/layer.py:41,45).
+ */
+TGT_API int tgt_sparse_attn_fwd_strided(const void* q, int64_t q_row_bytes, const void* k,
+                                        const void* v, int64_t kv_row_bytes, const float* bias,
+                                        int bias_heads, const tgt_layout* by_dst, void* out,
+                                        float* z, int heads, int head_dim, int dtype, void* scratch,
+                                        size_t scratch_bytes, void* stream);
+
+/*
  * Forward for callers that cannot allocate.  No counterpart in the reference.
  *
  * tgt_sparse_attn_fwd needs scratch from its caller.  Some callers have none to give and may not
@@ -214,6 +238,20 @@ TGT_API int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const vo
                                        const tgt_layout* by_src, void* dq, void* dk, void* dv,
                                        float* dbias, int heads, int head_dim, int dtype,
                                        void* scratch, size_t scratch_bytes, void* stream, int passes);
+
+/*
+ * tgt_sparse_attn_bwd_passes for inputs whose rows are not densely packed (see
+ * tgt_sparse_attn_fwd_strided): row distances of dout, of q and of k / v in bytes.  dq, dk, dv, out
+ * and z are dense.  passes = 0 runs what is needed (6, or 7 when dbias is wanted).
+ */
+TGT_API int tgt_sparse_attn_bwd_strided(const void* dout, int64_t dout_row_bytes, const void* q,
+                                        int64_t q_row_bytes, const void* k, const void* v,
+                                        int64_t kv_row_bytes, const float* bias, int bias_heads,
+                                        const void* out, const float* z, const tgt_layout* by_dst,
+                                        const tgt_layout* by_src, void* dq, void* dk, void* dv,
+                                        float* dbias, int heads, int head_dim, int dtype,
+                                        void* scratch, size_t scratch_bytes, void* stream,
+                                        int passes);
 
 /*
  * Ulysses head<->sequence exchange: local re-layout kernels around ONE all-to-all.

@@ -23,6 +23,10 @@ Outputs (all small .npz files, committed):
                  nodes): output, loss and the gradient of one copy of the loss
   graphormer_graph_level.npz  the reference's graph-level Graphormer, one rank (3 padded graphs of 40 nodes,
                  graph token at index 0 of each): output, loss, parameter gradients
+  batching_P2.npz  get_batch_reorder_blockize on two ranks (full and last batches, Graphormer and GT, with and
+                 without cluster-sparse blocks), gen_sub_edge_index, generate_new_edges_optimized, reformat_graph;
+                 the three torch_geometric.utils calls and the METIS partitioner are stand-ins (see
+                 install_batching_shims), everything else is the reference's own code
   graphormer_graph_level_P2.npz  the same model on two ranks (every rank's own graph token in front of its
                  20 nodes of each graph): per-rank outputs and per-rank parameter gradients
 """
@@ -586,17 +590,142 @@ def make_gt_cases(ref_path):
              nprocs=2, join=True)
 
 
+def install_batching_shims(k_hint=None):
+    """Working stand-ins for what gt_sp/utils.py needs to build a batch: the three torch_geometric.utils
+    calls (torch-geometric 2.0.0 behaviour, restated) and a deterministic partitioner in place of dgl's
+    METIS (node i of an n-node graph goes to partition ((13 i) mod n) * k // n)."""
+    install_shims()
+    tgu = sys.modules["torch_geometric.utils"]
+
+    def remove_self_loops(edge_index, edge_attr=None):
+        mask = edge_index[0] != edge_index[1]
+        return edge_index[:, mask], None
+
+    def add_self_loops(edge_index, edge_attr=None, fill_value=None, num_nodes=None):
+        loops = torch.arange(num_nodes, dtype=torch.long).unsqueeze(0).repeat(2, 1)
+        return torch.cat([edge_index, loops], dim=1), None
+
+    def subgraph(subset, edge_index, edge_attr=None, relabel_nodes=False, num_nodes=None):
+        n_mask = torch.zeros(num_nodes, dtype=torch.bool)
+        n_mask[subset] = 1
+        mask = n_mask[edge_index[0]] & n_mask[edge_index[1]]
+        edge_index = edge_index[:, mask]
+        if relabel_nodes:
+            n_idx = torch.zeros(num_nodes, dtype=torch.long)
+            n_idx[subset] = torch.arange(subset.size(0))
+            edge_index = n_idx[edge_index]
+        return edge_index, None
+
+    tgu.remove_self_loops, tgu.add_self_loops, tgu.subgraph = remove_self_loops, add_self_loops, subgraph
+    dgl = sys.modules["dgl"]
+
+    class _Graph:
+        def __init__(self, pair):
+            self.n = int(max(int(pair[0].max()), int(pair[1].max()))) + 1
+
+        def num_nodes(self):
+            return self.n
+
+    dgl.graph = lambda pair: _Graph(pair)
+    dgl.metis_partition_assignment = lambda g, k: ((torch.arange(g.n) * 13) % g.n) * k // g.n
+
+
+def golden_partition(edge_index, num_nodes, k):
+    """The partitioner the batching goldens were made with (see install_batching_shims)."""
+    return ((torch.arange(num_nodes) * 13) % num_nodes) * k // num_nodes
+
+
+BATCH_CASES = [
+    # name, model, nodes of the whole graph, seq_len, batch size (== seq_len: full batch; smaller: last batch).
+    # All with args.reorder = True: without it the reference's function stops on an unassigned variable
+    # (gt_sp/utils.py:511 reads attn_bias, which only the reorder branch sets).
+    ("graphormer_blocks", "graphormer", 200, 96, 96),
+    ("graphormer_blocks_last", "graphormer", 200, 96, 71),
+    ("gt_blocks", "gt", 200, 96, 96),
+    ("gt_blocks_last", "gt", 200, 96, 70),
+]
+
+
+def _batch_worker(rank, world, ref_path, port, out_path):
+    """get_batch_reorder_blockize of the reference on `world` gloo ranks: per case and rank the feature and
+    label slice, the edge list and the last-batch flag; plus gen_sub_edge_index and reformat_graph on their own."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ref_path)
+    install_batching_shims()
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import gt_sp.initialize as init
+    import gt_sp.utils as ref
+    init._GLOBAL_TOKEN_NUM = 1
+    init.initialize_sequence_parallel(96, 1, 1, world)
+    rec = {}
+    for name, model, n_all, seq_len, batch in BATCH_CASES:
+        gen = torch.Generator().manual_seed(sum(map(ord, name)))
+        edge_index = torch.randint(0, n_all, (2, 6 * n_all), generator=gen)
+        x = torch.randn(n_all, 5, generator=gen)
+        y = torch.randint(0, 7, (n_all,), generator=gen)
+        idx_batch = torch.randperm(n_all, generator=gen)[:batch]
+        rest = None
+        if batch < seq_len:
+            base, extra = divmod(batch, world)
+            rest = [base + (1 if r < extra else 0) for r in range(world)]
+        args = types.SimpleNamespace(seq_len=seq_len, model=model, reorder=True, rank=rank)
+        x_i, y_i, ei_i, bias = ref.get_batch_reorder_blockize(args, x, y, idx_batch, rest, "cpu", edge_index, n_all, 3, 4)
+        assert bias is None
+        rec.update({f"{name}/in_edge_index": edge_index.numpy(), f"{name}/in_x": x.numpy(), f"{name}/in_y": y.numpy(),
+                    f"{name}/in_idx_batch": idx_batch.numpy(),
+                    f"{name}/in_rest": np.asarray(rest if rest is not None else [], dtype=np.int64),
+                    f"{name}/r{rank}/x": x_i.numpy(), f"{name}/r{rank}/y": y_i.numpy(),
+                    f"{name}/r{rank}/edge_index": ei_i.numpy(),
+                    f"{name}/r{rank}/last_batch": np.int64(int(init.get_last_batch_flag()))})
+        if rank == 0:
+            rec[f"{name}/sub_edge_index"] = ref.gen_sub_edge_index(edge_index, idx_batch, n_all).numpy()
+    if rank == 0:   # the block generator on its own, both of its branches
+        gen = torch.Generator().manual_seed(77)
+        n, k, bs = 300, 4, 4
+        ei = torch.randint(0, n, (2, 2500), generator=gen)
+        part = ((torch.arange(n) * 13) % n) * k // n
+        mapping = np.empty(n, dtype=np.int64)
+        cur = 0
+        for pid in range(k):
+            nodes = np.where(part.numpy() == pid)[0]
+            mapping[nodes] = np.arange(cur, cur + len(nodes))
+            cur += len(nodes)
+        rec["blocks/edge_index"], rec["blocks/partition"], rec["blocks/mapping"] = ei.numpy(), part.numpy(), mapping
+        rec["blocks/p1"] = ref.generate_new_edges_optimized(ei, k, part, 1, bs, mapping).numpy()
+        rec["blocks/p002"] = ref.generate_new_edges_optimized(ei, k, part, 0.02, bs, mapping).numpy()
+        new_edges, order = ref.reformat_graph(ei, k, bs)
+        rec["blocks/reformat_edges"], rec["blocks/reformat_order"] = new_edges.numpy(), order.numpy()
+    gathered = [None] * world
+    dist.all_gather_object(gathered, rec)
+    if rank == 0:
+        flat = {}
+        for g in gathered:
+            flat.update(g)
+        np.savez_compressed(out_path, **flat)
+        print("wrote", out_path)
+    dist.destroy_process_group()
+
+
+def make_batch_cases(ref_path):
+    import torch.multiprocessing as mp
+    mp.spawn(_batch_worker, args=(2, ref_path, 29651, str(OUT_DIR / "batching_P2.npz")), nprocs=2, join=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of zxmeng98/torchgt")
     ap.add_argument("--only", default="", help="'gt' regenerates the GT and graph-level model files only, "
-                                               "'p8' the eight-rank exchange and layer files only")
+                                               "'p8' the eight-rank exchange and layer files only, 'batching' the batch-construction file only")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     install_shims()
     torch.set_num_threads(1)
     if args.only == "gt":
         make_gt_cases(args.reference)
+        return
+    if args.only == "batching":
+        make_batch_cases(args.reference)
         return
     if args.only == "p8":
         make_ulysses_cases(args.reference, worlds=(8,))
@@ -608,6 +737,7 @@ def main():
     make_model_case(args.reference)
     make_variant_cases(args.reference)
     make_gt_cases(args.reference)
+    make_batch_cases(args.reference)
 
 
 if __name__ == "__main__":

@@ -9,10 +9,15 @@ from oracle import sparse_attn_oracle as sao
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True)
-def _automatic_tile_size():
+@pytest.fixture(autouse=True, params=[1, 2], ids=["lanes16", "lanes32"])
+def _lane_widths(request):
+    """Every test of this file runs with both lane widths of the walk kernels forced: 16 bytes, and 32
+    bytes wherever they apply (fp32 heads of 32 to 128 bytes; other shapes fall back to 16).  The
+    library's own choice per head size is one of the two; the other test files run with that choice."""
     from torchgt_b200 import _cabi
-    yield
+    _cabi.check(_cabi.load().tgt_debug_set_lane_mode(request.param))
+    yield request.param
+    _cabi.check(_cabi.load().tgt_debug_set_lane_mode(0))
     _cabi.check(_cabi.load().tgt_debug_set_tile_edges(0))
 
 
@@ -357,3 +362,54 @@ def test_many_small_random_graphs_with_forced_tile_sizes():
             ref = dt if str(kind) == "edge_head" else dt.sum(axis=1)
             err = np.abs(res["dbias"].double().cpu().numpy() - ref).max()
             assert err < TOL_F32 * float(np.abs(ref).max()) + floor, ("dbias", err, ctx)
+
+
+@pytest.mark.parametrize("heads,head_dim,dtype", [(1, 8, torch.float32), (2, 8, torch.float32), (8, 8, torch.float32),
+                                                  (8, 8, torch.bfloat16), (4, 16, torch.float32)])
+def test_strided_rows_k_and_v_side_by_side_give_the_same_bits(heads, head_dim, dtype):
+    """tgt_sparse_attn_fwd_strided / _bwd_strided: q and dO with padded rows, K and V of a row stored side by
+    side ([N, 2, H, D], what the woven push of the exchange delivers).  Only addresses change, so every
+    result must equal the dense call bit for bit."""
+    import ctypes
+    from torchgt_b200 import SparseGraph, _cabi
+    lib = _cabi.load()
+    n = 700
+    ei = random_graph(31 + heads, n, 6.0)
+    graph = SparseGraph(ei.cuda(), n)
+    gen = torch.Generator().manual_seed(heads + head_dim)
+    q, k, v, dout = (torch.randn(n, heads, head_dim, generator=gen).to(dtype).cuda() for _ in range(4))
+    bias = (torch.randn(ei.shape[1], generator=gen) * 0.2).cuda()
+    code = _cabi.TGT_F32 if dtype == torch.float32 else _cabi.TGT_BF16
+    es = q.element_size()
+    row = heads * head_dim * es
+    kv = torch.stack([k, v], dim=1).contiguous()                       # [n, 2, H, D]
+    q_pad = torch.zeros(n, 2 * heads, head_dim, dtype=dtype, device="cuda"); q_pad[:, :heads] = q
+    do_pad = torch.zeros(n, 3 * heads, head_dim, dtype=dtype, device="cuda"); do_pad[:, :heads] = dout
+    stream = torch.cuda.current_stream().cuda_stream
+    _cabi.check(lib.tgt_debug_set_tile_edges(8))
+    nb = ctypes.c_size_t()
+    results = []
+    for (qq, q_row, kk, vv, kv_row, dd, d_row) in ((q, row, k, v, row, dout, row),
+                                                   (q_pad, 2 * row, kv[:, 0], kv[:, 1], 2 * row, do_pad, 3 * row)):
+        out, z = torch.empty_like(q), torch.empty(n, heads, device="cuda")
+        dq, dk, dv, dbias = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q), torch.empty_like(bias)
+        _cabi.check(lib.tgt_sparse_attn_scratch_bytes(graph.by_dst.byref(), graph.by_src.byref(), heads, head_dim,
+                                                      code, 1, ctypes.byref(nb)))
+        scratch = torch.empty(max(nb.value, 16), dtype=torch.uint8, device="cuda")
+        _cabi.check(lib.tgt_sparse_attn_fwd_strided(qq.data_ptr(), q_row, kk.data_ptr(), vv.data_ptr(), kv_row,
+                                                    bias.data_ptr(), 1, graph.by_dst.byref(), out.data_ptr(),
+                                                    z.data_ptr(), heads, head_dim, code, scratch.data_ptr(),
+                                                    scratch.numel(), stream))
+        _cabi.check(lib.tgt_sparse_attn_bwd_strided(dd.data_ptr(), d_row, qq.data_ptr(), q_row, kk.data_ptr(),
+                                                    vv.data_ptr(), kv_row, bias.data_ptr(), 1, out.data_ptr(),
+                                                    z.data_ptr(), graph.by_dst.byref(), graph.by_src.byref(),
+                                                    dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dbias.data_ptr(),
+                                                    heads, head_dim, code, scratch.data_ptr(), scratch.numel(), stream,
+                                                    0))
+        torch.cuda.synchronize()
+        results.append((out, z, dq, dk, dv, dbias))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    # and they are right
+    ref_out, _ = sao.forward_closed_form(q.float(), k.float(), v.float(), ei, bias)
+    assert rel_err(results[1][0].float(), ref_out) < (TOL_F32 if dtype == torch.float32 else TOL_BF16)

@@ -63,6 +63,13 @@ SIGNATURES = {
     "tgt_sparse_attn_scratch_bytes": (c_int, [_PL, _PL, c_int, c_int, c_int, c_int, POINTER(c_size_t)]),
     "tgt_sparse_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, _PL, c_void_p,
                                     c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "tgt_sparse_attn_fwd_strided": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int, _PL,
+                                            c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "tgt_sparse_attn_bwd_strided": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                            c_void_p, c_int, c_void_p, c_void_p, _PL, _PL, c_void_p, c_void_p,
+                                            c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p,
+                                            c_int]),
+    "tgt_debug_set_lane_mode": (c_int, [c_int]),
     "tgt_sparse_attn_fwd_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, _PL, c_void_p,
                                             c_void_p, c_int, c_int, c_int, c_void_p]),
     "tgt_sparse_attn_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,

@@ -38,6 +38,19 @@ namespace tgt {
 #ifndef TGT_STITCH_KERNEL_MAX_G
 #define TGT_STITCH_KERNEL_MAX_G 4
 #endif
+// Which walks use 32-byte lanes when nobody forces a lane width (see lane_bytes()).  Measured on B200
+// (fp32, 8-float heads, 64K-node batches and their 2-, 4- and 8-rank head slices): the forward and the dQ
+// pass gain on rows of 128 to 256 bytes (forward 55 -> 50 us, dQ 72 -> 62 us on 128-byte rows; dQ with
+// dbias 68 -> 65 us on 256-byte rows), the dQ pass also on 64-byte rows (86 -> 80 us); both lose on
+// 32-byte rows, and the dK/dV pass, with twice the accumulators per lane, loses 10-40 % everywhere.
+#ifndef TGT_WIDE_DEFAULT
+#define TGT_WIDE_DEFAULT(pass, row_bytes) \
+  ((pass) != kPassDkv && (row_bytes) <= 256 && (row_bytes) >= ((pass) == kPassDq ? 64 : 128))
+#endif
+// Edges per batch of the walk with 32-byte lanes (their operands take twice the registers).
+#ifndef TGT_WIDE_UNROLL
+#define TGT_WIDE_UNROLL 2
+#endif
 #ifdef TGT_MIN_CTAS
 #define TGT_WALK_BOUNDS __launch_bounds__(128, TGT_MIN_CTAS)
 #else
@@ -52,10 +65,12 @@ constexpr int kGeStep = 4;           // ge is a multiple of this (and of every b
 // 256-byte rows; bf16 128-byte rows): batches of 4 edges are best everywhere except for fp32 rows of
 // 16 lanes (the 8 heads x 8 case, two lane groups per warp), where batches of 2 are 9-10 % faster
 // (64K benchmark step 176 -> 158 us, 870K step 5.11 -> 4.67 ms); narrower groups lose 20-70 % with 2.
-template <typename T, int G>
+template <typename T, int W, int G>
 constexpr int walk_unroll() {
+  if (W == 32) return TGT_WIDE_UNROLL;
   return (std::is_same<T, float>::value && G == 16 && TGT_UNROLL == 4) ? 2 : TGT_UNROLL;
 }
+static_assert(kGeStep % TGT_WIDE_UNROLL == 0, "ge must stay a multiple of the batch size");
 static_assert(kGeStep % TGT_UNROLL == 0, "ge must stay a multiple of the batch size");
 
 template <int G>
@@ -429,20 +444,39 @@ __device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol
 inline bool stitch_in_second_kernel(int g) { return g <= TGT_STITCH_KERNEL_MAX_G; }
 
 struct HeadSplit {
+  int w;       // bytes one lane moves: 16 or 32
   int lph;     // lanes per head
   int hpg;     // heads per lane group
   int g;       // lanes per group
   int groups;  // number of head groups (gridDim.y)
 };
 
-// Returns false when (heads, head_dim, dtype) cannot be mapped onto 16-byte lanes.
-inline bool split_heads(int heads, int head_dim, int dtype, HeadSplit* hs) {
-  const int vec = dtype == TGT_F32 ? 4 : 8;
+enum { kPassFwd = 0, kPassDq = 1, kPassDkv = 2 };
+
+// Lane width of the walk kernels: 0 = chosen by the library, 1 = 16-byte lanes, 2 = 32-byte lanes
+// wherever the head size allows.  Set by tgt_debug_set_lane_mode().
+int lane_mode();
+
+// Bytes per lane for heads of head_dim elements.  32-byte lanes need heads that are whole multiples of
+// 32 bytes and 32-byte aligned tensors and strides (`can32`).
+inline int lane_bytes(int heads, int head_dim, int dtype, bool can32, int pass) {
+  const int head_bytes = head_dim * (dtype == TGT_F32 ? 4 : 2);
+  if (!can32 || dtype != TGT_F32 || head_bytes % 32 != 0 || head_bytes > 128) return 16;
+  const int mode = lane_mode();
+  if (mode == 1) return 16;
+  if (mode == 2) return 32;
+  return TGT_WIDE_DEFAULT(pass, heads * head_bytes) ? 32 : 16;
+}
+
+// Returns false when (heads, head_dim, dtype) cannot be mapped onto lanes of w bytes.
+inline bool split_heads(int heads, int head_dim, int dtype, int w, HeadSplit* hs) {
+  const int vec = w / (dtype == TGT_F32 ? 4 : 2);
   if (heads < 1 || head_dim < vec || head_dim % vec != 0) return false;
   const int lph = head_dim / vec;
   if (lph > 32 || (lph & (lph - 1)) != 0) return false;
   int hpg = 1;
   while (hpg * 2 * lph <= 32 && heads % (hpg * 2) == 0) hpg *= 2;
+  hs->w = w;
   hs->lph = lph;
   hs->hpg = hpg;
   hs->g = lph * hpg;
@@ -450,37 +484,50 @@ inline bool split_heads(int heads, int head_dim, int dtype, HeadSplit* hs) {
   return true;
 }
 
-// Expands to `CALL(T, LPH, G)` for the run-time (dtype, lph, g) triple.
-#define TGT_DISPATCH_G(T, LPH, g, CALL)                            \
-  switch (g) {                                                     \
-    case 1: if constexpr (LPH <= 1) { CALL(T, LPH, 1); } break;    \
-    case 2: if constexpr (LPH <= 2) { CALL(T, LPH, 2); } break;    \
-    case 4: if constexpr (LPH <= 4) { CALL(T, LPH, 4); } break;    \
-    case 8: if constexpr (LPH <= 8) { CALL(T, LPH, 8); } break;    \
-    case 16: if constexpr (LPH <= 16) { CALL(T, LPH, 16); } break; \
-    case 32: if constexpr (LPH <= 32) { CALL(T, LPH, 32); } break; \
-    default: break;                                                \
-  }
+// Compile-time shape of one kernel instantiation: element type, bytes per lane, lanes per head, lanes
+// per group.
+template <typename T_, int W_, int LPH_, int G_>
+struct LaneShape {
+  using T = T_;
+  static constexpr int W = W_, LPH = LPH_, G = G_;
+};
 
-#define TGT_DISPATCH_LPH(T, lph, g, CALL)          \
-  switch (lph) {                                   \
-    case 1: TGT_DISPATCH_G(T, 1, g, CALL) break;   \
-    case 2: TGT_DISPATCH_G(T, 2, g, CALL) break;   \
-    case 4: TGT_DISPATCH_G(T, 4, g, CALL) break;   \
-    case 8: TGT_DISPATCH_G(T, 8, g, CALL) break;   \
-    case 16: TGT_DISPATCH_G(T, 16, g, CALL) break; \
-    case 32: TGT_DISPATCH_G(T, 32, g, CALL) break; \
-    default: break;                                \
+// Calls f(LaneShape<...>{}) for the run-time (dtype, w, lph, g); only shapes that can occur are
+// instantiated (a group holds whole heads: LPH <= G; 32-byte lanes are built for fp32 heads of up to
+// 128 bytes).  Returns false when the combination is not built.
+template <typename T, int W, int LPH, class F>
+inline bool dispatch_group(int g, F&& f) {
+  switch (g) {
+    case 1: if constexpr (LPH <= 1) { f(LaneShape<T, W, LPH, 1>{}); return true; } break;
+    case 2: if constexpr (LPH <= 2) { f(LaneShape<T, W, LPH, 2>{}); return true; } break;
+    case 4: if constexpr (LPH <= 4) { f(LaneShape<T, W, LPH, 4>{}); return true; } break;
+    case 8: if constexpr (LPH <= 8) { f(LaneShape<T, W, LPH, 8>{}); return true; } break;
+    case 16: if constexpr (LPH <= 16) { f(LaneShape<T, W, LPH, 16>{}); return true; } break;
+    case 32: if constexpr (LPH <= 32) { f(LaneShape<T, W, LPH, 32>{}); return true; } break;
+    default: break;
   }
+  return false;
+}
 
-#define TGT_DISPATCH(dtype, lph, g, CALL)           \
-  do {                                              \
-    if ((dtype) == TGT_F32) {                       \
-      TGT_DISPATCH_LPH(float, lph, g, CALL)         \
-    } else {                                        \
-      TGT_DISPATCH_LPH(__nv_bfloat16, lph, g, CALL) \
-    }                                               \
-  } while (0)
+template <typename T, int W, class F>
+inline bool dispatch_head(int lph, int g, F&& f) {
+  switch (lph) {
+    case 1: return dispatch_group<T, W, 1>(g, f);
+    case 2: return dispatch_group<T, W, 2>(g, f);
+    case 4: return dispatch_group<T, W, 4>(g, f);
+    case 8: if constexpr (W == 16) return dispatch_group<T, W, 8>(g, f); else break;
+    case 16: if constexpr (W == 16) return dispatch_group<T, W, 16>(g, f); else break;
+    case 32: if constexpr (W == 16) return dispatch_group<T, W, 32>(g, f); else break;
+    default: break;
+  }
+  return false;
+}
+
+template <class F>
+inline bool dispatch_shape(int dtype, int w, int lph, int g, F&& f) {
+  if (dtype == TGT_F32) return w == 32 ? dispatch_head<float, 32>(lph, g, f) : dispatch_head<float, 16>(lph, g, f);
+  return w == 16 ? dispatch_head<__nv_bfloat16, 16>(lph, g, f) : false;
+}
 
 int check_layout(const tgt_layout* L, const char* name);
 

@@ -10,7 +10,10 @@ namespace tgt {
 namespace {
 thread_local char g_error[512] = "";
 std::atomic<int> g_forced_ge{0};
+std::atomic<int> g_lane_mode{0};
 }  // namespace
+
+int lane_mode() { return g_lane_mode.load(std::memory_order_relaxed); }
 
 int set_error(int code, const char* fmt, ...) {
   va_list ap;
@@ -69,5 +72,11 @@ extern "C" const char* tgt_last_error(void) { return tgt::g_error; }
 extern "C" int tgt_debug_set_tile_edges(int edges_per_lane_group) {
   TGT_CHECK_ARG(edges_per_lane_group >= 0, "edges_per_lane_group must be >= 0");
   tgt::g_forced_ge.store(edges_per_lane_group, std::memory_order_relaxed);
+  return TGT_OK;
+}
+
+extern "C" int tgt_debug_set_lane_mode(int mode) {
+  TGT_CHECK_ARG(mode >= 0 && mode <= 2, "mode must be 0 (library's choice), 1 (16-byte lanes) or 2 (32-byte lanes)");
+  tgt::g_lane_mode.store(mode, std::memory_order_relaxed);
   return TGT_OK;
 }

@@ -32,6 +32,7 @@ struct BwdParams {
   float* dbias;
   float2* stats;  // [n_rows, heads]
   int heads, row_elems;
+  int64_t q_row_bytes, kv_row_bytes, g_row_bytes;   // distance between rows of q, of k / v and of dout
   int64_t n_rows;
   float inv_scale;
   SegWalk walk;
@@ -50,7 +51,8 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const BwdParams p) {
 #pragma unroll
   for (int j = 0; j < VEC; ++j) g[j] = o[j] = 0.f;
   if (live) {
-    Vec16<T>::load(static_cast<const T*>(p.dout) + idx * VEC, g);
+    const int64_t row = idx / chunks, col = idx % chunks;
+    Vec16<T>::load(reinterpret_cast<const T*>(static_cast<const char*>(p.dout) + row * p.g_row_bytes) + col * VEC, g);
     Vec16<T>::load(static_cast<const T*>(p.out) + idx * VEC, o);
   }
   const float delta = group_sum<LPH>(dot<VEC>(g, o));
@@ -63,11 +65,11 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const BwdParams p) {
 }
 
 // ---- pass A: dQ and dbias -----------------------------------------------------------------------
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 struct DqPolicy {
-  static constexpr int VEC = Vec16<T>::kElems;
+  static constexpr int VEC = Lane<T, W>::kElems;
   static constexpr int NACC = VEC;
-  static constexpr int kUnroll = walk_unroll<T, G>();
+  static constexpr int kUnroll = walk_unroll<T, W, G>();
 
   const T* __restrict__ q;
   const T* __restrict__ k;
@@ -78,12 +80,12 @@ struct DqPolicy {
   float* __restrict__ dbias;
   T* __restrict__ dq;
   int bias_stride, bias_off;
-  unsigned row_vecs, cvec;
+  unsigned row_vecs, cvec, q_vecs, kv_vecs, g_vecs;
   int heads, head;
   bool head_leader, group_leader;
   float inv_scale;
 
-  using Raw = typename Vec16<T>::Raw;
+  using Raw = typename Lane<T, W>::Raw;
   struct Operands {
     Raw k, v, q, g;  // packed 16-byte pieces, unpacked where they are used
     float2 st;
@@ -94,27 +96,26 @@ struct DqPolicy {
   };
 
   __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
-    const unsigned so = unsigned(src) * row_vecs + cvec;
-    const unsigned ro = unsigned(row) * row_vecs + cvec;
-    o.k = Vec16<T>::raw_at(k, so);
-    o.v = Vec16<T>::raw_at(v, so);
-    o.q = Vec16<T>::raw_at(q, ro);
-    o.g = Vec16<T>::raw_at(dout, ro);
+    const unsigned so = unsigned(src) * kv_vecs + cvec;
+    o.k = Lane<T, W>::raw_at(k, so);
+    o.v = Lane<T, W>::raw_at(v, so);
+    o.q = Lane<T, W>::raw_at(q, unsigned(row) * q_vecs + cvec);
+    o.g = Lane<T, W>::raw_at(dout, unsigned(row) * g_vecs + cvec);
     o.st = __ldg(stats + int64_t(row) * heads + head);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
   __device__ __forceinline__ void clear(Operands& o) const {
-    o.k = o.v = o.q = o.g = Vec16<T>::raw_zero();
+    o.k = o.v = o.q = o.g = Lane<T, W>::raw_zero();
     o.st = make_float2(0.f, 0.f);
     o.b = 0.f;
   }
   __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int pe) const {
     float a[VEC], b[VEC];
-    Vec16<T>::unpack(o.q, a);
-    Vec16<T>::unpack(o.k, b);
+    Lane<T, W>::unpack(o.q, a);
+    Lane<T, W>::unpack(o.k, b);
     const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
-    Vec16<T>::unpack(o.g, a);
-    Vec16<T>::unpack(o.v, b);
+    Lane<T, W>::unpack(o.g, a);
+    Lane<T, W>::unpack(o.v, b);
     const float gv = group_sum<LPH>(dot<VEC>(a, b));
     const float wgt = fast_exp(clamp_score(raw) + o.b);
     const float dt = valid ? (gv - o.st.y) * o.st.x * wgt : 0.f;
@@ -133,7 +134,7 @@ struct DqPolicy {
   __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
                                              const Scalars& s) const {
     float kf[VEC];
-    Vec16<T>::unpack(o.k, kf);
+    Lane<T, W>::unpack(o.k, kf);
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[j] = fmaf(s.da, kf[j], acc[j]);
   }
@@ -141,22 +142,22 @@ struct DqPolicy {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = acc[j] * inv_scale;
-    Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
+    Lane<T, W>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
   }
   __device__ __forceinline__ void zero_row(int row) const {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
+    Lane<T, W>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
   }
 };
 
 // ---- pass A without a statistics pre-pass (no dbias) ---------------------------------------------
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 struct DqFusedPolicy {
-  static constexpr int VEC = Vec16<T>::kElems;
+  static constexpr int VEC = Lane<T, W>::kElems;
   static constexpr int NACC = 2 * VEC + 1;  // A1, A2, S
-  static constexpr int kUnroll = walk_unroll<T, G>();
+  static constexpr int kUnroll = walk_unroll<T, W, G>();
 
   const T* __restrict__ q;
   const T* __restrict__ k;
@@ -167,12 +168,12 @@ struct DqFusedPolicy {
   float2* __restrict__ stats;
   T* __restrict__ dq;
   int bias_stride, bias_off;
-  unsigned row_vecs, cvec;
+  unsigned row_vecs, cvec, q_vecs, kv_vecs, g_vecs;
   int heads, head;
   bool head_leader;
   float inv_scale;
 
-  using Raw = typename Vec16<T>::Raw;
+  using Raw = typename Lane<T, W>::Raw;
   struct Operands {
     Raw k, v, q, g;
     float b;
@@ -182,25 +183,24 @@ struct DqFusedPolicy {
   };
 
   __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
-    const unsigned so = unsigned(src) * row_vecs + cvec;
-    const unsigned ro = unsigned(row) * row_vecs + cvec;
-    o.k = Vec16<T>::raw_at(k, so);
-    o.v = Vec16<T>::raw_at(v, so);
-    o.q = Vec16<T>::raw_at(q, ro);
-    o.g = Vec16<T>::raw_at(dout, ro);
+    const unsigned so = unsigned(src) * kv_vecs + cvec;
+    o.k = Lane<T, W>::raw_at(k, so);
+    o.v = Lane<T, W>::raw_at(v, so);
+    o.q = Lane<T, W>::raw_at(q, unsigned(row) * q_vecs + cvec);
+    o.g = Lane<T, W>::raw_at(dout, unsigned(row) * g_vecs + cvec);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
   __device__ __forceinline__ void clear(Operands& o) const {
-    o.k = o.v = o.q = o.g = Vec16<T>::raw_zero();
+    o.k = o.v = o.q = o.g = Lane<T, W>::raw_zero();
     o.b = 0.f;
   }
   __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
     float a[VEC], b[VEC];
-    Vec16<T>::unpack(o.q, a);
-    Vec16<T>::unpack(o.k, b);
+    Lane<T, W>::unpack(o.q, a);
+    Lane<T, W>::unpack(o.k, b);
     const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
-    Vec16<T>::unpack(o.g, a);
-    Vec16<T>::unpack(o.v, b);
+    Lane<T, W>::unpack(o.g, a);
+    Lane<T, W>::unpack(o.v, b);
     const float gv = group_sum<LPH>(dot<VEC>(a, b));
     const float wgt = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
     Scalars s;
@@ -212,7 +212,7 @@ struct DqFusedPolicy {
   __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
                                              const Scalars& s) const {
     float kf[VEC];
-    Vec16<T>::unpack(o.k, kf);
+    Lane<T, W>::unpack(o.k, kf);
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       acc[j] = fmaf(s.wgv_m, kf[j], acc[j]);
@@ -226,23 +226,23 @@ struct DqFusedPolicy {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = (acc[j] - delta * acc[VEC + j]) * (inv * inv_scale);
-    Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
+    Lane<T, W>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
     if (head_leader) stats[int64_t(row) * heads + head] = make_float2(inv, delta);
   }
   __device__ __forceinline__ void zero_row(int row) const {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    Vec16<T>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
+    Lane<T, W>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
   }
 };
 
 // ---- pass B: dK and dV --------------------------------------------------------------------------
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 struct DkvPolicy {
-  static constexpr int VEC = Vec16<T>::kElems;
+  static constexpr int VEC = Lane<T, W>::kElems;
   static constexpr int NACC = 2 * VEC;  // dK then dV
-  static constexpr int kUnroll = walk_unroll<T, G>();
+  static constexpr int kUnroll = walk_unroll<T, W, G>();
 
   const T* __restrict__ q;
   const T* __restrict__ k;
@@ -253,11 +253,11 @@ struct DkvPolicy {
   T* __restrict__ dk;
   T* __restrict__ dv;
   int bias_stride, bias_off;
-  unsigned row_vecs, cvec;
+  unsigned row_vecs, cvec, q_vecs, kv_vecs, g_vecs;
   int heads, head;
   float inv_scale;
 
-  using Raw = typename Vec16<T>::Raw;
+  using Raw = typename Lane<T, W>::Raw;
   struct Operands {
     Raw q, g, k, v;  // packed 16-byte pieces, unpacked where they are used
     float2 st;
@@ -269,27 +269,26 @@ struct DkvPolicy {
 
   // `row` is the source (K/V row), `dst` the destination whose Q, dO and statistics are gathered
   __device__ __forceinline__ void load(Operands& o, int row, int dst, int pe) const {
-    const unsigned d = unsigned(dst) * row_vecs + cvec;
-    const unsigned ro = unsigned(row) * row_vecs + cvec;
-    o.q = Vec16<T>::raw_at(q, d);
-    o.g = Vec16<T>::raw_at(dout, d);
-    o.k = Vec16<T>::raw_at(k, ro);
-    o.v = Vec16<T>::raw_at(v, ro);
+    const unsigned ro = unsigned(row) * kv_vecs + cvec;
+    o.q = Lane<T, W>::raw_at(q, unsigned(dst) * q_vecs + cvec);
+    o.g = Lane<T, W>::raw_at(dout, unsigned(dst) * g_vecs + cvec);
+    o.k = Lane<T, W>::raw_at(k, ro);
+    o.v = Lane<T, W>::raw_at(v, ro);
     o.st = __ldg(stats + int64_t(dst) * heads + head);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
   __device__ __forceinline__ void clear(Operands& o) const {
-    o.k = o.v = o.q = o.g = Vec16<T>::raw_zero();
+    o.k = o.v = o.q = o.g = Lane<T, W>::raw_zero();
     o.st = make_float2(0.f, 0.f);
     o.b = 0.f;
   }
   __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
     float a[VEC], b[VEC];
-    Vec16<T>::unpack(o.q, a);
-    Vec16<T>::unpack(o.k, b);
+    Lane<T, W>::unpack(o.q, a);
+    Lane<T, W>::unpack(o.k, b);
     const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
-    Vec16<T>::unpack(o.g, a);
-    Vec16<T>::unpack(o.v, b);
+    Lane<T, W>::unpack(o.g, a);
+    Lane<T, W>::unpack(o.v, b);
     const float gv = group_sum<LPH>(dot<VEC>(a, b));
     const float wgt = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
     const float dt = (gv - o.st.y) * o.st.x * wgt;
@@ -301,8 +300,8 @@ struct DkvPolicy {
   __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
                                              const Scalars& s) const {
     float qf[VEC], gf[VEC];
-    Vec16<T>::unpack(o.q, qf);
-    Vec16<T>::unpack(o.g, gf);
+    Lane<T, W>::unpack(o.q, qf);
+    Lane<T, W>::unpack(o.g, gf);
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       acc[j] = fmaf(s.da, qf[j], acc[j]);
@@ -317,24 +316,24 @@ struct DkvPolicy {
       b[j] = acc[VEC + j];
     }
     const unsigned off = unsigned(row) * row_vecs + cvec;
-    Vec16<T>::store_at(dk, off, a);
-    Vec16<T>::store_at(dv, off, b);
+    Lane<T, W>::store_at(dk, off, a);
+    Lane<T, W>::store_at(dv, off, b);
   }
   __device__ __forceinline__ void zero_row(int row) const {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = 0.f;
     const unsigned off = unsigned(row) * row_vecs + cvec;
-    Vec16<T>::store_at(dk, off, o);
-    Vec16<T>::store_at(dv, off, o);
+    Lane<T, W>::store_at(dk, off, o);
+    Lane<T, W>::store_at(dv, off, o);
   }
 };
 
-template <typename T, int LPH, int G>
-__device__ __forceinline__ DqPolicy<T, LPH, G> make_dq_policy(const BwdParams& p) {
-  constexpr int VEC = Vec16<T>::kElems;
+template <typename T, int W, int LPH, int G>
+__device__ __forceinline__ DqPolicy<T, W, LPH, G> make_dq_policy(const BwdParams& p) {
+  constexpr int VEC = Lane<T, W>::kElems;
   const int c = threadIdx.x % G;
-  DqPolicy<T, LPH, G> pol;
+  DqPolicy<T, W, LPH, G> pol;
   pol.q = static_cast<const T*>(p.q);
   pol.k = static_cast<const T*>(p.k);
   pol.v = static_cast<const T*>(p.v);
@@ -347,6 +346,9 @@ __device__ __forceinline__ DqPolicy<T, LPH, G> make_dq_policy(const BwdParams& p
   pol.bias_stride = p.bias_heads;
   pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
   pol.row_vecs = unsigned(p.row_elems / VEC);
+  pol.q_vecs = unsigned(p.q_row_bytes / W);
+  pol.kv_vecs = unsigned(p.kv_row_bytes / W);
+  pol.g_vecs = unsigned(p.g_row_bytes / W);
   pol.heads = p.heads;
   pol.cvec = blockIdx.y * G + c;
   pol.head_leader = c % LPH == 0;
@@ -355,11 +357,11 @@ __device__ __forceinline__ DqPolicy<T, LPH, G> make_dq_policy(const BwdParams& p
   return pol;
 }
 
-template <typename T, int LPH, int G>
-__device__ __forceinline__ DkvPolicy<T, LPH, G> make_dkv_policy(const BwdParams& p) {
-  constexpr int VEC = Vec16<T>::kElems;
+template <typename T, int W, int LPH, int G>
+__device__ __forceinline__ DkvPolicy<T, W, LPH, G> make_dkv_policy(const BwdParams& p) {
+  constexpr int VEC = Lane<T, W>::kElems;
   const int c = threadIdx.x % G;
-  DkvPolicy<T, LPH, G> pol;
+  DkvPolicy<T, W, LPH, G> pol;
   pol.q = static_cast<const T*>(p.q);
   pol.k = static_cast<const T*>(p.k);
   pol.v = static_cast<const T*>(p.v);
@@ -372,17 +374,20 @@ __device__ __forceinline__ DkvPolicy<T, LPH, G> make_dkv_policy(const BwdParams&
   pol.bias_stride = p.bias_heads;
   pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
   pol.row_vecs = unsigned(p.row_elems / VEC);
+  pol.q_vecs = unsigned(p.q_row_bytes / W);
+  pol.kv_vecs = unsigned(p.kv_row_bytes / W);
+  pol.g_vecs = unsigned(p.g_row_bytes / W);
   pol.heads = p.heads;
   pol.cvec = blockIdx.y * G + c;
   pol.inv_scale = p.inv_scale;
   return pol;
 }
 
-template <typename T, int LPH, int G>
-__device__ __forceinline__ DqFusedPolicy<T, LPH, G> make_dq_fused_policy(const BwdParams& p) {
-  constexpr int VEC = Vec16<T>::kElems;
+template <typename T, int W, int LPH, int G>
+__device__ __forceinline__ DqFusedPolicy<T, W, LPH, G> make_dq_fused_policy(const BwdParams& p) {
+  constexpr int VEC = Lane<T, W>::kElems;
   const int c = threadIdx.x % G;
-  DqFusedPolicy<T, LPH, G> pol;
+  DqFusedPolicy<T, W, LPH, G> pol;
   pol.q = static_cast<const T*>(p.q);
   pol.k = static_cast<const T*>(p.k);
   pol.v = static_cast<const T*>(p.v);
@@ -395,6 +400,9 @@ __device__ __forceinline__ DqFusedPolicy<T, LPH, G> make_dq_fused_policy(const B
   pol.bias_stride = p.bias_heads;
   pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
   pol.row_vecs = unsigned(p.row_elems / VEC);
+  pol.q_vecs = unsigned(p.q_row_bytes / W);
+  pol.kv_vecs = unsigned(p.kv_row_bytes / W);
+  pol.g_vecs = unsigned(p.g_row_bytes / W);
   pol.heads = p.heads;
   pol.cvec = blockIdx.y * G + c;
   pol.head_leader = c % LPH == 0;
@@ -402,50 +410,50 @@ __device__ __forceinline__ DqFusedPolicy<T, LPH, G> make_dq_fused_policy(const B
   return pol;
 }
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 __global__ void TGT_WALK_BOUNDS bwd_dq_fused_kernel(const BwdParams p) {
-  using Policy = DqFusedPolicy<T, LPH, G>;
+  using Policy = DqFusedPolicy<T, W, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
-  const Policy pol = make_dq_fused_policy<T, LPH, G>(p);
+  const Policy pol = make_dq_fused_policy<T, W, LPH, G>(p);
   walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 __global__ void TGT_WALK_BOUNDS bwd_dq_kernel(const BwdParams p) {
-  using Policy = DqPolicy<T, LPH, G>;
+  using Policy = DqPolicy<T, W, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
-  const Policy pol = make_dq_policy<T, LPH, G>(p);
+  const Policy pol = make_dq_policy<T, W, LPH, G>(p);
   walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 __global__ void TGT_WALK_BOUNDS bwd_dkv_kernel(const BwdParams p) {
-  using Policy = DkvPolicy<T, LPH, G>;
+  using Policy = DkvPolicy<T, W, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
-  const Policy pol = make_dkv_policy<T, LPH, G>(p);
+  const Policy pol = make_dkv_policy<T, W, LPH, G>(p);
   walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 __global__ void __launch_bounds__(kBlockThreads) bwd_dq_fused_stitch_kernel(const BwdParams p) {
-  using Policy = DqFusedPolicy<T, LPH, G>;
-  const Policy pol = make_dq_fused_policy<T, LPH, G>(p);
+  using Policy = DqFusedPolicy<T, W, LPH, G>;
+  const Policy pol = make_dq_fused_policy<T, W, LPH, G>(p);
   __shared__ float s_part[kBlockThreads * Policy::NACC];
   stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 __global__ void __launch_bounds__(kBlockThreads) bwd_dq_stitch_kernel(const BwdParams p) {
-  using Policy = DqPolicy<T, LPH, G>;
-  const Policy pol = make_dq_policy<T, LPH, G>(p);
+  using Policy = DqPolicy<T, W, LPH, G>;
+  const Policy pol = make_dq_policy<T, W, LPH, G>(p);
   __shared__ float s_part[kBlockThreads * Policy::NACC];
   stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 __global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const BwdParams p) {
-  using Policy = DkvPolicy<T, LPH, G>;
-  const Policy pol = make_dkv_policy<T, LPH, G>(p);
+  using Policy = DkvPolicy<T, W, LPH, G>;
+  const Policy pol = make_dkv_policy<T, W, LPH, G>(p);
   __shared__ float s_part[kBlockThreads * Policy::NACC];
   stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
@@ -453,20 +461,18 @@ __global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const Bwd
 enum { kWalkDq = 0, kWalkDkv = 1, kWalkDqFused = 2 };
 
 int bwd_resident_ctas(int dtype, const HeadSplit& hs, int which) {
-  static int cache[kMaxDevices][3][2][6][6] = {};   // occupancy is a property of the device
+  static int cache[kMaxDevices][2][3][2][6][6] = {};   // occupancy is a property of the device
   auto log2i = [](int x) { int l = 0; while ((1 << l) < x) ++l; return l; };
   const int dev = current_device();
-  int* slot = &cache[dev < 0 ? 0 : dev][which][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
+  int* slot = &cache[dev < 0 ? 0 : dev][hs.w == 32 ? 1 : 0][which][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
   int result = 4;
-#define TGT_OCC_DQ(T, LPH, G) result = resident_ctas(bwd_dq_kernel<T, LPH, G>, slot)
-#define TGT_OCC_DKV(T, LPH, G) result = resident_ctas(bwd_dkv_kernel<T, LPH, G>, slot)
-#define TGT_OCC_DQF(T, LPH, G) result = resident_ctas(bwd_dq_fused_kernel<T, LPH, G>, slot)
-  if (which == kWalkDkv) TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DKV);
-  else if (which == kWalkDqFused) TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DQF);
-  else TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_DQ);
-#undef TGT_OCC_DQ
-#undef TGT_OCC_DKV
-#undef TGT_OCC_DQF
+  dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
+    using S = decltype(sh);
+    using T = typename S::T;
+    if (which == kWalkDkv) result = resident_ctas(bwd_dkv_kernel<T, S::W, S::LPH, S::G>, slot);
+    else if (which == kWalkDqFused) result = resident_ctas(bwd_dq_fused_kernel<T, S::W, S::LPH, S::G>, slot);
+    else result = resident_ctas(bwd_dq_kernel<T, S::W, S::LPH, S::G>, slot);
+  });
   return result;
 }
 
@@ -475,12 +481,15 @@ struct BwdScratch {
   TilePlan plan_a, plan_a_fused, plan_b;
 };
 
-BwdScratch plan_bwd_scratch(const tgt_layout* by_dst, const HeadSplit& hs, int heads, int dtype) {
+// hs: lane layout of pass A (by destination), hsb: of pass B (by source); they may use different lane widths
+BwdScratch plan_bwd_scratch(const tgt_layout* by_dst, const HeadSplit& hs, const HeadSplit& hsb, int heads,
+                            int dtype) {
   BwdScratch s;
-  const int vec = dtype == TGT_F32 ? 4 : 8;
+  const int vec = hs.w / (dtype == TGT_F32 ? 4 : 2);
+  const int vecb = hsb.w / (dtype == TGT_F32 ? 4 : 2);
   s.plan_a = plan_tiles(by_dst->n_edges, hs, vec, bwd_resident_ctas(dtype, hs, kWalkDq));
   s.plan_a_fused = plan_tiles(by_dst->n_edges, hs, 2 * vec + 1, bwd_resident_ctas(dtype, hs, kWalkDqFused));
-  s.plan_b = plan_tiles(by_dst->n_edges, hs, 2 * vec, bwd_resident_ctas(dtype, hs, kWalkDkv));
+  s.plan_b = plan_tiles(by_dst->n_edges, hsb, 2 * vecb, bwd_resident_ctas(dtype, hsb, kWalkDkv));
   size_t off = 0;
   s.stats = off; off += round_up(size_t(by_dst->n_rows) * heads * 8, 256);
   s.carry_a = off;
@@ -522,7 +531,7 @@ extern "C" int tgt_sparse_attn_scratch_bytes(const tgt_layout* by_dst, const tgt
   int rc = check_layout(by_dst, "by_dst");
   if (rc != TGT_OK) return rc;
   HeadSplit hs;
-  if (!split_heads(heads, head_dim, dtype, &hs))
+  if (!split_heads(heads, head_dim, dtype, 16, &hs))
     return set_error(TGT_ERR_UNSUPPORTED, "heads=%d head_dim=%d dtype=%d is not supported", heads,
                      head_dim, dtype);
   if (phase == 0) {
@@ -531,7 +540,19 @@ extern "C" int tgt_sparse_attn_scratch_bytes(const tgt_layout* by_dst, const tgt
   }
   rc = check_layout(by_src, "by_src");
   if (rc != TGT_OK) return rc;
-  *bytes = plan_bwd_scratch(by_dst, hs, heads, dtype).total;
+  // enough for whichever lane width the call ends up using (it depends on pointer alignment)
+  size_t need = 0;
+  for (int wa = 16; wa <= 32; wa += 16)
+    for (int wb = 16; wb <= 32; wb += 16) {
+      HeadSplit a, b;
+      if ((wa == 32 && lane_bytes(heads, head_dim, dtype, true, kPassDq) != 32) ||
+          (wb == 32 && lane_bytes(heads, head_dim, dtype, true, kPassDkv) != 32))
+        continue;
+      if (!split_heads(heads, head_dim, dtype, wa, &a) || !split_heads(heads, head_dim, dtype, wb, &b)) continue;
+      const size_t t = plan_bwd_scratch(by_dst, a, b, heads, dtype).total;
+      if (t > need) need = t;
+    }
+  *bytes = need;
   return TGT_OK;
 }
 
@@ -552,12 +573,29 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
                                           const void* out, const float* z, const tgt_layout* by_dst,
                                           const tgt_layout* by_src, void* dq, void* dk, void* dv,
                                           float* dbias, int heads, int head_dim, int dtype,
-                                          void* scratch, size_t scratch_bytes, void* stream_,
+                                          void* scratch, size_t scratch_bytes, void* stream,
                                           int passes) {
-  using namespace tgt;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(passes >= 1 && passes <= 7,
                 "passes is a bit mask: 1 = row-statistics pre-pass, 2 = dQ/dbias, 4 = dK/dV");
+  const int64_t row_bytes = int64_t(heads) * head_dim * (dtype == TGT_F32 ? 4 : 2);
+  return tgt_sparse_attn_bwd_strided(dout, row_bytes, q, row_bytes, k, v, row_bytes, bias, bias_heads,
+                                     out, z, by_dst, by_src, dq, dk, dv, dbias, heads, head_dim, dtype,
+                                     scratch, scratch_bytes, stream, passes);
+}
+
+extern "C" int tgt_sparse_attn_bwd_strided(const void* dout, int64_t dout_row_bytes, const void* q,
+                                           int64_t q_row_bytes, const void* k, const void* v,
+                                           int64_t kv_row_bytes, const float* bias, int bias_heads,
+                                           const void* out, const float* z, const tgt_layout* by_dst,
+                                           const tgt_layout* by_src, void* dq, void* dk, void* dv,
+                                           float* dbias, int heads, int head_dim, int dtype,
+                                           void* scratch, size_t scratch_bytes, void* stream_,
+                                           int passes) {
+  using namespace tgt;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (passes == 0) passes = dbias != nullptr ? 7 : 6;
+  TGT_CHECK_ARG(passes >= 1 && passes <= 7,
+                "passes is a bit mask: 1 = row-statistics pre-pass, 2 = dQ/dbias, 4 = dK/dV (0 = all that are needed)");
   TGT_CHECK_ARG(dtype == TGT_F32 || dtype == TGT_BF16, "dtype must be TGT_F32 or TGT_BF16");
   int rc = check_layout(by_dst, "by_dst");
   if (rc != TGT_OK) return rc;
@@ -565,8 +603,12 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
   if (rc != TGT_OK) return rc;
   TGT_CHECK_ARG(by_dst->n_rows == by_src->n_rows && by_dst->n_edges == by_src->n_edges,
                 "by_dst and by_src describe different graphs");
-  HeadSplit hs;
-  if (!split_heads(heads, head_dim, dtype, &hs))
+  const bool can32 = aligned32(dout) && aligned32(q) && aligned32(k) && aligned32(v) && aligned32(dq) &&
+                     aligned32(dk) && aligned32(dv) && dout_row_bytes % 32 == 0 && q_row_bytes % 32 == 0 &&
+                     kv_row_bytes % 32 == 0;
+  HeadSplit hs, hsb;   // lane layouts of pass A (dQ) and pass B (dK/dV)
+  if (!split_heads(heads, head_dim, dtype, lane_bytes(heads, head_dim, dtype, can32, kPassDq), &hs) ||
+      !split_heads(heads, head_dim, dtype, lane_bytes(heads, head_dim, dtype, can32, kPassDkv), &hsb))
     return set_error(TGT_ERR_UNSUPPORTED,
                      "heads=%d head_dim=%d dtype=%d: head_dim must be a power of two multiple of "
                      "16 bytes, at most 512 bytes per head",
@@ -581,16 +623,21 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
                      "<= 512 bytes, heads a power of two); pass a per-head bias instead");
   const int64_t n_rows = by_dst->n_rows, n_edges = by_dst->n_edges;
   if (n_rows == 0) return TGT_OK;
+  const size_t elem = dtype == TGT_F32 ? 4 : 2;
+  const int64_t row_bytes = int64_t(heads) * head_dim * int64_t(elem);
   TGT_CHECK_ARG(dout && q && k && v && z && dq && dk && dv, "tensor pointers must not be null");
   TGT_CHECK_ARG(out != nullptr || !(passes & 1), "out is needed by the row-statistics pre-pass (dbias)");
-  TGT_CHECK_ARG(uint64_t(n_rows) * uint64_t(heads) * head_dim * (dtype == TGT_F32 ? 4 : 2) / 16 <
-                    (uint64_t(1) << 32),
+  TGT_CHECK_ARG(dout_row_bytes >= row_bytes && q_row_bytes >= row_bytes && kv_row_bytes >= row_bytes &&
+                    dout_row_bytes % 16 == 0 && q_row_bytes % 16 == 0 && kv_row_bytes % 16 == 0,
+                "row strides must be multiples of 16 bytes and at least heads * head_dim elements");
+  int64_t widest = dout_row_bytes > q_row_bytes ? dout_row_bytes : q_row_bytes;
+  if (kv_row_bytes > widest) widest = kv_row_bytes;
+  TGT_CHECK_ARG(uint64_t(n_rows) * uint64_t(widest) / 16 < (uint64_t(1) << 32),
                 "tensors larger than 64 GiB are not supported");
   TGT_CHECK_ARG(aligned16(dout) && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) &&
                     aligned16(z) && aligned16(dq) && aligned16(dk) && aligned16(dv) &&
                     aligned16(bias) && aligned16(dbias) && aligned16(scratch),
                 "device pointers must be 16-byte aligned");
-  const size_t elem = dtype == TGT_F32 ? 4 : 2;
   const size_t tensor_bytes = size_t(n_rows) * heads * head_dim * elem;
   if (n_edges == 0) {  // no edges: all gradients vanish
     if (passes & 2) TGT_CHECK_CUDA(cudaMemsetAsync(dq, 0, tensor_bytes, stream));
@@ -600,7 +647,7 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
     }
     return TGT_OK;
   }
-  const BwdScratch sc = plan_bwd_scratch(by_dst, hs, heads, dtype);
+  const BwdScratch sc = plan_bwd_scratch(by_dst, hs, hsb, heads, dtype);
   if (scratch == nullptr || scratch_bytes < sc.total)
     return set_error(TGT_ERR_WORKSPACE, "scratch holds %zu bytes, %zu needed", scratch_bytes,
                      sc.total);
@@ -613,62 +660,66 @@ extern "C" int tgt_sparse_attn_bwd_passes(const void* dout, const void* q, const
   p.stats = reinterpret_cast<float2*>(base + sc.stats);
   p.heads = heads;
   p.row_elems = heads * head_dim;
+  p.q_row_bytes = q_row_bytes;
+  p.kv_row_bytes = kv_row_bytes;
+  p.g_row_bytes = dout_row_bytes;
   p.n_rows = n_rows;
   p.inv_scale = 1.0f / sqrtf(float(head_dim));
 
   if (passes & 1) {
+    // streaming pre-pass, always with 16-byte lanes
+    const int lph16 = head_dim / (dtype == TGT_F32 ? 4 : 8);
     const int64_t lanes = n_rows * (p.row_elems / (dtype == TGT_F32 ? 4 : 8));
     const unsigned blocks = unsigned((lanes + 255) / 256);
-#define TGT_LAUNCH_STATS(T, LPH, G) bwd_stats_kernel<T, LPH><<<blocks, 256, 0, stream>>>(p)
-    TGT_DISPATCH(dtype, hs.lph, hs.lph, TGT_LAUNCH_STATS);
-#undef TGT_LAUNCH_STATS
+    dispatch_shape(dtype, 16, lph16, lph16, [&](auto sh) {
+      using S = decltype(sh);
+      bwd_stats_kernel<typename S::T, S::LPH><<<blocks, 256, 0, stream>>>(p);
+    });
   }
-  const bool second_kernel = stitch_in_second_kernel(hs.g);
+  const bool second_kernel = stitch_in_second_kernel(hs.g);      // pass A
+  const bool second_kernel_b = stitch_in_second_kernel(hsb.g);   // pass B
   int* counters_a = second_kernel ? nullptr : reinterpret_cast<int*>(base + sc.counters);
-  int* counters_b = second_kernel ? nullptr
-                                  : reinterpret_cast<int*>(base + sc.counters + sc.counter_bytes -
-                                                           sc.plan_b.counter_bytes);
-  if ((passes & 6) && !second_kernel)
-    TGT_CHECK_CUDA(cudaMemsetAsync(counters_a, 0, sc.counter_bytes, stream));
+  int* counters_b = second_kernel_b ? nullptr
+                                    : reinterpret_cast<int*>(base + sc.counters + sc.counter_bytes -
+                                                             sc.plan_b.counter_bytes);
+  if ((passes & 6) && !(second_kernel && second_kernel_b))
+    TGT_CHECK_CUDA(cudaMemsetAsync(base + sc.counters, 0, sc.counter_bytes, stream));
+  // one walk kernel per pass, plus the kernel that finishes cross-tile rows when the lane group is narrow
+  bool built = true;
   if ((passes & 2) && dbias == nullptr) {
     // pass A that derives the row statistics itself (and leaves them in scratch for pass B)
     fill_walk(&p.walk, *by_dst, sc.plan_a_fused, reinterpret_cast<float*>(base + sc.carry_a), counters_a,
               bias != nullptr);
     const dim3 grid(sc.plan_a_fused.n_tiles, hs.groups);
-#define TGT_LAUNCH_DQF(T, LPH, G)                                                   \
-  do {                                                                              \
-    bwd_dq_fused_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
-    if (second_kernel && sc.plan_a_fused.n_tiles > 1)                               \
-      bwd_dq_fused_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
-  } while (0)
-    TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQF);
-#undef TGT_LAUNCH_DQF
+    built = dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
+      using S = decltype(sh);
+      bwd_dq_fused_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+      if (second_kernel && sc.plan_a_fused.n_tiles > 1)
+        bwd_dq_fused_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+    });
   } else if (passes & 2) {
     // pass A with per-edge dbias: uses the statistics of the pre-pass (stage 1)
     fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a), counters_a, true);
     const dim3 grid(sc.plan_a.n_tiles, hs.groups);
-#define TGT_LAUNCH_DQ(T, LPH, G)                                              \
-  do {                                                                        \
-    bwd_dq_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
-    if (second_kernel && sc.plan_a.n_tiles > 1)                               \
-      bwd_dq_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
-  } while (0)
-    TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DQ);
-#undef TGT_LAUNCH_DQ
+    built = dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
+      using S = decltype(sh);
+      bwd_dq_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+      if (second_kernel && sc.plan_a.n_tiles > 1)
+        bwd_dq_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+    });
   }
-  if (passes & 4) {
+  if (built && (passes & 4)) {
     fill_walk(&p.walk, *by_src, sc.plan_b, reinterpret_cast<float*>(base + sc.carry_b), counters_b,
               bias != nullptr);
-    const dim3 grid(sc.plan_b.n_tiles, hs.groups);
-#define TGT_LAUNCH_DKV(T, LPH, G)                                              \
-  do {                                                                         \
-    bwd_dkv_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
-    if (second_kernel && sc.plan_b.n_tiles > 1)                                \
-      bwd_dkv_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
-  } while (0)
-    TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_DKV);
-#undef TGT_LAUNCH_DKV
+    const dim3 grid(sc.plan_b.n_tiles, hsb.groups);
+    built = dispatch_shape(dtype, hsb.w, hsb.lph, hsb.g, [&](auto sh) {
+      using S = decltype(sh);
+      bwd_dkv_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+      if (second_kernel_b && sc.plan_b.n_tiles > 1)
+        bwd_dkv_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+    });
   }
+  if (!built) return set_error(TGT_ERR_UNSUPPORTED, "no kernel is built for this head layout");
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }

@@ -6,11 +6,11 @@
 namespace tgt {
 namespace {
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 struct FwdPolicy {
-  static constexpr int VEC = Vec16<T>::kElems;
+  static constexpr int VEC = Lane<T, W>::kElems;
   static constexpr int NACC = VEC + 1;  // w*V and, last, the sum of w
-  static constexpr int kUnroll = walk_unroll<T, G>();
+  static constexpr int kUnroll = walk_unroll<T, W, G>();
 
   const T* __restrict__ q;
   const T* __restrict__ k;
@@ -19,12 +19,13 @@ struct FwdPolicy {
   T* __restrict__ out;
   float* __restrict__ z;           // [n_rows, heads]
   int bias_stride, bias_off;
-  unsigned row_vecs, cvec;         // 16-byte units per row; this lane's unit inside a row
+  unsigned row_vecs, cvec;         // lane-wide units per (dense) row; this lane's unit inside a row
+  unsigned q_vecs, kv_vecs;        // row strides of q and of k / v in lane-wide units
   int heads, head;                 // head count; the head this lane belongs to
   bool z_writer;                   // one lane per head stores Z
   float inv_scale;
 
-  using Raw = typename Vec16<T>::Raw;
+  using Raw = typename Lane<T, W>::Raw;
   struct Operands {
     Raw k, v, q;  // packed 16-byte pieces, unpacked where they are used
     float b;
@@ -34,20 +35,20 @@ struct FwdPolicy {
   };
 
   __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
-    const unsigned so = unsigned(src) * row_vecs + cvec;
-    o.k = Vec16<T>::raw_at(k, so);
-    o.v = Vec16<T>::raw_at(v, so);
-    o.q = Vec16<T>::raw_at(q, unsigned(row) * row_vecs + cvec);
+    const unsigned so = unsigned(src) * kv_vecs + cvec;
+    o.k = Lane<T, W>::raw_at(k, so);
+    o.v = Lane<T, W>::raw_at(v, so);
+    o.q = Lane<T, W>::raw_at(q, unsigned(row) * q_vecs + cvec);
     o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
   }
   __device__ __forceinline__ void clear(Operands& o) const {
-    o.k = o.v = o.q = Vec16<T>::raw_zero();
+    o.k = o.v = o.q = Lane<T, W>::raw_zero();
     o.b = 0.f;
   }
   __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
     float qf[VEC], kf[VEC];
-    Vec16<T>::unpack(o.q, qf);
-    Vec16<T>::unpack(o.k, kf);
+    Lane<T, W>::unpack(o.q, qf);
+    Lane<T, W>::unpack(o.k, kf);
     const float raw = group_sum<LPH>(dot<VEC>(qf, kf)) * inv_scale;
     Scalars s;
     s.w = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
@@ -56,7 +57,7 @@ struct FwdPolicy {
   __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
                                              const Scalars& s) const {
     float vf[VEC];
-    Vec16<T>::unpack(o.v, vf);
+    Lane<T, W>::unpack(o.v, vf);
 #pragma unroll
     for (int j = 0; j < VEC; ++j) acc[j] = fmaf(s.w, vf[j], acc[j]);
     acc[VEC] += s.w;
@@ -66,14 +67,14 @@ struct FwdPolicy {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = acc[j] * inv;
-    Vec16<T>::store_at(out, unsigned(row) * row_vecs + cvec, o);
+    Lane<T, W>::store_at(out, unsigned(row) * row_vecs + cvec, o);
     if (z_writer) z[int64_t(row) * heads + head] = acc[VEC];
   }
   __device__ __forceinline__ void zero_row(int row) const {
     float o[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    Vec16<T>::store_at(out, unsigned(row) * row_vecs + cvec, o);
+    Lane<T, W>::store_at(out, unsigned(row) * row_vecs + cvec, o);
     if (z_writer) z[int64_t(row) * heads + head] = 0.f;
   }
 };
@@ -87,15 +88,16 @@ struct FwdParams {
   void* out;
   float* z;
   int heads, row_elems;
+  int64_t q_row_bytes, kv_row_bytes;   // distance between consecutive rows of q and of k / v
   float inv_scale;
   SegWalk walk;
 };
 
-template <typename T, int LPH, int G>
-__device__ __forceinline__ FwdPolicy<T, LPH, G> make_policy(const FwdParams& p) {
-  constexpr int VEC = Vec16<T>::kElems;
+template <typename T, int W, int LPH, int G>
+__device__ __forceinline__ FwdPolicy<T, W, LPH, G> make_policy(const FwdParams& p) {
+  constexpr int VEC = Lane<T, W>::kElems;
   const int c = threadIdx.x % G;
-  FwdPolicy<T, LPH, G> pol;
+  FwdPolicy<T, W, LPH, G> pol;
   pol.q = static_cast<const T*>(p.q);
   pol.k = static_cast<const T*>(p.k);
   pol.v = static_cast<const T*>(p.v);
@@ -106,6 +108,8 @@ __device__ __forceinline__ FwdPolicy<T, LPH, G> make_policy(const FwdParams& p) 
   pol.bias_stride = p.bias_heads;
   pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
   pol.row_vecs = unsigned(p.row_elems / VEC);
+  pol.q_vecs = unsigned(p.q_row_bytes / W);
+  pol.kv_vecs = unsigned(p.kv_row_bytes / W);
   pol.heads = p.heads;
   pol.cvec = blockIdx.y * G + c;
   pol.z_writer = c % LPH == 0;
@@ -113,32 +117,33 @@ __device__ __forceinline__ FwdPolicy<T, LPH, G> make_policy(const FwdParams& p) 
   return pol;
 }
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 __global__ void TGT_WALK_BOUNDS fwd_kernel(const FwdParams p) {
-  using Policy = FwdPolicy<T, LPH, G>;
+  using Policy = FwdPolicy<T, W, LPH, G>;
   __shared__ TileSmem<G, Policy::NACC> sm;
-  const Policy pol = make_policy<T, LPH, G>(p);
+  const Policy pol = make_policy<T, W, LPH, G>(p);
   walk_tile_in<G, Policy>(sm, p.walk, pol);
 }
 
-template <typename T, int LPH, int G>
+template <typename T, int W, int LPH, int G>
 __global__ void __launch_bounds__(kBlockThreads) fwd_stitch_kernel(const FwdParams p) {
-  using Policy = FwdPolicy<T, LPH, G>;
-  const Policy pol = make_policy<T, LPH, G>(p);
+  using Policy = FwdPolicy<T, W, LPH, G>;
+  const Policy pol = make_policy<T, W, LPH, G>(p);
   __shared__ float s_part[kBlockThreads * Policy::NACC];
   stitch_tiles<G, Policy>(p.walk, pol, s_part);
 }
 
-// Resident CTAs per SM of fwd_kernel<T, LPH, G> for the run-time triple.
+// Resident CTAs per SM of fwd_kernel<T, W, LPH, G> for the run-time triple.
 int fwd_resident_ctas(int dtype, const HeadSplit& hs) {
-  static int cache[kMaxDevices][2][6][6] = {};   // occupancy is a property of the device
+  static int cache[kMaxDevices][2][2][6][6] = {};   // occupancy is a property of the device
   auto log2i = [](int x) { int l = 0; while ((1 << l) < x) ++l; return l; };
   const int dev = current_device();
-  int* slot = &cache[dev < 0 ? 0 : dev][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
+  int* slot = &cache[dev < 0 ? 0 : dev][hs.w == 32 ? 1 : 0][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
   int result = 4;
-#define TGT_OCC_FWD(T, LPH, G) result = resident_ctas(fwd_kernel<T, LPH, G>, slot)
-  TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_OCC_FWD);
-#undef TGT_OCC_FWD
+  dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
+    using S = decltype(sh);
+    result = resident_ctas(fwd_kernel<typename S::T, S::W, S::LPH, S::G>, slot);
+  });
   return result;
 }
 
@@ -155,11 +160,23 @@ TilePlan plan_tiles(int64_t n_edges, const HeadSplit& hs, int nacc, int ctas_per
   return t;
 }
 
-size_t fwd_scratch_bytes(const tgt_layout* L, int heads, int head_dim, int dtype) {
+// Scratch of the forward for lanes of w bytes (0 when that width does not fit the heads).
+size_t fwd_scratch_bytes_w(const tgt_layout* L, int heads, int head_dim, int dtype, int w) {
   HeadSplit hs;
-  if (!split_heads(heads, head_dim, dtype, &hs) || L->n_edges == 0) return 0;
-  const int nacc = (dtype == TGT_F32 ? 4 : 8) + 1;
+  if (!split_heads(heads, head_dim, dtype, w, &hs) || L->n_edges == 0) return 0;
+  const int nacc = w / (dtype == TGT_F32 ? 4 : 2) + 1;
   return plan_tiles(L->n_edges, hs, nacc, fwd_resident_ctas(dtype, hs)).scratch_bytes;
+}
+
+// What a caller must provide: enough for whichever lane width the call ends up using (the width depends
+// on pointer alignment, which the size query does not see).
+size_t fwd_scratch_bytes(const tgt_layout* L, int heads, int head_dim, int dtype) {
+  size_t need = fwd_scratch_bytes_w(L, heads, head_dim, dtype, 16);
+  if (lane_bytes(heads, head_dim, dtype, true, kPassFwd) == 32) {
+    const size_t wide = fwd_scratch_bytes_w(L, heads, head_dim, dtype, 32);
+    if (wide > need) need = wide;
+  }
+  return need;
 }
 
 }  // namespace tgt
@@ -167,14 +184,26 @@ size_t fwd_scratch_bytes(const tgt_layout* L, int heads, int head_dim, int dtype
 extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, const float* bias,
                                    int bias_heads, const tgt_layout* by_dst, void* out, float* z,
                                    int heads, int head_dim, int dtype, void* scratch,
-                                   size_t scratch_bytes, void* stream_) {
+                                   size_t scratch_bytes, void* stream) {
+  const int64_t row_bytes = int64_t(heads) * head_dim * (dtype == TGT_F32 ? 4 : 2);
+  return tgt_sparse_attn_fwd_strided(q, row_bytes, k, v, row_bytes, bias, bias_heads, by_dst, out, z,
+                                     heads, head_dim, dtype, scratch, scratch_bytes, stream);
+}
+
+extern "C" int tgt_sparse_attn_fwd_strided(const void* q, int64_t q_row_bytes, const void* k,
+                                           const void* v, int64_t kv_row_bytes, const float* bias,
+                                           int bias_heads, const tgt_layout* by_dst, void* out,
+                                           float* z, int heads, int head_dim, int dtype,
+                                           void* scratch, size_t scratch_bytes, void* stream_) {
   using namespace tgt;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(dtype == TGT_F32 || dtype == TGT_BF16, "dtype must be TGT_F32 or TGT_BF16");
   int rc = check_layout(by_dst, "by_dst");
   if (rc != TGT_OK) return rc;
+  const bool can32 = aligned32(q) && aligned32(k) && aligned32(v) && aligned32(out) && q_row_bytes % 32 == 0 &&
+                     kv_row_bytes % 32 == 0;
   HeadSplit hs;
-  if (!split_heads(heads, head_dim, dtype, &hs))
+  if (!split_heads(heads, head_dim, dtype, lane_bytes(heads, head_dim, dtype, can32, kPassFwd), &hs))
     return set_error(TGT_ERR_UNSUPPORTED,
                      "heads=%d head_dim=%d dtype=%d: head_dim must be a power of two multiple of "
                      "16 bytes, at most 512 bytes per head",
@@ -184,20 +213,24 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   TGT_CHECK_ARG((bias_heads == 0) == (bias == nullptr), "bias pointer and bias_heads disagree");
   const tgt_layout& L = *by_dst;
   if (L.n_rows == 0) return TGT_OK;
+  const size_t elem = dtype == TGT_F32 ? 4 : 2;
+  const int64_t row_bytes = int64_t(heads) * head_dim * int64_t(elem);
   TGT_CHECK_ARG(q && k && v && out && z, "q/k/v/out/z must not be null");
-  TGT_CHECK_ARG(uint64_t(L.n_rows) * uint64_t(heads) * head_dim * (dtype == TGT_F32 ? 4 : 2) / 16 <
+  TGT_CHECK_ARG(q_row_bytes >= row_bytes && kv_row_bytes >= row_bytes && q_row_bytes % 16 == 0 &&
+                    kv_row_bytes % 16 == 0,
+                "row strides must be multiples of 16 bytes and at least heads * head_dim elements");
+  TGT_CHECK_ARG(uint64_t(L.n_rows) * uint64_t(q_row_bytes > kv_row_bytes ? q_row_bytes : kv_row_bytes) / 16 <
                     (uint64_t(1) << 32),
                 "tensors larger than 64 GiB are not supported");
   TGT_CHECK_ARG(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(z) &&
                     aligned16(bias) && aligned16(scratch),
                 "device pointers must be 16-byte aligned");
-  const size_t elem = dtype == TGT_F32 ? 4 : 2;
   if (L.n_edges == 0) {  // no edges: every row is empty
     TGT_CHECK_CUDA(cudaMemsetAsync(out, 0, size_t(L.n_rows) * heads * head_dim * elem, stream));
     TGT_CHECK_CUDA(cudaMemsetAsync(z, 0, size_t(L.n_rows) * heads * 4, stream));
     return TGT_OK;
   }
-  const int nacc = (dtype == TGT_F32 ? 4 : 8) + 1;
+  const int nacc = hs.w / int(elem) + 1;
   const TilePlan tp = plan_tiles(L.n_edges, hs, nacc, fwd_resident_ctas(dtype, hs));
   if (scratch == nullptr || scratch_bytes < tp.scratch_bytes)
     return set_error(TGT_ERR_WORKSPACE, "scratch holds %zu bytes, %zu needed", scratch_bytes,
@@ -208,6 +241,8 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
   p.out = out; p.z = z;
   p.heads = heads;
   p.row_elems = heads * head_dim;
+  p.q_row_bytes = q_row_bytes;
+  p.kv_row_bytes = kv_row_bytes;
   p.inv_scale = 1.0f / sqrtf(float(head_dim));
   p.walk.ptr = L.ptr; p.walk.other = L.other; p.walk.perm = L.perm; p.walk.seg = L.seg;
   p.walk.n_rows = int(L.n_rows); p.walk.n_edges = int(L.n_edges);
@@ -220,14 +255,13 @@ extern "C" int tgt_sparse_attn_fwd(const void* q, const void* k, const void* v, 
     TGT_CHECK_CUDA(cudaMemsetAsync(p.walk.tile_done, 0, tp.counter_bytes, stream));
 
   const dim3 grid(tp.n_tiles, hs.groups);
-#define TGT_LAUNCH_FWD(T, LPH, G)                                          \
-  do {                                                                     \
-    fwd_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p);          \
-    if (second_kernel && tp.n_tiles > 1)                                   \
-      fwd_stitch_kernel<T, LPH, G><<<grid, kBlockThreads, 0, stream>>>(p); \
-  } while (0)
-  TGT_DISPATCH(dtype, hs.lph, hs.g, TGT_LAUNCH_FWD);
-#undef TGT_LAUNCH_FWD
+  const bool built = dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
+    using S = decltype(sh);
+    fwd_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+    if (second_kernel && tp.n_tiles > 1)
+      fwd_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+  });
+  if (!built) return set_error(TGT_ERR_UNSUPPORTED, "no kernel is built for this head layout");
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }
@@ -273,7 +307,7 @@ extern "C" int tgt_sparse_attn_fwd_noalloc(const void* q, const void* k, const v
   int rc = check_layout(by_dst, "by_dst");
   if (rc != TGT_OK) return rc;
   HeadSplit hs;
-  if (!split_heads(heads, head_dim, dtype, &hs))
+  if (!split_heads(heads, head_dim, dtype, 16, &hs))
     return set_error(TGT_ERR_UNSUPPORTED, "heads=%d head_dim=%d dtype=%d is not supported", heads,
                      head_dim, dtype);
   // size check first: nothing is launched and nothing is looked up for a graph that does not fit

@@ -29,6 +29,7 @@ int set_error(int code, const char* fmt, ...);
   } while (0)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 constexpr int kMaxDevices = 64;  // device ordinals the per-device caches cover
 
@@ -40,13 +41,17 @@ int sm_count();
 
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// ---- 16-byte vector access --------------------------------------------------------------------
-// One lane always moves 16 bytes of a row: 4 fp32 or 8 bf16 values, widened to fp32 registers.
+// ---- lane-wide vector access --------------------------------------------------------------------
+// One lane moves W bytes of a row, W = 16 (4 fp32 or 8 bf16 values) or 32 (8 fp32 / 16 bf16 values,
+// fetched with the 256-bit global loads and stores of sm_100), widened to fp32 registers.
+template <typename T, int W>
+struct Lane;
+
 template <typename T>
-struct Vec16;
+using Vec16 = Lane<T, 16>;
 
 template <>
-struct Vec16<float> {
+struct Lane<float, 16> {
   static constexpr int kElems = 4;
   __device__ __forceinline__ static void load(const float* p, float (&r)[4]) {
     const float4 t = __ldg(reinterpret_cast<const float4*>(p));
@@ -55,8 +60,9 @@ struct Vec16<float> {
   __device__ __forceinline__ static void store(float* p, const float (&r)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(r[0], r[1], r[2], r[3]);
   }
-  // Packed form of one 16-byte piece: operands wait in registers in this form until they are used.
+  // Packed form of one piece: operands wait in registers in this form until they are used.
   using Raw = float4;
+  // The position is a 32-bit index in units of W bytes (cheaper addressing than 64-bit offsets).
   __device__ __forceinline__ static Raw raw_at(const float* base, unsigned v) {
     return __ldg(reinterpret_cast<const float4*>(base) + v);
   }
@@ -64,36 +70,30 @@ struct Vec16<float> {
   __device__ __forceinline__ static void unpack(const Raw& t, float (&r)[4]) {
     r[0] = t.x; r[1] = t.y; r[2] = t.z; r[3] = t.w;
   }
-  // The same with the position given as a 32-bit index in units of 16 bytes (cheaper addressing).
-  __device__ __forceinline__ static void load_at(const float* base, unsigned v, float (&r)[4]) {
-    load(reinterpret_cast<const float*>(reinterpret_cast<const float4*>(base) + v), r);
-  }
   __device__ __forceinline__ static void store_at(float* base, unsigned v, const float (&r)[4]) {
     store(reinterpret_cast<float*>(reinterpret_cast<float4*>(base) + v), r);
   }
 };
 
+// bf16 -> fp32 is a 16-bit left shift of the payload
+__device__ __forceinline__ void bf16x2_to_f32(uint32_t w, float& lo, float& hi) {
+  lo = __uint_as_float(w << 16);
+  hi = __uint_as_float(w & 0xffff0000u);
+}
+__device__ __forceinline__ uint32_t f32_to_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 template <>
-struct Vec16<__nv_bfloat16> {
+struct Lane<__nv_bfloat16, 16> {
   static constexpr int kElems = 8;
   __device__ __forceinline__ static void load(const __nv_bfloat16* p, float (&r)[8]) {
-    const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      // bf16 -> fp32 is a 16-bit left shift of the payload
-      r[2 * i] = __uint_as_float(w[i] << 16);
-      r[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+    unpack(__ldg(reinterpret_cast<const uint4*>(p)), r);
   }
   __device__ __forceinline__ static void store(__nv_bfloat16* p, const float (&r)[8]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * i], r[2 * i + 1]);
-      w[i] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(p) = make_uint4(f32_to_bf16x2(r[0], r[1]), f32_to_bf16x2(r[2], r[3]),
+                                              f32_to_bf16x2(r[4], r[5]), f32_to_bf16x2(r[6], r[7]));
   }
   using Raw = uint4;
   __device__ __forceinline__ static Raw raw_at(const __nv_bfloat16* base, unsigned v) {
@@ -101,20 +101,76 @@ struct Vec16<__nv_bfloat16> {
   }
   __device__ __forceinline__ static Raw raw_zero() { return make_uint4(0u, 0u, 0u, 0u); }
   __device__ __forceinline__ static void unpack(const Raw& t, float (&r)[8]) {
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      r[2 * i] = __uint_as_float(w[i] << 16);
-      r[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+    bf16x2_to_f32(t.x, r[0], r[1]); bf16x2_to_f32(t.y, r[2], r[3]);
+    bf16x2_to_f32(t.z, r[4], r[5]); bf16x2_to_f32(t.w, r[6], r[7]);
   }
-  __device__ __forceinline__ static void load_at(const __nv_bfloat16* base, unsigned v,
-                                                 float (&r)[8]) {
-    load(reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const uint4*>(base) + v), r);
-  }
-  __device__ __forceinline__ static void store_at(__nv_bfloat16* base, unsigned v,
-                                                  const float (&r)[8]) {
+  __device__ __forceinline__ static void store_at(__nv_bfloat16* base, unsigned v, const float (&r)[8]) {
     store(reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint4*>(base) + v), r);
+  }
+};
+
+// 32-byte lanes: one 256-bit load per piece (ld.global.nc.v8, sm_100), so a row of 32 bytes — one head
+// of 8 fp32 values, the head slice of one rank of an 8-rank run — is one lane, one load, and its dot
+// product needs no shuffle.  Addresses must be 32-byte aligned.
+struct Raw32 {
+  uint32_t w[8];
+};
+__device__ __forceinline__ Raw32 ld_nc_256(const void* p) {
+  Raw32 r;
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]), "=r"(r.w[4]), "=r"(r.w[5]),
+                 "=r"(r.w[6]), "=r"(r.w[7])
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_256(void* p, const Raw32& r) {
+  asm volatile("st.global.v8.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};" ::"r"(r.w[0]), "r"(r.w[1]), "r"(r.w[2]),
+               "r"(r.w[3]), "r"(r.w[4]), "r"(r.w[5]), "r"(r.w[6]), "r"(r.w[7]), "l"(p)
+               : "memory");
+}
+
+template <>
+struct Lane<float, 32> {
+  static constexpr int kElems = 8;
+  using Raw = Raw32;
+  __device__ __forceinline__ static Raw raw_at(const float* base, unsigned v) {
+    return ld_nc_256(reinterpret_cast<const char*>(base) + size_t(v) * 32);
+  }
+  __device__ __forceinline__ static Raw raw_zero() {
+    Raw r;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.w[i] = 0u;
+    return r;
+  }
+  __device__ __forceinline__ static void unpack(const Raw& t, float (&r)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = __uint_as_float(t.w[i]);
+  }
+  __device__ __forceinline__ static void store_at(float* base, unsigned v, const float (&r)[8]) {
+    Raw t;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t.w[i] = __float_as_uint(r[i]);
+    st_256(reinterpret_cast<char*>(base) + size_t(v) * 32, t);
+  }
+};
+
+template <>
+struct Lane<__nv_bfloat16, 32> {
+  static constexpr int kElems = 16;
+  using Raw = Raw32;
+  __device__ __forceinline__ static Raw raw_at(const __nv_bfloat16* base, unsigned v) {
+    return ld_nc_256(reinterpret_cast<const char*>(base) + size_t(v) * 32);
+  }
+  __device__ __forceinline__ static Raw raw_zero() { return Lane<float, 32>::raw_zero(); }
+  __device__ __forceinline__ static void unpack(const Raw& t, float (&r)[16]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bf16x2_to_f32(t.w[i], r[2 * i], r[2 * i + 1]);
+  }
+  __device__ __forceinline__ static void store_at(__nv_bfloat16* base, unsigned v, const float (&r)[16]) {
+    Raw t;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t.w[i] = f32_to_bf16x2(r[2 * i], r[2 * i + 1]);
+    st_256(reinterpret_cast<char*>(base) + size_t(v) * 32, t);
   }
 };
 

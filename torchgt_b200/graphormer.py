@@ -64,12 +64,16 @@ class MultiHeadAttention(nn.Module):
 
     def forward(self, x, attn_bias=None, edge_index=None, attn_type=None, mask=None):
         b = x.size(0)
-        q = self.linear_q(x).view(b, -1, self.num_heads, self.att_size)
-        k = self.linear_k(x).view(b, -1, self.num_heads, self.att_size)
-        v = self.linear_v(x).view(b, -1, self.num_heads, self.att_size)
         use_sp = sequence_parallel_is_initialized() if self.sequence_parallel is None else self.sequence_parallel
+        q = self.linear_q(x).view(b, -1, self.num_heads, self.att_size)
+        # the exchange of q starts now and runs under the next two projections; k follows under v's
+        pending = self.dist_attn.start_exchange(q, attn_bias, edge_index, attn_type) if use_sp else None
+        k = self.linear_k(x).view(b, -1, self.num_heads, self.att_size)
+        if pending is not None:
+            pending.add(k)
+        v = self.linear_v(x).view(b, -1, self.num_heads, self.att_size)
         if use_sp:
-            ctx = self.dist_attn(q, k, v, attn_bias, edge_index, attn_type)
+            ctx = self.dist_attn(q, k, v, attn_bias, edge_index, attn_type, pending=pending)
         else:  # single process without a sequence-parallel group: the layer would only pass through
             ctx = self.dist_attn.local_attn(q, k, v, attn_bias, edge_index, attn_type)
         return self.output_layer(ctx)

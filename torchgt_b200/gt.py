@@ -48,11 +48,16 @@ class MultiHeadAttention(nn.Module):
 
     def forward(self, x, attn_bias=None, mask=None, edge_index=None, attn_type=None):
         b = x.size(0)
+        use_sp = sequence_parallel_is_initialized()
         q = self.linear_q(x).view(b, -1, self.num_heads, self.att_size)
+        # the exchange of q starts now and runs under the next two projections; k follows under v's
+        pending = self.dist_attn.start_exchange(q, attn_bias, edge_index, attn_type) if use_sp else None
         k = self.linear_k(x).view(b, -1, self.num_heads, self.att_size)
+        if pending is not None:
+            pending.add(k)
         v = self.linear_v(x).view(b, -1, self.num_heads, self.att_size)
-        if sequence_parallel_is_initialized():
-            out = self.dist_attn(q, k, v, attn_bias, edge_index, attn_type)
+        if use_sp:
+            out = self.dist_attn(q, k, v, attn_bias, edge_index, attn_type, pending=pending)
         else:  # single process without a sequence-parallel group: the layer would only pass through
             out = self.dist_attn.local_attn(q, k, v, attn_bias, edge_index, attn_type)
         if out.size() != x.size():

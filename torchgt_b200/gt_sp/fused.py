@@ -49,10 +49,55 @@ def eligible(query: Tensor, attn_bias, edge_index, attn_type, world: int) -> boo
     return row_bytes % 16 == 0 and (head_dim * query.element_size()) % 16 == 0
 
 
+class PendingPush:
+    """q, k and v on their way to the peers while the caller still computes the later ones.
+
+    The reference computes the three projections and then exchanges them one after the other
+    (models/graphormer_dist_node_level.py:254-264).  Here the landing slot is reserved when the first
+    projection exists and each tensor is pushed on the exchange's side stream as soon as it has been
+    computed, so its transfer runs under the next projection's GEMM; the layer's forward then only waits
+    for the side stream before the barrier."""
+
+    def __init__(self, px: "p2p.PeerExchange", first: Tensor):
+        b, rows, heads, head_dim = first.shape
+        self.px = px
+        self.shape, self.dtype = tuple(first.shape), first.dtype
+        self.row_bytes = (heads // px.world) * head_dim * first.element_size()
+        self.tensor_bytes = b * px.world * rows * self.row_bytes
+        px.check()
+        self.slot = px.acquire(3 * self.tensor_bytes)
+        self.sent = []                 # data_ptr of every tensor already on its way, in slot order
+        self.keep = []
+        self.add(first)
+
+    def add(self, t: Tensor) -> None:
+        if tuple(t.shape) != self.shape or t.dtype != self.dtype or len(self.sent) >= 3:
+            raise ValueError("tensors pushed together must share shape and dtype (at most three)")
+        t = t.detach().contiguous()
+        px, side = self.px, self.px.side_stream
+        side.wait_stream(torch.cuda.current_stream(t.device))      # t has been computed
+        with torch.cuda.stream(side):
+            b, rows = self.shape[0], self.shape[1]
+            px.push([t], self.slot, b * rows, self.row_bytes, rows * self.row_bytes,
+                    offset_bytes=len(self.sent) * self.tensor_bytes)
+        t.record_stream(side)
+        self.sent.append(t.data_ptr())
+        self.keep.append(t)
+
+    def finish(self, tensors) -> None:
+        """Push what has not been pushed yet and make the current stream wait for all of it."""
+        if [t.data_ptr() for t in tensors[:len(self.sent)]] != self.sent:
+            raise RuntimeError("the tensors given to the layer are not the ones whose exchange was started")
+        for t in tensors[len(self.sent):]:
+            self.add(t)
+        torch.cuda.current_stream(tensors[0].device).wait_stream(self.px.side_stream)
+        self.keep = []
+
+
 class _UlyssesSparseAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q: Tensor, k: Tensor, v: Tensor, graph: SparseGraph, px: "p2p.PeerExchange",
-                alias_rows: Optional[Tensor]):
+                alias_rows: Optional[Tensor], pending: Optional[PendingPush] = None):
         lib = _cabi.load()
         b, rows, heads, head_dim = q.shape
         world = px.world
@@ -61,10 +106,14 @@ class _UlyssesSparseAttention(torch.autograd.Function):
         n_rows = b * world * rows
         tensor_bytes = n_rows * row_bytes
         code = _DTYPES[q.dtype]
-        px.check()
         # q, k, v -> peers: rank r' receives heads r' * heads_l .. of every row, at rows rank * rows + l
-        qkv = px.acquire(3 * tensor_bytes)
-        px.push([q, k, v], qkv, b * rows, row_bytes, rows * row_bytes)
+        if pending is not None:
+            pending.finish([q, k, v])          # (some of) the pushes were started while k and v were computed
+            qkv = pending.slot
+        else:
+            px.check()
+            qkv = px.acquire(3 * tensor_bytes)
+            px.push([q, k, v], qkv, b * rows, row_bytes, rows * row_bytes)
         px.barrier()
         qg, kg, vg = (qkv.view(t * tensor_bytes, (n_rows, heads_l, head_dim), q.dtype) for t in range(3))
         landing = px.acquire(tensor_bytes, p2p.SOURCE)
@@ -120,11 +169,11 @@ class _UlyssesSparseAttention(torch.autograd.Function):
         px.pull(grads, [dq, dk, dv], b, rows, row_bytes)
         px.release(grads)
         px.check()
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
 def ulysses_sparse_attention(px: "p2p.PeerExchange", query: Tensor, key: Tensor, value: Tensor, edge_index,
-                             alias_rows: Optional[Tensor] = None) -> Tensor:
+                             alias_rows: Optional[Tensor] = None, pending: Optional[PendingPush] = None) -> Tensor:
     """[b, rows, H, D] x3 on every rank -> [b, rows, H*D]: sparse attention over the gathered sequence
     (``world * rows`` rows per batch entry, numbered rank-major) with the heads sharded over the ranks.
     ``alias_rows`` (device int32): rows of the gathered sequence whose output is row 0's output."""
@@ -132,4 +181,4 @@ def ulysses_sparse_attention(px: "p2p.PeerExchange", query: Tensor, key: Tensor,
     graph = graph_for(edge_index, b * px.world * rows)
     graph.poll()
     q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
-    return _UlyssesSparseAttention.apply(q, k, v, graph, px, alias_rows)
+    return _UlyssesSparseAttention.apply(q, k, v, graph, px, alias_rows, pending)

@@ -16,9 +16,11 @@ class DistributedAttention(_UlyssesBase):
     """gt_sp/gt_layer.py:142-206: q, k, v [b, s/p, H, D]; an optional dense bias [b, H, s/p, s] is
     exchanged with heads scattered (dim 1) and rows gathered (dim 2)."""
 
+    exchanges_in_eval = True
+
     def forward(self, query: Tensor, key: Tensor, value: Tensor, attn_bias: Tensor, edge_index: Tensor,
-                attn_type, *args: Any) -> Tensor:
-        out = self._single_node(query, key, value, attn_bias, edge_index, attn_type, alias=False)
+                attn_type, *args: Any, pending=None) -> Tensor:
+        out = self._single_node(query, key, value, attn_bias, edge_index, attn_type, alias=False, pending=pending)
         if out is not None:
             return out
         q, k, v = self._gather_sequence(query, key, value)
@@ -33,8 +35,10 @@ class DistributedAttentionNodeLevel(DistributedAttention):
     """gt_sp/gt_layer.py:209-286: same exchange, bypassed in evaluation mode where rank 0 runs the
     whole sequence with all heads."""
 
+    exchanges_in_eval = False
+
     def forward(self, query: Tensor, key: Tensor, value: Tensor, attn_bias: Tensor, edge_index: Tensor,
-                attn_type, *args: Any) -> Tensor:
+                attn_type, *args: Any, pending=None) -> Tensor:
         if not self.training:
             return self.local_attn(query, key, value, attn_bias, edge_index, attn_type, *args)
-        return super().forward(query, key, value, attn_bias, edge_index, attn_type, *args)
+        return super().forward(query, key, value, attn_bias, edge_index, attn_type, *args, pending=pending)

@@ -91,21 +91,38 @@ class _UlyssesBase(Module):
         self.scatter_idx = scatter_idx  # heads
         self.gather_idx = gather_idx    # sequence
 
-    def _single_node(self, query: Tensor, key: Tensor, value: Tensor, attn_bias, edge_index, attn_type,
-                     alias: bool):
-        """Exchange + sparse attention + exchange back as one autograd node over peer memory, when the
-        call qualifies (our CoreAttention, CUDA, no bias, transport available); else None."""
+    exchanges_in_eval = False   # layers that also exchange in evaluation mode set this
+
+    def _peer_exchange(self, query: Tensor, attn_bias, edge_index, attn_type):
+        """The peer-memory transport when this call can run as one autograd node (our CoreAttention, CUDA,
+        sparse attention without a bias, transport available); else None."""
         from ..attn_module import CoreAttention
         if not isinstance(self.local_attn, CoreAttention):
             return None
         world = get_sequence_parallel_world_size()
         if not fused.eligible(query, attn_bias, edge_index, attn_type, world):
             return None
-        px = p2p.peer_exchange_for(self.spg, query.device)
+        return p2p.peer_exchange_for(self.spg, query.device)
+
+    def start_exchange(self, query: Tensor, attn_bias, edge_index, attn_type):
+        """Begin moving ``query`` to the peers while the caller computes key and value (models call this
+        right after the first projection).  Returns a handle to ``add()`` the later tensors to and to pass
+        to ``forward(..., pending=handle)``, or None when this call will not use the peer transport."""
+        if not (self.training or self.exchanges_in_eval) or not query.is_cuda:
+            return None
+        if query.dim() != 4 or not query.is_contiguous():
+            return None
+        px = self._peer_exchange(query, attn_bias, edge_index, attn_type)
+        return fused.PendingPush(px, query) if px is not None else None
+
+    def _single_node(self, query: Tensor, key: Tensor, value: Tensor, attn_bias, edge_index, attn_type,
+                     alias: bool, pending=None):
+        """Exchange + sparse attention + exchange back as one autograd node over peer memory, or None."""
+        px = pending.px if pending is not None else self._peer_exchange(query, attn_bias, edge_index, attn_type)
         if px is None:
             return None
         rows = get_global_token_rows_on(query.device, get_last_batch_flag()) if alias else None
-        return fused.ulysses_sparse_attention(px, query, key, value, edge_index, rows)
+        return fused.ulysses_sparse_attention(px, query, key, value, edge_index, rows, pending)
 
     def _gather_sequence(self, query: Tensor, key: Tensor, value: Tensor):
         """[b, s/p(+1), H, D] x3 -> [b, s(+p), H/p, D] x3 in one collective."""
@@ -176,10 +193,10 @@ class DistributedAttentionNoMerge(_UlyssesBase):
     point at row 0, and after attention row 0's output is copied into the other slots."""
 
     def forward(self, query: Tensor, key: Tensor, value: Tensor, attn_bias: Tensor, edge_index: Tensor,
-                attn_type, *args: Any) -> Tensor:
+                attn_type, *args: Any, pending=None) -> Tensor:
         if not self.training:
             return self.local_attn(query, key, value, attn_bias, edge_index, attn_type, *args)
-        out = self._single_node(query, key, value, attn_bias, edge_index, attn_type, alias=True)
+        out = self._single_node(query, key, value, attn_bias, edge_index, attn_type, alias=True, pending=pending)
         if out is not None:
             return out
         q, k, v = self._gather_sequence(query, key, value)

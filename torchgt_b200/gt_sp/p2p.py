@@ -60,6 +60,17 @@ class Slot:
         self.peers = (ctypes.c_void_p * world)(*[int(p) for p in handle.buffer_ptrs])
         self.free_epoch = -1          # barrier count at the moment it was last given back
         self.in_use = False
+        self._shifted = {}
+
+    def peers_at(self, offset_bytes: int):
+        """Peer table of the slot's addresses ``offset_bytes`` further in (for filling it piece by piece)."""
+        if offset_bytes == 0:
+            return self.peers
+        table = self._shifted.get(offset_bytes)
+        if table is None:
+            table = (ctypes.c_void_p * len(self.peers))(*[int(p) + offset_bytes for p in self.peers])
+            self._shifted[offset_bytes] = table
+        return table
 
     def view(self, offset_bytes: int, shape, dtype: torch.dtype) -> Tensor:
         """This rank's copy of the slot, ``shape`` elements of ``dtype`` starting at ``offset_bytes``."""
@@ -84,6 +95,7 @@ class PeerExchange:
         self.spin_limit = int(os.environ.get("TGT_P2P_SPIN_LIMIT", DEFAULT_SPIN_LIMIT))
         self.epoch = 0                 # barriers enqueued so far (host count, same on every rank)
         self.slots: List[Slot] = []
+        self.side_stream = torch.cuda.Stream(device=device)   # pushes that overlap the caller's own work
         lib = _cabi.load()
         control_bytes = max(int(lib.tgt_p2p_control_bytes()), 256)
         self.control = self._new_symmetric(control_bytes)
@@ -126,14 +138,16 @@ class PeerExchange:
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def push(self, xs: Sequence[Tensor], slot: Slot, outer_s: int, width_s_bytes: int, width_g_bytes: int,
-             alias_rows: Optional[Tensor] = None, alias_row_bytes: int = 0, mode: int = _cabi.TGT_PUSH_FINAL) -> None:
+             alias_rows: Optional[Tensor] = None, alias_row_bytes: int = 0, mode: int = _cabi.TGT_PUSH_FINAL,
+             offset_bytes: int = 0) -> None:
+        """Enqueue the push on the current stream; the tensors land ``offset_bytes`` into the peers' slots."""
         lib = _cabi.load()
         ptrs = [t.data_ptr() for t in xs] + [None] * (3 - len(xs))
         n_alias = 0 if alias_rows is None else int(alias_rows.numel())
-        _cabi.check(lib.tgt_p2p_push(ptrs[0], ptrs[1], ptrs[2], len(xs), slot.peers, slot.nbytes, outer_s,
-                                     width_s_bytes, width_g_bytes, self.world, self.rank,
-                                     alias_rows.data_ptr() if n_alias else None, n_alias, alias_row_bytes, mode,
-                                     self._stream()))
+        _cabi.check(lib.tgt_p2p_push(ptrs[0], ptrs[1], ptrs[2], len(xs), slot.peers_at(offset_bytes),
+                                     slot.nbytes - offset_bytes, outer_s, width_s_bytes, width_g_bytes, self.world,
+                                     self.rank, alias_rows.data_ptr() if n_alias else None, n_alias, alias_row_bytes,
+                                     mode, self._stream()))
 
     def pull(self, slot: Slot, outs: Sequence[Tensor], outer: int, rows: int, width_bytes: int,
              alias_rows: Optional[Tensor] = None) -> None:

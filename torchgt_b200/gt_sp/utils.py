@@ -161,3 +161,17 @@ def copy_global_token0(x_layer: Tensor, extend_dim: int) -> Tensor:
     rows = torch.tensor(_active_global_rows(), dtype=torch.long)
     x_layer[:, rows, :] = x_layer[:, 0:1, :].expand(-1, rows.numel(), -1)
     return x_layer.contiguous()
+
+
+# Batch construction (induced sub-graph, cluster-sparse blocks, per-rank slicing) lives in its own module,
+# which builds on the helpers above; its names resolve here too, where the reference has them
+# (gt_sp/utils.py:61-82,187-520).
+_BATCHING_NAMES = ("create_pairs", "gen_sub_edge_index", "generate_new_edges_optimized", "get_batch_reorder_blockize",
+                   "pad_2d", "pad_y", "random_split_idx", "reformat_graph")
+
+
+def __getattr__(name: str):
+    if name in _BATCHING_NAMES:
+        from . import batching
+        return getattr(batching, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
