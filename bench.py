@@ -635,7 +635,7 @@ def run_single_gpu(args, dtype):
 
     # ---- end to end through the public API from pinned host memory -----------------------------------
     hq, hk, hv, hdout, hbias = (t.pin_memory() for t in make_inputs(n_rows, n_edges, dtype, 99, None))
-    hei = edge_index.pin_memory()
+    hei = edge_index.to(torch.int32).pin_memory()   # the layouts are built from int32 ids: 8 bytes per edge on the bus
     host_out = [torch.empty_like(hq).pin_memory() for _ in range(4)]
     host_dbias = torch.empty_like(hbias).pin_memory()
 
@@ -675,7 +675,7 @@ def run_single_gpu(args, dtype):
             q, k, v = (t.to(dev, non_blocking=True).requires_grad_() for t in (hq, hk, hv))
             bias = hbias.to(dev, non_blocking=True).requires_grad_()
             dout = hdout.to(dev, non_blocking=True)
-            g = SparseGraph(hei.to(dev, non_blocking=True), n_rows, defer_check=True)   # no host sync
+            g = SparseGraph(hei.to(dev, non_blocking=True), n_rows)   # builds without a host synchronisation
             out = sparse_graph_attention(q, k, v, g, bias)
             out.backward(dout)
             for dst, src in zip(host_out2[i % 2], (out.detach(), q.grad, k.grad, v.grad)):
@@ -693,7 +693,7 @@ def run_single_gpu(args, dtype):
     clocks = sampler.stop()
 
     elem = 4 if dtype == torch.float32 else 2
-    h2d = 4 * n_rows * HEADS * HEAD_DIM * elem + n_edges * 4 + 2 * n_edges * 8
+    h2d = 4 * n_rows * HEADS * HEAD_DIM * elem + n_edges * 4 + 2 * n_edges * 4
     d2h = 4 * n_rows * HEADS * HEAD_DIM * elem + n_edges * 4
     peak, peak_kind = measured_hbm_peak()
     bytes_ = algorithmic_bytes(n_rows, n_edges, HEADS, HEAD_DIM, elem, 4)
@@ -734,7 +734,7 @@ def run_single_gpu(args, dtype):
         "clocks": clocks,
         "e2e": {"value": n_edges / results["pipelined"], "unit": "edges/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": results["pipelined"] * 1e3,
-                "includes": "pinned-host uploads of q,k,v,bias,dO and the int64 edge list, both edge layouts "
+                "includes": "pinned-host uploads of q,k,v,bias,dO and the int32 edge list, both edge layouts "
                             "built, forward, backward, downloads of out,dq,dk,dv,dbias, every step; steps "
                             "alternate between two streams so uploads overlap the previous step's downloads",
                 "one_step_at_a_time_value": n_edges / results["full"],
@@ -930,6 +930,25 @@ def run_multi_gpu(args, dtype, rank, world):
     p2p.check_peer_exchanges()           # a barrier that gave up on a peer invalidates the timing
     note(f"graph {ms_per_step:.3f} ms")
 
+    # where the time of one step goes: CUDA events between the phases of eagerly issued steps (a profiler
+    # cannot wrap a multi-rank job here); a barrier's time includes waiting for the slowest rank
+    breakdown = None
+    if px is not None:
+        totals = {}
+        n_traced = 20
+        for i in range(n_traced):
+            torch.cuda.synchronize(); dist.barrier()
+            px.start_trace()
+            step(i)
+            for label, ms in px.stop_trace():
+                totals[label] = totals.get(label, 0.0) + ms
+        labels = sorted(totals)
+        t = torch.tensor([totals[k] / n_traced for k in labels], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        breakdown = {k: round(v, 4) for k, v in zip(labels, t.tolist())}
+        breakdown["note"] = ("ms per step and phase, eager launches, max over ranks; 'barrier' sums the four barriers "
+                             "of a step (each includes the wait for the slowest rank and host launch gaps)")
+
     # the attention alone (no exchange) on this rank's head slice of the same graph, for reference
     heads_local = HEADS // world
     op_sets = []
@@ -1022,6 +1041,7 @@ def run_multi_gpu(args, dtype, rank, world):
                                 "exchanges, downloads of out,dq,dk,dv; edge layouts resident"},
             "gpu_launches": launches * args.steps,
             "eager_ms_per_step": eager_ms,
+            "step_breakdown_ms": breakdown,
             "epoch": epoch,
             "weak_scaling_training_step": weak,
             "attention_only": {"ms_per_step": op_ms, "value": n_edges / (op_ms * 1e-3), "unit": "edges/s",

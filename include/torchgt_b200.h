@@ -359,6 +359,36 @@ TGT_API int tgt_p2p_fetch(const void* slot_mine, size_t slot_bytes, int n_tensor
                           void* y1, void* y2, int64_t bytes_per_tensor, int staged, int world,
                           int64_t width_g_bytes, void* stream);
 
+/*
+ * The dense layers next to the exchange, fused with it (fp32, hidden size = projection width = 64, the
+ * reference models' size; other sizes return TGT_ERR_UNSUPPORTED and the caller uses the separate steps).
+ *
+ * tgt_ln_qkv_push replaces, per encoder layer, LayerNorm (models/graphormer_dist_node_level.py:301), the
+ * three projections (:254-257) and the q/k/v all-to-alls with their `contiguous` copies
+ * (gt_sp/layer.py:41,516-518): x is this rank's [batch * rows, hidden]; for every tile of rows the kernel
+ * normalises (gamma / beta NULL: no LayerNorm), multiplies by the three [out_features, hidden] weights
+ * (nn.Linear layout, fp32 FMA), adds the biases and stores every rank's head slice at its final position
+ * in that rank's slot (q, k, v back to back, each [batch][world * rows][out_features / world]) — plain
+ * stores into peer memory.  Follow it with tgt_p2p_barrier; the attention then reads the slot in place.
+ *
+ * tgt_pull_out_proj replaces copy_global_token0 (gt_sp/utils.py:817-838), the output all-to-all
+ * (gt_sp/layer.py:545) and the output projection (models/graphormer_dist_node_level.py:271): call it
+ * after a tgt_p2p_barrier that follows the attention; every peer's slot holds its attention output
+ * [batch][world * rows][in_features / world]; the kernel gathers this rank's rows of all of them
+ * (rows listed in alias_rows read row 0), writes the gathered [batch * rows, in_features] to ctx (the
+ * input of the projection, needed for its weight gradient) and y = ctx W^T + b ([hidden, in_features]
+ * weight) to y.
+ */
+TGT_API int tgt_ln_qkv_push(const float* x, const float* gamma, const float* beta, float eps,
+                            const float* wq, const float* bq, const float* wk, const float* bk,
+                            const float* wv, const float* bv, int hidden, int out_features,
+                            void* const* peer_slots, size_t slot_bytes, int64_t batch, int64_t rows,
+                            int world, int rank, void* stream);
+TGT_API int tgt_pull_out_proj(void* const* peer_slots, size_t slot_bytes, const float* w, const float* b,
+                              int hidden, int in_features, float* ctx, float* y, int64_t batch,
+                              int64_t rows, int world, int rank, const int32_t* alias_rows, int n_alias,
+                              void* stream);
+
 #ifdef __cplusplus
 }
 #endif

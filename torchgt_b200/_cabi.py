@@ -91,6 +91,11 @@ SIGNATURES = {
                                           c_void_p]),
     "tgt_global_rows_reduce": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int,
                                        c_void_p]),
+    "tgt_ln_qkv_push": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_int, c_int, POINTER(c_void_p), c_size_t, c_int64, c_int64, c_int,
+                                c_int, c_void_p]),
+    "tgt_pull_out_proj": (c_int, [POINTER(c_void_p), c_size_t, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                  c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_void_p]),
     "tgt_p2p_control_bytes": (c_size_t, []),
     "tgt_p2p_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), c_size_t, c_int64, c_int64,
                              c_int64, c_int, c_int, c_void_p, c_int, c_int64, c_int, c_void_p]),

@@ -91,8 +91,34 @@ class EncoderLayer(nn.Module):
         self.ffn = FeedForwardNetwork(hidden_size, ffn_size, dropout_rate)
         self.ffn_dropout = nn.Dropout(dropout_rate)
 
+    def _fused_attention_half(self, x, attn_bias, edge_index, attn_type):
+        """LayerNorm, projections, exchange, attention, exchange and output projection as one autograd
+        node of two compute-and-move kernels around the attention kernels, when the call qualifies: training
+        under sequence parallelism over peer memory, fp32, hidden size 64, sparse attention without a bias."""
+        from .gt_sp import fused
+        from .gt_sp.initialize import get_global_token_rows_on, get_last_batch_flag, get_sequence_parallel_world_size
+        mha = self.self_attention
+        if not (self.training and fused.fused_block_enabled() and mha.sequence_parallel is not False
+                and sequence_parallel_is_initialized()):
+            return None
+        if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 3 and x.size(-1) == 64
+                and mha.num_heads * mha.att_size == 64 and attn_bias is None and attn_type == "sparse"
+                and edge_index is not None):
+            return None
+        world = get_sequence_parallel_world_size()
+        if world < 2 or mha.num_heads % world != 0 or ((mha.num_heads // world) * mha.att_size) % 4 != 0:
+            return None
+        px = mha.dist_attn._peer_exchange(x.new_empty((1, 1, mha.num_heads, mha.att_size)), attn_bias, edge_index,
+                                          attn_type)
+        if px is None:
+            return None
+        rows = get_global_token_rows_on(x.device, get_last_batch_flag())
+        return fused.attention_block(px, x, self.self_attention_norm, mha, edge_index, rows)
+
     def forward(self, x, attn_bias=None, edge_index=None, attn_type=None, mask=None):
-        y = self.self_attention(self.self_attention_norm(x), attn_bias, edge_index, attn_type=attn_type)
+        y = self._fused_attention_half(x, attn_bias, edge_index, attn_type)
+        if y is None:
+            y = self.self_attention(self.self_attention_norm(x), attn_bias, edge_index, attn_type=attn_type)
         x = x + self.self_attention_dropout(y)
         y = self.ffn(self.ffn_norm(x))
         return x + self.ffn_dropout(y)

@@ -114,7 +114,9 @@ class _UlyssesSparseAttention(torch.autograd.Function):
             px.check()
             qkv = px.acquire(3 * tensor_bytes)
             px.push([q, k, v], qkv, b * rows, row_bytes, rows * row_bytes)
+        px.mark("push q,k,v")
         px.barrier()
+        px.mark("barrier")
         qg, kg, vg = (qkv.view(t * tensor_bytes, (n_rows, heads_l, head_dim), q.dtype) for t in range(3))
         landing = px.acquire(tensor_bytes, p2p.SOURCE)
         out_g = landing.view(0, (n_rows, heads_l, head_dim), q.dtype)
@@ -123,9 +125,12 @@ class _UlyssesSparseAttention(torch.autograd.Function):
         _cabi.check(lib.tgt_sparse_attn_fwd(qg.data_ptr(), kg.data_ptr(), vg.data_ptr(), None, 0,
                                             graph.by_dst.byref(), out_g.data_ptr(), z.data_ptr(), heads_l, head_dim,
                                             code, scratch.data_ptr(), scratch.numel(), _stream(q)))
+        px.mark("attention forward")
         px.barrier()
+        px.mark("barrier")
         out = torch.empty((b, rows, heads * head_dim), dtype=q.dtype, device=q.device)
         px.pull(landing, [out], b, rows, row_bytes, alias_rows)
+        px.mark("pull out")
         px.release(landing)
         ctx.graph, ctx.px, ctx.qkv, ctx.alias_rows = graph, px, qkv, alias_rows
         ctx.dims = (b, rows, heads, head_dim, heads_l, row_bytes, n_rows, tensor_bytes, code)
@@ -147,7 +152,9 @@ class _UlyssesSparseAttention(torch.autograd.Function):
         px.check()
         landing = px.acquire(tensor_bytes)
         px.push([dout], landing, b * rows, row_bytes, rows * row_bytes)
+        px.mark("push dO")
         px.barrier()
+        px.mark("barrier")
         dog = landing.view(0, (n_rows, heads_l, head_dim), dtype)
         if ctx.alias_rows is not None:
             # gradient of "listed rows := row 0": row 0 collects the listed rows' gradients
@@ -161,12 +168,15 @@ class _UlyssesSparseAttention(torch.autograd.Function):
             dog.data_ptr(), qg.data_ptr(), kg.data_ptr(), vg.data_ptr(), None, 0, None, z.data_ptr(),
             graph.by_dst.byref(), graph.by_src.byref(), dqg.data_ptr(), dkg.data_ptr(), dvg.data_ptr(), None,
             heads_l, head_dim, code, scratch.data_ptr(), scratch.numel(), _stream(dog)))
+        px.mark("attention backward")
         px.release(qkv)
         px.release(landing)
         ctx.qkv = None
         px.barrier()
+        px.mark("barrier")
         dq, dk, dv = (torch.empty((b, rows, heads, head_dim), dtype=dtype, device=dev) for _ in range(3))
         px.pull(grads, [dq, dk, dv], b, rows, row_bytes)
+        px.mark("pull dq,dk,dv")
         px.release(grads)
         px.check()
         return dq, dk, dv, None, None, None, None
@@ -182,3 +192,132 @@ def ulysses_sparse_attention(px: "p2p.PeerExchange", query: Tensor, key: Tensor,
     graph.poll()
     q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
     return _UlyssesSparseAttention.apply(q, k, v, graph, px, alias_rows, pending)
+
+
+# ---- the attention half of an encoder layer as one node -----------------------------------------------
+def fused_block_enabled() -> bool:
+    return os.environ.get("TGT_FUSED_BLOCK", "1") != "0"
+
+
+class _UlyssesAttentionBlock(torch.autograd.Function):
+    """``y = out_proj(attention(q_proj(LN(x)), k_proj(LN(x)), v_proj(LN(x))))`` with the Ulysses exchange
+    inside, for fp32 and hidden size 64 (models/graphormer_dist_node_level.py:246-273,301 and
+    gt_sp/layer.py:502-550 in one node).
+
+    Forward: ``tgt_ln_qkv_push`` (LayerNorm, the three projections and the stores into the peers' slots
+    in one kernel) -> barrier -> attention on the slot -> barrier -> ``tgt_pull_out_proj`` (gather over
+    NVLink, global-token copy and output projection in one kernel).  No q, k, v tensor exists.
+    Backward: the output projection's gradients (library GEMMs), then push dO -> barrier -> both attention
+    backward passes -> barrier -> pull dQ, dK, dV, then the gradients of the three projections and of the
+    LayerNorm from the saved layer input (the normalised input is recomputed, not stored)."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, wq, bq, wk, bk, wv, bv, wo, bo, eps, heads, graph, px, alias_rows):
+        lib = _cabi.load()
+        b, rows, hidden = x.shape
+        world = px.world
+        head_dim = hidden // heads
+        heads_l = heads // world
+        row_bytes = heads_l * head_dim * 4
+        n_rows = b * world * rows
+        tensor_bytes = n_rows * row_bytes
+        code = _cabi.TGT_F32
+        px.check()
+        x = x.contiguous()
+        qkv = px.acquire(3 * tensor_bytes)
+        _cabi.check(lib.tgt_ln_qkv_push(x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), float(eps), wq.data_ptr(),
+                                        bq.data_ptr(), wk.data_ptr(), bk.data_ptr(), wv.data_ptr(), bv.data_ptr(),
+                                        hidden, hidden, qkv.peers, qkv.nbytes, b, rows, world, px.rank, _stream(x)))
+        px.mark("LayerNorm + q,k,v projections + push")
+        px.barrier()
+        px.mark("barrier")
+        qg, kg, vg = (qkv.view(t * tensor_bytes, (n_rows, heads_l, head_dim), x.dtype) for t in range(3))
+        landing = px.acquire(tensor_bytes, p2p.SOURCE)
+        out_g = landing.view(0, (n_rows, heads_l, head_dim), x.dtype)
+        z = torch.empty((n_rows, heads_l), dtype=torch.float32, device=x.device)
+        scratch = _scratch(graph, heads_l, head_dim, code, 0, x.device)
+        _cabi.check(lib.tgt_sparse_attn_fwd(qg.data_ptr(), kg.data_ptr(), vg.data_ptr(), None, 0,
+                                            graph.by_dst.byref(), out_g.data_ptr(), z.data_ptr(), heads_l, head_dim,
+                                            code, scratch.data_ptr(), scratch.numel(), _stream(x)))
+        px.mark("attention forward")
+        px.barrier()
+        px.mark("barrier")
+        attn = torch.empty((b, rows, hidden), dtype=x.dtype, device=x.device)
+        y = torch.empty((b, rows, hidden), dtype=x.dtype, device=x.device)
+        n_alias = 0 if alias_rows is None else int(alias_rows.numel())
+        _cabi.check(lib.tgt_pull_out_proj(landing.peers, landing.nbytes, wo.data_ptr(), bo.data_ptr(), hidden, hidden,
+                                          attn.data_ptr(), y.data_ptr(), b, rows, world, px.rank,
+                                          alias_rows.data_ptr() if n_alias else None, n_alias, _stream(x)))
+        px.mark("pull + output projection")
+        px.release(landing)
+        ctx.graph, ctx.px, ctx.qkv, ctx.alias_rows = graph, px, qkv, alias_rows
+        ctx.dims = (b, rows, heads, head_dim, heads_l, row_bytes, n_rows, tensor_bytes, code, float(eps))
+        ctx.save_for_backward(x, gamma, beta, wq, wk, wv, wo, attn, z)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _cabi.load()
+        x, gamma, beta, wq, wk, wv, wo, attn, z = ctx.saved_tensors
+        px, graph, qkv = ctx.px, ctx.graph, ctx.qkv
+        b, rows, heads, head_dim, heads_l, row_bytes, n_rows, tensor_bytes, code, eps = ctx.dims
+        hidden = heads * head_dim
+        world, dev = px.world, x.device
+        dy2 = dy.contiguous().view(-1, hidden)
+        # output projection
+        d_wo = dy2.t() @ attn.view(-1, hidden)
+        d_bo = dy2.sum(dim=0)
+        dout = (dy2 @ wo).view(b, rows, hidden)
+        px.check()
+        landing = px.acquire(tensor_bytes)
+        px.push([dout], landing, b * rows, row_bytes, rows * row_bytes)
+        px.mark("push dO")
+        px.barrier()
+        px.mark("barrier")
+        dog = landing.view(0, (n_rows, heads_l, head_dim), x.dtype)
+        if ctx.alias_rows is not None:
+            _cabi.check(lib.tgt_global_rows_reduce(dog.data_ptr(), ctx.alias_rows.data_ptr(), ctx.alias_rows.numel(),
+                                                   b, world * rows, heads_l * head_dim, code, _stream(dog)))
+        qg, kg, vg = (qkv.view(t * tensor_bytes, (n_rows, heads_l, head_dim), x.dtype) for t in range(3))
+        grads = px.acquire(3 * tensor_bytes, p2p.SOURCE)
+        dqg, dkg, dvg = (grads.view(t * tensor_bytes, (n_rows, heads_l, head_dim), x.dtype) for t in range(3))
+        scratch = _scratch(graph, heads_l, head_dim, code, 1, dev)
+        _cabi.check(lib.tgt_sparse_attn_bwd(
+            dog.data_ptr(), qg.data_ptr(), kg.data_ptr(), vg.data_ptr(), None, 0, None, z.data_ptr(),
+            graph.by_dst.byref(), graph.by_src.byref(), dqg.data_ptr(), dkg.data_ptr(), dvg.data_ptr(), None,
+            heads_l, head_dim, code, scratch.data_ptr(), scratch.numel(), _stream(dog)))
+        px.mark("attention backward")
+        px.release(qkv)
+        px.release(landing)
+        ctx.qkv = None
+        px.barrier()
+        px.mark("barrier")
+        dq, dk, dv = (torch.empty((b * rows, hidden), dtype=x.dtype, device=dev) for _ in range(3))
+        px.pull(grads, [dq, dk, dv], b, rows, row_bytes)
+        px.mark("pull dq,dk,dv")
+        px.release(grads)
+        px.check()
+        # the three projections and the LayerNorm (its output recomputed from the saved layer input)
+        with torch.enable_grad():
+            x_leaf = x.detach().requires_grad_()
+            g_leaf, b_leaf = gamma.detach().requires_grad_(), beta.detach().requires_grad_()
+            xn = torch.nn.functional.layer_norm(x_leaf, (hidden,), g_leaf, b_leaf, eps)
+        xn2 = xn.detach().view(-1, hidden)
+        d_wq, d_wk, d_wv = dq.t() @ xn2, dk.t() @ xn2, dv.t() @ xn2
+        d_bq, d_bk, d_bv = dq.sum(dim=0), dk.sum(dim=0), dv.sum(dim=0)
+        dxn = (dq @ wq).addmm_(dk, wk).addmm_(dv, wv).view(b, rows, hidden)
+        dx, d_gamma, d_beta = torch.autograd.grad(xn, (x_leaf, g_leaf, b_leaf), dxn)
+        return (dx, d_gamma, d_beta, d_wq, d_bq, d_wk, d_bk, d_wv, d_bv, d_wo, d_bo,
+                None, None, None, None, None)
+
+
+def attention_block(px, x, norm, mha, edge_index, alias_rows):
+    """The fused attention half of a Graphormer encoder layer (see ``_UlyssesAttentionBlock``).  ``norm`` is the
+    layer's LayerNorm, ``mha`` its MultiHeadAttention (linear_q/k/v, output_layer, num_heads)."""
+    b, rows, _ = x.shape
+    graph = graph_for(edge_index, b * px.world * rows)
+    graph.poll()
+    return _UlyssesAttentionBlock.apply(x, norm.weight, norm.bias, mha.linear_q.weight, mha.linear_q.bias,
+                                        mha.linear_k.weight, mha.linear_k.bias, mha.linear_v.weight,
+                                        mha.linear_v.bias, mha.output_layer.weight, mha.output_layer.bias, norm.eps,
+                                        mha.num_heads, graph, px, alias_rows)

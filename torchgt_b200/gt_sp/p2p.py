@@ -96,6 +96,7 @@ class PeerExchange:
         self.epoch = 0                 # barriers enqueued so far (host count, same on every rank)
         self.slots: List[Slot] = []
         self.side_stream = torch.cuda.Stream(device=device)   # pushes that overlap the caller's own work
+        self.trace = None              # list of (label, CUDA event) while a caller measures the phases of a step
         lib = _cabi.load()
         control_bytes = max(int(lib.tgt_p2p_control_bytes()), 256)
         self.control = self._new_symmetric(control_bytes)
@@ -128,6 +129,23 @@ class PeerExchange:
             self.slots.append(best)
         best.in_use = True
         return best
+
+    def mark(self, label: str) -> None:
+        """Record a timing event on the current stream when tracing is on (see ``start_trace``)."""
+        if self.trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(self.device))
+            self.trace.append((label, ev))
+
+    def start_trace(self) -> None:
+        self.trace = []
+        self.mark("start")
+
+    def stop_trace(self):
+        """Milliseconds between consecutive marks, as (label of the phase that ended, ms); waits for the device."""
+        torch.cuda.synchronize(self.device)
+        marks, self.trace = self.trace, None
+        return [(marks[i][0], marks[i - 1][1].elapsed_time(marks[i][1])) for i in range(1, len(marks))]
 
     def release(self, slot: Slot) -> None:
         slot.in_use = False
