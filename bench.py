@@ -930,24 +930,49 @@ def run_multi_gpu(args, dtype, rank, world):
     p2p.check_peer_exchanges()           # a barrier that gave up on a peer invalidates the timing
     note(f"graph {ms_per_step:.3f} ms")
 
-    # where the time of one step goes: CUDA events between the phases of eagerly issued steps (a profiler
-    # cannot wrap a multi-rank job here); a barrier's time includes waiting for the slowest rank
-    breakdown = None
+    # the exchange alone: the data movement of one step (both pushes, four barriers, both pulls) with the
+    # attention kernels left out, captured and replayed like the step itself
+    exchange_ms = None
     if px is not None:
-        totals = {}
-        n_traced = 20
-        for i in range(n_traced):
-            torch.cuda.synchronize(); dist.barrier()
-            px.start_trace()
-            step(i)
-            for label, ms in px.stop_trace():
-                totals[label] = totals.get(label, 0.0) + ms
-        labels = sorted(totals)
-        t = torch.tensor([totals[k] / n_traced for k in labels], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        breakdown = {k: round(v, 4) for k, v in zip(labels, t.tolist())}
-        breakdown["note"] = ("ms per step and phase, eager launches, max over ranks; 'barrier' sums the four barriers "
-                             "of a step (each includes the wait for the slowest rank and host launch gaps)")
+        heads_l = HEADS // world
+        row_bytes = heads_l * HEAD_DIM * sets[0][0].element_size()
+        tensor_bytes = n_rows * row_bytes
+        rows_dev = sp.get_global_token_rows_on(dev)
+        scratch_out = torch.empty(1, L + 1, HEADS * HEAD_DIM, dtype=dtype, device=dev)
+        scratch_grads = [torch.empty(1, L + 1, HEADS, HEAD_DIM, dtype=dtype, device=dev) for _ in range(3)]
+
+        def exchange_step(i):
+            q, k, v, dout = sets[i % ROTATING_SETS]
+            qkv = px.acquire(3 * tensor_bytes)
+            px.push([q.detach(), k.detach(), v.detach()], qkv, L + 1, row_bytes, (L + 1) * row_bytes)
+            px.barrier()
+            landing = px.acquire(tensor_bytes, p2p.SOURCE)
+            px.barrier()
+            px.pull(landing, [scratch_out], 1, L + 1, row_bytes, rows_dev)
+            px.release(landing)
+            landing = px.acquire(tensor_bytes)
+            px.push([dout], landing, L + 1, row_bytes, (L + 1) * row_bytes)
+            px.barrier()
+            grads = px.acquire(3 * tensor_bytes, p2p.SOURCE)
+            px.release(qkv); px.release(landing)
+            px.barrier()
+            px.pull(grads, scratch_grads, 1, L + 1, row_bytes)
+            px.release(grads)
+
+        with torch.cuda.stream(side):
+            for i in range(ROTATING_SETS):
+                exchange_step(i)
+        side.synchronize(); dist.barrier()
+        ex_graphs = []
+        for i in range(ROTATING_SETS):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                exchange_step(i)
+            ex_graphs.append(g)
+        torch.cuda.synchronize(); dist.barrier()
+        exchange_ms = timed(lambda i: ex_graphs[i % ROTATING_SETS].replay())
+        ex_graphs.clear()
+        p2p.check_peer_exchanges()
 
     # the attention alone (no exchange) on this rank's head slice of the same graph, for reference
     heads_local = HEADS // world
@@ -1041,7 +1066,11 @@ def run_multi_gpu(args, dtype, rank, world):
                                 "exchanges, downloads of out,dq,dk,dv; edge layouts resident"},
             "gpu_launches": launches * args.steps,
             "eager_ms_per_step": eager_ms,
-            "step_breakdown_ms": breakdown,
+            "exchange_only": None if exchange_ms is None else {
+                "ms_per_step": exchange_ms,
+                "bytes_over_nvlink_per_rank_each_way": int(8 * (L + 1) * HEADS * HEAD_DIM * elem * (world - 1) / world),
+                "note": "both pushes, four barriers and both pulls of one step without the attention kernels "
+                        "(CUDA graph); the pulls read slots nobody wrote in this leg, the bytes moved are the step's"},
             "epoch": epoch,
             "weak_scaling_training_step": weak,
             "attention_only": {"ms_per_step": op_ms, "value": n_edges / (op_ms * 1e-3), "unit": "edges/s",
