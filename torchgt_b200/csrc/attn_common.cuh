@@ -39,13 +39,14 @@ namespace tgt {
 #define TGT_STITCH_KERNEL_MAX_G 4
 #endif
 // Which walks use 32-byte lanes when nobody forces a lane width (see lane_bytes()).  Measured on B200
-// (fp32, 8-float heads, 64K-node batches and their 2-, 4- and 8-rank head slices): the forward and the dQ
-// pass gain on rows of 128 to 256 bytes (forward 55 -> 50 us, dQ 72 -> 62 us on 128-byte rows; dQ with
-// dbias 68 -> 65 us on 256-byte rows), the dQ pass also on 64-byte rows (86 -> 80 us); both lose on
-// 32-byte rows, and the dK/dV pass, with twice the accumulators per lane, loses 10-40 % everywhere.
+// (fp32, 8-float heads, 64K-node batches and their 2-, 4- and 8-rank head slices, 870K-node batch): the
+// forward gains on 128-byte rows (55 -> 50 us), the dQ pass on 64- and 128-byte rows (86 -> 80 us,
+// 72 -> 62 us).  On 256-byte rows they tie at 64K nodes and lose 4-5 % at 870K nodes, where K and V no
+// longer fit the L2 and the higher occupancy of the 16-byte-lane kernels (64-72 registers) counts; both
+// lose on 32-byte rows, and the dK/dV pass, with twice the accumulators per lane, loses 10-40 % everywhere.
 #ifndef TGT_WIDE_DEFAULT
 #define TGT_WIDE_DEFAULT(pass, row_bytes) \
-  ((pass) != kPassDkv && (row_bytes) <= 256 && (row_bytes) >= ((pass) == kPassDq ? 64 : 128))
+  ((pass) != kPassDkv && (row_bytes) <= 128 && (row_bytes) >= ((pass) == kPassDq ? 64 : 128))
 #endif
 // Edges per batch of the walk with 32-byte lanes (their operands take twice the registers).
 #ifndef TGT_WIDE_UNROLL
