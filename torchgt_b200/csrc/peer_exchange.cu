@@ -25,6 +25,8 @@
 //
 // Waits are bounded: after `spin_limit` polls the barrier gives up, records the rank it was waiting
 // for in a status word the host can read, and returns; the context stays usable.
+#include <cstdlib>
+
 #include "tgt_common.cuh"
 
 namespace tgt {
@@ -57,6 +59,27 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// The copy kernels move "units" of 16 bytes (uint4) or, where every width and address allows it, of 32
+// bytes (one 256-bit load / store of sm_100 per unit: half the requests per byte on the wire).
+struct alignas(32) Unit32 {
+  Raw32 r;
+};
+template <typename U>
+__device__ __forceinline__ U load_unit(const U* p) {
+  if constexpr (sizeof(U) == 32) {
+    U u;
+    u.r = ld_nc_256(p);
+    return u;
+  } else {
+    return *p;
+  }
+}
+template <typename U>
+__device__ __forceinline__ void store_unit(U* p, const U& v) {
+  if constexpr (sizeof(U) == 32) st_256(p, v.r);
+  else *p = v;
 }
 
 // Fused split + transfer + concatenate.  Source tensor t is [outer_s][world][ws] in 16-byte units
@@ -113,7 +136,7 @@ __global__ void push_kernel(Ptrs3 src, PeerTable landing, int n_tensors, int n_w
             break;
           }
       }
-      val[u] = static_cast<const U*>(src.p[t])[a * world * ws + pos];
+      val[u] = load_unit(static_cast<const U*>(src.p[t]) + (a * world * ws + pos));
       // final position on the destination, or (staged) this rank's contiguous block of the slot
       const int64_t og = f / wgv, o = f % wgv;
       const int64_t where = staged ? int64_t(rank) * chunk + f : (og * world + rank) * wgv + o;
@@ -121,7 +144,7 @@ __global__ void push_kernel(Ptrs3 src, PeerTable landing, int n_tensors, int n_w
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u)
-      if (dst[u] != nullptr) *dst[u] = val[u];
+      if (dst[u] != nullptr) store_unit(dst[u], val[u]);
   }
 }
 
@@ -163,12 +186,12 @@ __global__ void pull_kernel(Ptrs3 dst, PeerTable slots, int n_tensors, int64_t o
           src_row = 0;
           break;
         }
-      val[u] = static_cast<const U*>(slots.p[peer])[t * per_tensor_src + (o * world * rows + src_row) * wu + w];
+      val[u] = load_unit(static_cast<const U*>(slots.p[peer]) + (t * per_tensor_src + (o * world * rows + src_row) * wu + w));
       where[u] = static_cast<U*>(dst.p[t]) + ((o * rows + l) * world + peer) * wu + w;
     }
 #pragma unroll
     for (int u = 0; u < kBatch; ++u)
-      if (where[u] != nullptr) *where[u] = val[u];
+      if (where[u] != nullptr) store_unit(where[u], val[u]);
   }
 }
 
@@ -235,9 +258,29 @@ __global__ void fetch_kernel(Ptrs3 dst, const U* __restrict__ src, int n_tensors
   }
 }
 
+// CTAs per SM of the copy kernels; the environment variable TGT_P2P_CTAS (1..32) overrides the default
+// for tuning runs.
+int ctas_per_sm() {
+  static const int value = [] {
+    const char* e = getenv("TGT_P2P_CTAS");
+    const int v = e != nullptr ? atoi(e) : 0;
+    return v >= 1 && v <= 32 ? v : 8;
+  }();
+  return value;
+}
+
+// 32-byte units in the copy kernels; TGT_P2P_UNIT=16 in the environment keeps them at 16 bytes.
+bool wide_units() {
+  static const bool value = [] {
+    const char* e = getenv("TGT_P2P_UNIT");
+    return !(e != nullptr && atoi(e) == 16);
+  }();
+  return value;
+}
+
 int grid_for(int64_t n) {
   int64_t b = (n + kThreads - 1) / kThreads;
-  const int64_t cap = int64_t(sm_count()) * 8;
+  const int64_t cap = int64_t(sm_count()) * ctas_per_sm();
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return int(b);
@@ -289,11 +332,22 @@ extern "C" int tgt_p2p_push(const void* x0, const void* x1, const void* x2, int 
   if (rc != TGT_OK) return rc;
   Ptrs3 src;
   for (int t = 0; t < 3; ++t) src.p[t] = const_cast<void*>(xs[t]);
-  const int64_t ws = width_s_bytes / 16, wg = width_g_bytes / 16;
+  // 32-byte units when every width, row and address is a multiple of 32 bytes
+  bool wide = wide_units() && width_s_bytes % 32 == 0 && width_g_bytes % 32 == 0 && aligned32(x0) && aligned32(x1) &&
+              aligned32(x2) && (n_alias == 0 || alias_row_bytes % 32 == 0);
+  for (int i = 0; i < world; ++i) wide = wide && aligned32(tab.p[i]);
+  wide = wide && (outer_s * width_s_bytes * world) % 32 == 0;
+  const int ub = wide ? 32 : 16;
+  const int64_t ws = width_s_bytes / ub, wg = width_g_bytes / ub;
   const int64_t total = ((outer_s * ws + 255) / 256) * 256 * world * n_tensors;
-  push_kernel<uint4><<<grid_for((total + 3) / 4), kThreads, 0, stream>>>(
-      src, tab, n_tensors, mode == TGT_PUSH_WOVEN ? n_tensors : 1, outer_s, ws, wg, world, rank,
-      alias_rows, n_alias, n_alias > 0 ? alias_row_bytes / 16 : 1, mode == TGT_PUSH_STAGED);
+  if (wide)
+    push_kernel<Unit32><<<grid_for((total + 3) / 4), kThreads, 0, stream>>>(
+        src, tab, n_tensors, mode == TGT_PUSH_WOVEN ? n_tensors : 1, outer_s, ws, wg, world, rank,
+        alias_rows, n_alias, n_alias > 0 ? alias_row_bytes / ub : 1, mode == TGT_PUSH_STAGED);
+  else
+    push_kernel<uint4><<<grid_for((total + 3) / 4), kThreads, 0, stream>>>(
+        src, tab, n_tensors, mode == TGT_PUSH_WOVEN ? n_tensors : 1, outer_s, ws, wg, world, rank,
+        alias_rows, n_alias, n_alias > 0 ? alias_row_bytes / ub : 1, mode == TGT_PUSH_STAGED);
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }
@@ -320,10 +374,17 @@ extern "C" int tgt_p2p_pull(void* const* peer_slots, size_t slot_bytes, int n_te
   if (rc != TGT_OK) return rc;
   Ptrs3 dst;
   for (int t = 0; t < 3; ++t) dst.p[t] = ys[t];
-  const int64_t wu = width_bytes / 16;
+  bool wide = wide_units() && width_bytes % 32 == 0 && aligned32(y0) && aligned32(y1) && aligned32(y2);
+  for (int i = 0; i < world; ++i) wide = wide && aligned32(tab.p[i]);
+  wide = wide && (size_t(outer) * size_t(world) * size_t(rows) * size_t(width_bytes)) % 32 == 0;
+  const int64_t wu = width_bytes / (wide ? 32 : 16);
   const int64_t total = ((rows * wu + 255) / 256) * 256 * world * outer * n_tensors;
-  pull_kernel<uint4><<<grid_for((total + 7) / 8), kThreads, 0, stream>>>(dst, tab, n_tensors, outer, rows, wu,
-                                                                        world, rank, alias_rows, n_alias);
+  if (wide)
+    pull_kernel<Unit32><<<grid_for((total + 7) / 8), kThreads, 0, stream>>>(dst, tab, n_tensors, outer, rows, wu,
+                                                                           world, rank, alias_rows, n_alias);
+  else
+    pull_kernel<uint4><<<grid_for((total + 7) / 8), kThreads, 0, stream>>>(dst, tab, n_tensors, outer, rows, wu,
+                                                                          world, rank, alias_rows, n_alias);
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }
