@@ -1,42 +1,11 @@
-// Backward of the sparse graph attention: two passes without floating-point atomics that recompute the scores.
-//   pass A: edges sorted by destination -> dQ, and the row statistics
-//           stats[d,h] = { inv_d = 1/(Z+1e-6), delta_d = dO_d . O_d } that pass B reads
-//   pass B: edges sorted by source      -> dK and dV
-// Pass A needs delta_d before the row is complete.  Because O_d = inv_d * sum_e w_e V_s,
-// delta_d = inv_d * sum_e w_e (dO_d . V_s) is a sum over the same edges, so the pass accumulates
-//   A1 = sum mask w (dO.V) K,  A2 = sum mask w K,  S = sum w (dO.V)
-// and finishes the row with delta = inv S, dQ = inv (A1 - delta A2) / sqrt(D): no separate statistics
-// pass and no read of O.  Only when dbias is wanted (it needs delta per edge) a streaming pre-pass
-// computes the statistics from dO and O first and pass A uses them per edge.
-// With G = dO, inv = 1/(Z+1e-6), w = exp(clamp(raw)+bias):
-//   dw = (G_d.V_s - G_d.O_d) * inv_d      dV_s += w * inv_d * G_d      dt = dw * w  (= dbias)
-//   da = dt * [-5 <= raw <= 5]            dQ_d += da * K_s / sqrt(D)   dK_s += da * Q_d / sqrt(D)
-#include "attn_common.cuh"
+// Entry points of the backward of the sparse graph attention: argument checks, scratch planning, the
+// streaming row-statistics pre-pass, and the launches of the three passes (sparse_attn_bwd.cuh).
+#include "sparse_attn_bwd.cuh"
 
 namespace tgt {
-
 namespace {
 
-struct BwdParams {
-  const void* dout;
-  const void* q;
-  const void* k;
-  const void* v;
-  const void* out;
-  const float* z;
-  const float* bias;
-  int bias_heads;
-  void* dq;
-  void* dk;
-  void* dv;
-  float* dbias;
-  float2* stats;  // [n_rows, heads]
-  int heads, row_elems;
-  int64_t q_row_bytes, kv_row_bytes, g_row_bytes;   // distance between rows of q, of k / v and of dout
-  int64_t n_rows;
-  float inv_scale;
-  SegWalk walk;
-};
+using bwd::BwdParams;
 
 // ---- row statistics ---------------------------------------------------------------------------
 // One lane per 16-byte chunk of a row; the LPH lanes of a head are adjacent.
@@ -64,400 +33,6 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const BwdParams p) {
   }
 }
 
-// ---- pass A: dQ and dbias -----------------------------------------------------------------------
-template <typename T, int W, int LPH, int G>
-struct DqPolicy {
-  static constexpr int VEC = Lane<T, W>::kElems;
-  static constexpr int NACC = VEC;
-  static constexpr int kUnroll = walk_unroll<T, W, G>();
-
-  const T* __restrict__ q;
-  const T* __restrict__ k;
-  const T* __restrict__ v;
-  const T* __restrict__ dout;
-  const float2* __restrict__ stats;
-  const float* __restrict__ bias;
-  float* __restrict__ dbias;
-  T* __restrict__ dq;
-  int bias_stride, bias_off;
-  unsigned row_vecs, cvec, q_vecs, kv_vecs, g_vecs;
-  int heads, head;
-  bool head_leader, group_leader;
-  float inv_scale;
-
-  using Raw = typename Lane<T, W>::Raw;
-  struct Operands {
-    Raw k, v, q, g;  // packed 16-byte pieces, unpacked where they are used
-    float2 st;
-    float b;
-  };
-  struct Scalars {
-    float da;
-  };
-
-  __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
-    const unsigned so = unsigned(src) * kv_vecs + cvec;
-    o.k = Lane<T, W>::raw_at(k, so);
-    o.v = Lane<T, W>::raw_at(v, so);
-    o.q = Lane<T, W>::raw_at(q, unsigned(row) * q_vecs + cvec);
-    o.g = Lane<T, W>::raw_at(dout, unsigned(row) * g_vecs + cvec);
-    o.st = __ldg(stats + int64_t(row) * heads + head);
-    o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
-  }
-  __device__ __forceinline__ void clear(Operands& o) const {
-    o.k = o.v = o.q = o.g = Lane<T, W>::raw_zero();
-    o.st = make_float2(0.f, 0.f);
-    o.b = 0.f;
-  }
-  __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int pe) const {
-    float a[VEC], b[VEC];
-    Lane<T, W>::unpack(o.q, a);
-    Lane<T, W>::unpack(o.k, b);
-    const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
-    Lane<T, W>::unpack(o.g, a);
-    Lane<T, W>::unpack(o.v, b);
-    const float gv = group_sum<LPH>(dot<VEC>(a, b));
-    const float wgt = fast_exp(clamp_score(raw) + o.b);
-    const float dt = valid ? (gv - o.st.y) * o.st.x * wgt : 0.f;
-    if (dbias != nullptr) {
-      if (bias_stride == 1) {
-        const float s = sum_over_heads<LPH, G>(dt);   // every head's dt sits on all LPH lanes of the head
-        if (valid && group_leader) dbias[pe] = s;
-      } else if (valid && head_leader) {
-        dbias[int64_t(pe) * bias_stride + head] = dt;
-      }
-    }
-    Scalars s;
-    s.da = clamp_passes_grad(raw) ? dt : 0.f;
-    return s;
-  }
-  __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
-                                             const Scalars& s) const {
-    float kf[VEC];
-    Lane<T, W>::unpack(o.k, kf);
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) acc[j] = fmaf(s.da, kf[j], acc[j]);
-  }
-  __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {
-    float o[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o[j] = acc[j] * inv_scale;
-    Lane<T, W>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
-  }
-  __device__ __forceinline__ void zero_row(int row) const {
-    float o[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    Lane<T, W>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
-  }
-};
-
-// ---- pass A without a statistics pre-pass (no dbias) ---------------------------------------------
-template <typename T, int W, int LPH, int G>
-struct DqFusedPolicy {
-  static constexpr int VEC = Lane<T, W>::kElems;
-  static constexpr int NACC = 2 * VEC + 1;  // A1, A2, S
-  static constexpr int kUnroll = walk_unroll<T, W, G>();
-
-  const T* __restrict__ q;
-  const T* __restrict__ k;
-  const T* __restrict__ v;
-  const T* __restrict__ dout;
-  const float* __restrict__ z;
-  const float* __restrict__ bias;
-  float2* __restrict__ stats;
-  T* __restrict__ dq;
-  int bias_stride, bias_off;
-  unsigned row_vecs, cvec, q_vecs, kv_vecs, g_vecs;
-  int heads, head;
-  bool head_leader;
-  float inv_scale;
-
-  using Raw = typename Lane<T, W>::Raw;
-  struct Operands {
-    Raw k, v, q, g;
-    float b;
-  };
-  struct Scalars {
-    float wm, wgv_m, wgv;  // mask*w, mask*w*(dO.V), w*(dO.V)
-  };
-
-  __device__ __forceinline__ void load(Operands& o, int row, int src, int pe) const {
-    const unsigned so = unsigned(src) * kv_vecs + cvec;
-    o.k = Lane<T, W>::raw_at(k, so);
-    o.v = Lane<T, W>::raw_at(v, so);
-    o.q = Lane<T, W>::raw_at(q, unsigned(row) * q_vecs + cvec);
-    o.g = Lane<T, W>::raw_at(dout, unsigned(row) * g_vecs + cvec);
-    o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
-  }
-  __device__ __forceinline__ void clear(Operands& o) const {
-    o.k = o.v = o.q = o.g = Lane<T, W>::raw_zero();
-    o.b = 0.f;
-  }
-  __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
-    float a[VEC], b[VEC];
-    Lane<T, W>::unpack(o.q, a);
-    Lane<T, W>::unpack(o.k, b);
-    const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
-    Lane<T, W>::unpack(o.g, a);
-    Lane<T, W>::unpack(o.v, b);
-    const float gv = group_sum<LPH>(dot<VEC>(a, b));
-    const float wgt = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
-    Scalars s;
-    s.wgv = wgt * gv;
-    s.wm = clamp_passes_grad(raw) ? wgt : 0.f;
-    s.wgv_m = s.wm * gv;
-    return s;
-  }
-  __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
-                                             const Scalars& s) const {
-    float kf[VEC];
-    Lane<T, W>::unpack(o.k, kf);
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      acc[j] = fmaf(s.wgv_m, kf[j], acc[j]);
-      acc[VEC + j] = fmaf(s.wm, kf[j], acc[VEC + j]);
-    }
-    acc[2 * VEC] += s.wgv;
-  }
-  __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {
-    const float inv = 1.0f / (__ldg(z + int64_t(row) * heads + head) + kZEps);
-    const float delta = inv * acc[2 * VEC];
-    float o[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o[j] = (acc[j] - delta * acc[VEC + j]) * (inv * inv_scale);
-    Lane<T, W>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
-    if (head_leader) stats[int64_t(row) * heads + head] = make_float2(inv, delta);
-  }
-  __device__ __forceinline__ void zero_row(int row) const {
-    float o[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    Lane<T, W>::store_at(dq, unsigned(row) * row_vecs + cvec, o);
-  }
-};
-
-// ---- pass B: dK and dV --------------------------------------------------------------------------
-template <typename T, int W, int LPH, int G>
-struct DkvPolicy {
-  static constexpr int VEC = Lane<T, W>::kElems;
-  static constexpr int NACC = 2 * VEC;  // dK then dV
-  static constexpr int kUnroll = walk_unroll<T, W, G>();
-
-  const T* __restrict__ q;
-  const T* __restrict__ k;
-  const T* __restrict__ v;
-  const T* __restrict__ dout;
-  const float2* __restrict__ stats;
-  const float* __restrict__ bias;
-  T* __restrict__ dk;
-  T* __restrict__ dv;
-  int bias_stride, bias_off;
-  unsigned row_vecs, cvec, q_vecs, kv_vecs, g_vecs;
-  int heads, head;
-  float inv_scale;
-
-  using Raw = typename Lane<T, W>::Raw;
-  struct Operands {
-    Raw q, g, k, v;  // packed 16-byte pieces, unpacked where they are used
-    float2 st;
-    float b;
-  };
-  struct Scalars {
-    float da, wi;
-  };
-
-  // `row` is the source (K/V row), `dst` the destination whose Q, dO and statistics are gathered
-  __device__ __forceinline__ void load(Operands& o, int row, int dst, int pe) const {
-    const unsigned ro = unsigned(row) * kv_vecs + cvec;
-    o.q = Lane<T, W>::raw_at(q, unsigned(dst) * q_vecs + cvec);
-    o.g = Lane<T, W>::raw_at(dout, unsigned(dst) * g_vecs + cvec);
-    o.k = Lane<T, W>::raw_at(k, ro);
-    o.v = Lane<T, W>::raw_at(v, ro);
-    o.st = __ldg(stats + int64_t(dst) * heads + head);
-    o.b = bias != nullptr ? __ldg(bias + int64_t(pe) * bias_stride + bias_off) : 0.f;
-  }
-  __device__ __forceinline__ void clear(Operands& o) const {
-    o.k = o.v = o.q = o.g = Lane<T, W>::raw_zero();
-    o.st = make_float2(0.f, 0.f);
-    o.b = 0.f;
-  }
-  __device__ __forceinline__ Scalars prep(const Operands& o, bool valid, int) const {
-    float a[VEC], b[VEC];
-    Lane<T, W>::unpack(o.q, a);
-    Lane<T, W>::unpack(o.k, b);
-    const float raw = group_sum<LPH>(dot<VEC>(a, b)) * inv_scale;
-    Lane<T, W>::unpack(o.g, a);
-    Lane<T, W>::unpack(o.v, b);
-    const float gv = group_sum<LPH>(dot<VEC>(a, b));
-    const float wgt = valid ? fast_exp(clamp_score(raw) + o.b) : 0.f;
-    const float dt = (gv - o.st.y) * o.st.x * wgt;
-    Scalars s;
-    s.da = clamp_passes_grad(raw) ? dt : 0.f;
-    s.wi = wgt * o.st.x;
-    return s;
-  }
-  __device__ __forceinline__ void accumulate(float (&acc)[NACC], const Operands& o,
-                                             const Scalars& s) const {
-    float qf[VEC], gf[VEC];
-    Lane<T, W>::unpack(o.q, qf);
-    Lane<T, W>::unpack(o.g, gf);
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      acc[j] = fmaf(s.da, qf[j], acc[j]);
-      acc[VEC + j] = fmaf(s.wi, gf[j], acc[VEC + j]);
-    }
-  }
-  __device__ __forceinline__ void finalize(int row, const float (&acc)[NACC]) const {
-    float a[VEC], b[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      a[j] = acc[j] * inv_scale;
-      b[j] = acc[VEC + j];
-    }
-    const unsigned off = unsigned(row) * row_vecs + cvec;
-    Lane<T, W>::store_at(dk, off, a);
-    Lane<T, W>::store_at(dv, off, b);
-  }
-  __device__ __forceinline__ void zero_row(int row) const {
-    float o[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) o[j] = 0.f;
-    const unsigned off = unsigned(row) * row_vecs + cvec;
-    Lane<T, W>::store_at(dk, off, o);
-    Lane<T, W>::store_at(dv, off, o);
-  }
-};
-
-template <typename T, int W, int LPH, int G>
-__device__ __forceinline__ DqPolicy<T, W, LPH, G> make_dq_policy(const BwdParams& p) {
-  constexpr int VEC = Lane<T, W>::kElems;
-  const int c = threadIdx.x % G;
-  DqPolicy<T, W, LPH, G> pol;
-  pol.q = static_cast<const T*>(p.q);
-  pol.k = static_cast<const T*>(p.k);
-  pol.v = static_cast<const T*>(p.v);
-  pol.dout = static_cast<const T*>(p.dout);
-  pol.stats = p.stats;
-  pol.bias = p.bias;
-  pol.dbias = p.dbias;
-  pol.dq = static_cast<T*>(p.dq);
-  pol.head = blockIdx.y * (G / LPH) + c / LPH;
-  pol.bias_stride = p.bias_heads;
-  pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
-  pol.row_vecs = unsigned(p.row_elems / VEC);
-  pol.q_vecs = unsigned(p.q_row_bytes / W);
-  pol.kv_vecs = unsigned(p.kv_row_bytes / W);
-  pol.g_vecs = unsigned(p.g_row_bytes / W);
-  pol.heads = p.heads;
-  pol.cvec = blockIdx.y * G + c;
-  pol.head_leader = c % LPH == 0;
-  pol.group_leader = c == 0;
-  pol.inv_scale = p.inv_scale;
-  return pol;
-}
-
-template <typename T, int W, int LPH, int G>
-__device__ __forceinline__ DkvPolicy<T, W, LPH, G> make_dkv_policy(const BwdParams& p) {
-  constexpr int VEC = Lane<T, W>::kElems;
-  const int c = threadIdx.x % G;
-  DkvPolicy<T, W, LPH, G> pol;
-  pol.q = static_cast<const T*>(p.q);
-  pol.k = static_cast<const T*>(p.k);
-  pol.v = static_cast<const T*>(p.v);
-  pol.dout = static_cast<const T*>(p.dout);
-  pol.stats = p.stats;
-  pol.bias = p.bias;
-  pol.dk = static_cast<T*>(p.dk);
-  pol.dv = static_cast<T*>(p.dv);
-  pol.head = blockIdx.y * (G / LPH) + c / LPH;
-  pol.bias_stride = p.bias_heads;
-  pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
-  pol.row_vecs = unsigned(p.row_elems / VEC);
-  pol.q_vecs = unsigned(p.q_row_bytes / W);
-  pol.kv_vecs = unsigned(p.kv_row_bytes / W);
-  pol.g_vecs = unsigned(p.g_row_bytes / W);
-  pol.heads = p.heads;
-  pol.cvec = blockIdx.y * G + c;
-  pol.inv_scale = p.inv_scale;
-  return pol;
-}
-
-template <typename T, int W, int LPH, int G>
-__device__ __forceinline__ DqFusedPolicy<T, W, LPH, G> make_dq_fused_policy(const BwdParams& p) {
-  constexpr int VEC = Lane<T, W>::kElems;
-  const int c = threadIdx.x % G;
-  DqFusedPolicy<T, W, LPH, G> pol;
-  pol.q = static_cast<const T*>(p.q);
-  pol.k = static_cast<const T*>(p.k);
-  pol.v = static_cast<const T*>(p.v);
-  pol.dout = static_cast<const T*>(p.dout);
-  pol.z = p.z;
-  pol.bias = p.bias;
-  pol.stats = p.stats;
-  pol.dq = static_cast<T*>(p.dq);
-  pol.head = blockIdx.y * (G / LPH) + c / LPH;
-  pol.bias_stride = p.bias_heads;
-  pol.bias_off = p.bias_heads > 1 ? pol.head : 0;
-  pol.row_vecs = unsigned(p.row_elems / VEC);
-  pol.q_vecs = unsigned(p.q_row_bytes / W);
-  pol.kv_vecs = unsigned(p.kv_row_bytes / W);
-  pol.g_vecs = unsigned(p.g_row_bytes / W);
-  pol.heads = p.heads;
-  pol.cvec = blockIdx.y * G + c;
-  pol.head_leader = c % LPH == 0;
-  pol.inv_scale = p.inv_scale;
-  return pol;
-}
-
-template <typename T, int W, int LPH, int G>
-__global__ void TGT_WALK_BOUNDS bwd_dq_fused_kernel(const BwdParams p) {
-  using Policy = DqFusedPolicy<T, W, LPH, G>;
-  __shared__ TileSmem<G, Policy::NACC> sm;
-  const Policy pol = make_dq_fused_policy<T, W, LPH, G>(p);
-  walk_tile_in<G, Policy>(sm, p.walk, pol);
-}
-
-template <typename T, int W, int LPH, int G>
-__global__ void TGT_WALK_BOUNDS bwd_dq_kernel(const BwdParams p) {
-  using Policy = DqPolicy<T, W, LPH, G>;
-  __shared__ TileSmem<G, Policy::NACC> sm;
-  const Policy pol = make_dq_policy<T, W, LPH, G>(p);
-  walk_tile_in<G, Policy>(sm, p.walk, pol);
-}
-
-template <typename T, int W, int LPH, int G>
-__global__ void TGT_WALK_BOUNDS bwd_dkv_kernel(const BwdParams p) {
-  using Policy = DkvPolicy<T, W, LPH, G>;
-  __shared__ TileSmem<G, Policy::NACC> sm;
-  const Policy pol = make_dkv_policy<T, W, LPH, G>(p);
-  walk_tile_in<G, Policy>(sm, p.walk, pol);
-}
-
-template <typename T, int W, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) bwd_dq_fused_stitch_kernel(const BwdParams p) {
-  using Policy = DqFusedPolicy<T, W, LPH, G>;
-  const Policy pol = make_dq_fused_policy<T, W, LPH, G>(p);
-  __shared__ float s_part[kBlockThreads * Policy::NACC];
-  stitch_tiles<G, Policy>(p.walk, pol, s_part);
-}
-
-template <typename T, int W, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) bwd_dq_stitch_kernel(const BwdParams p) {
-  using Policy = DqPolicy<T, W, LPH, G>;
-  const Policy pol = make_dq_policy<T, W, LPH, G>(p);
-  __shared__ float s_part[kBlockThreads * Policy::NACC];
-  stitch_tiles<G, Policy>(p.walk, pol, s_part);
-}
-
-template <typename T, int W, int LPH, int G>
-__global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const BwdParams p) {
-  using Policy = DkvPolicy<T, W, LPH, G>;
-  const Policy pol = make_dkv_policy<T, W, LPH, G>(p);
-  __shared__ float s_part[kBlockThreads * Policy::NACC];
-  stitch_tiles<G, Policy>(p.walk, pol, s_part);
-}
-
 enum { kWalkDq = 0, kWalkDkv = 1, kWalkDqFused = 2 };
 
 int bwd_resident_ctas(int dtype, const HeadSplit& hs, int which) {
@@ -465,15 +40,9 @@ int bwd_resident_ctas(int dtype, const HeadSplit& hs, int which) {
   auto log2i = [](int x) { int l = 0; while ((1 << l) < x) ++l; return l; };
   const int dev = current_device();
   int* slot = &cache[dev < 0 ? 0 : dev][hs.w == 32 ? 1 : 0][which][dtype == TGT_F32 ? 0 : 1][log2i(hs.lph)][log2i(hs.g)];
-  int result = 4;
-  dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
-    using S = decltype(sh);
-    using T = typename S::T;
-    if (which == kWalkDkv) result = resident_ctas(bwd_dkv_kernel<T, S::W, S::LPH, S::G>, slot);
-    else if (which == kWalkDqFused) result = resident_ctas(bwd_dq_fused_kernel<T, S::W, S::LPH, S::G>, slot);
-    else result = resident_ctas(bwd_dq_kernel<T, S::W, S::LPH, S::G>, slot);
-  });
-  return result;
+  if (which == kWalkDkv) return bwd::occupancy_dkv(dtype, hs, slot);
+  if (which == kWalkDqFused) return bwd::occupancy_dq_fused(dtype, hs, slot);
+  return bwd::occupancy_dq(dtype, hs, slot);
 }
 
 struct BwdScratch {
@@ -691,33 +260,18 @@ extern "C" int tgt_sparse_attn_bwd_strided(const void* dout, int64_t dout_row_by
     fill_walk(&p.walk, *by_dst, sc.plan_a_fused, reinterpret_cast<float*>(base + sc.carry_a), counters_a,
               bias != nullptr);
     const dim3 grid(sc.plan_a_fused.n_tiles, hs.groups);
-    built = dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
-      using S = decltype(sh);
-      bwd_dq_fused_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
-      if (second_kernel && sc.plan_a_fused.n_tiles > 1)
-        bwd_dq_fused_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
-    });
+    built = bwd::launch_dq_fused(p, dtype, hs, grid, second_kernel, stream);
   } else if (passes & 2) {
     // pass A with per-edge dbias: uses the statistics of the pre-pass (stage 1)
     fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a), counters_a, true);
     const dim3 grid(sc.plan_a.n_tiles, hs.groups);
-    built = dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
-      using S = decltype(sh);
-      bwd_dq_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
-      if (second_kernel && sc.plan_a.n_tiles > 1)
-        bwd_dq_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
-    });
+    built = bwd::launch_dq(p, dtype, hs, grid, second_kernel, stream);
   }
   if (built && (passes & 4)) {
     fill_walk(&p.walk, *by_src, sc.plan_b, reinterpret_cast<float*>(base + sc.carry_b), counters_b,
               bias != nullptr);
     const dim3 grid(sc.plan_b.n_tiles, hsb.groups);
-    built = dispatch_shape(dtype, hsb.w, hsb.lph, hsb.g, [&](auto sh) {
-      using S = decltype(sh);
-      bwd_dkv_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
-      if (second_kernel_b && sc.plan_b.n_tiles > 1)
-        bwd_dkv_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
-    });
+    built = bwd::launch_dkv(p, dtype, hsb, grid, second_kernel_b, stream);
   }
   if (!built) return set_error(TGT_ERR_UNSUPPORTED, "no kernel is built for this head layout");
   TGT_CHECK_CUDA(cudaGetLastError());
