@@ -89,6 +89,16 @@ TGT_API int tgt_debug_set_tile_edges(int edges_per_lane_group);
 TGT_API int tgt_debug_set_lane_mode(int mode);
 
 /*
+ * Tuning / test knob with no counterpart in the reference: which consecutive kernels of one attention call
+ * are chained with programmatic dependent launches (the next kernel's CTAs stage their edge indices while
+ * the previous kernel drains, then wait for it to complete).  A bit mask: 1 = a walk kernel after the
+ * statistics kernel or another walk kernel, 2 = the kernel that finishes cross-tile rows after its walk
+ * kernel, 4 = a walk kernel after such a kernel; 0 launches everything one after the other, the default is
+ * 1 | 4.  The results are bitwise the same.  Process-wide.
+ */
+TGT_API int tgt_debug_set_dependent_launch(int links);
+
+/*
  * Bytes of device workspace tgt_edge_layout_build needs.
  * Replaces nothing in the reference (the reference keeps edges as an unsorted COO list).
  */

@@ -413,3 +413,37 @@ def test_strided_rows_k_and_v_side_by_side_give_the_same_bits(heads, head_dim, d
     # and they are right
     ref_out, _ = sao.forward_closed_form(q.float(), k.float(), v.float(), ei, bias)
     assert rel_err(results[1][0].float(), ref_out) < (TOL_F32 if dtype == torch.float32 else TOL_BF16)
+
+
+@pytest.mark.parametrize("heads,head_dim,dtype", [(1, 8, torch.float32), (2, 8, torch.float32), (8, 8, torch.float32),
+                                                  (8, 8, torch.bfloat16), (2, 64, torch.float32)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_dependent_launches_change_no_bit(heads, head_dim, dtype, with_bias):
+    """tgt_debug_set_dependent_launch: the kernels of a call chained with programmatic dependent launches in
+    every combination of links, on a graph cut into many tiles, against the same call with ordinary launches;
+    twice in a row each, so that a kernel that ran ahead of the one before it would show."""
+    from torchgt_b200 import _cabi
+    lib = _cabi.load()
+    n = 3000
+    ei = random_graph(77 + heads, n, 7.0)
+    gen = torch.Generator().manual_seed(3 * heads + head_dim)
+    q, k, v, dout = (torch.randn(n, heads, head_dim, generator=gen) for _ in range(4))
+    bias = torch.randn(ei.shape[1], generator=gen) * 0.2 if with_bias else None
+    results = {}
+    try:
+        for links in (0, 1, 2, 4, 5, 7):
+            _cabi.check(lib.tgt_debug_set_dependent_launch(links))
+            for _ in range(2):
+                results.setdefault(links, []).append(_run_cuda(q, k, v, ei, dout, bias, dtype=dtype, tile_edges=8))
+    finally:
+        _cabi.check(lib.tgt_debug_set_dependent_launch(5))
+    assert lib.tgt_debug_set_dependent_launch(8) != 0
+    _cabi.check(lib.tgt_debug_set_dependent_launch(5))
+    base = results[0][0]
+    for links, runs in results.items():
+        for res in runs:
+            for name in base:
+                assert torch.equal(res[name], base[name]), (links, name)
+    _check_against_closed_form(q.to(dtype).float(), k.to(dtype).float(), v.to(dtype).float(), ei,
+                               dout.to(dtype).float(), bias, {n_: t for n_, t in base.items() if n_ != "dbias"},
+                               TOL_F32 if dtype == torch.float32 else TOL_BF16)

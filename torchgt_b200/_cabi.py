@@ -70,6 +70,7 @@ SIGNATURES = {
                                             c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p,
                                             c_int]),
     "tgt_debug_set_lane_mode": (c_int, [c_int]),
+    "tgt_debug_set_dependent_launch": (c_int, [c_int]),
     "tgt_sparse_attn_fwd_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, _PL, c_void_p,
                                             c_void_p, c_int, c_int, c_int, c_void_p]),
     "tgt_sparse_attn_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,

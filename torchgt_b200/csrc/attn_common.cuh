@@ -206,6 +206,7 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
   const int te = NG * w.ge;
   const int64_t t0 = int64_t(blockIdx.x) * te;
   const int n = int(min(int64_t(te), int64_t(w.n_edges) - t0));  // edges in this tile (>= 1)
+  release_dependents();   // the next kernel of the call may take this SM's slots as they free up
 
   // ---- stage the tile's indices.  Tile edge i lives at position i + i / ge: one pad word per
   // lane-group range, so the groups of a warp (which read ranges ge apart) hit different banks.
@@ -224,6 +225,9 @@ __device__ __forceinline__ void walk_tile(const SegWalk& w, const Policy& pol, i
     s_halo[1] = t0 + n >= w.n_edges ? -2 : __ldg(w.seg + t0 + n);
   }
   for (int i = tid; i < 2 * NG; i += kBlockThreads) s_carry_row[i] = -3;  // [g][0] head row, [g][1] tail row
+  // the indices are the layout's, complete long before this call; everything below reads or overwrites what
+  // the previous kernel of the call works on
+  dependent_wait();
   __syncthreads();
 
   // ---- walk this group's range [gb, ge) of the tile
@@ -435,6 +439,8 @@ __device__ __forceinline__ void stitch_tiles(const SegWalk& w, const Policy& pol
   const int tile = blockIdx.x;
   const int te = TileGeom<G>::NG * w.ge;
   const int64_t t1 = int64_t(tile + 1) * te;
+  release_dependents();
+  dependent_wait();                                  // the walk kernel's carries; every CTA waits, also those that return
   if (t1 >= w.n_edges) return;                       // last tile: nothing runs past it
   const int r = __ldg(w.seg + t1 - 1);
   if (__ldg(w.seg + t1) != r) return;                // the tile ends on a row boundary

@@ -16,6 +16,7 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const BwdParams p) {
   const int chunks = p.row_elems / VEC;
   const int64_t total = p.n_rows * chunks;
   const bool live = idx < total;
+  release_dependents();   // pass A stages its edge indices while this kernel drains
   float g[VEC], o[VEC];
 #pragma unroll
   for (int j = 0; j < VEC; ++j) g[j] = o[j] = 0.f;
@@ -235,6 +236,17 @@ extern "C" int tgt_sparse_attn_bwd_strided(const void* dout, int64_t dout_row_by
   p.n_rows = n_rows;
   p.inv_scale = 1.0f / sqrtf(float(head_dim));
 
+  const bool second_kernel = stitch_in_second_kernel(hs.g);      // pass A
+  const bool second_kernel_b = stitch_in_second_kernel(hsb.g);   // pass B
+  int* counters_a = second_kernel ? nullptr : reinterpret_cast<int*>(base + sc.counters);
+  int* counters_b = second_kernel_b ? nullptr
+                                    : reinterpret_cast<int*>(base + sc.counters + sc.counter_bytes -
+                                                             sc.plan_b.counter_bytes);
+  if ((passes & 6) && !(second_kernel && second_kernel_b))
+    TGT_CHECK_CUDA(cudaMemsetAsync(base + sc.counters, 0, sc.counter_bytes, stream));
+  // from here on the kernels of this call follow one another on the stream without anything in between, and
+  // each is launched as the dependent of the one before
+  int link = 0;
   if (passes & 1) {
     // streaming pre-pass, always with 16-byte lanes
     const int lph16 = head_dim / (dtype == TGT_F32 ? 4 : 8);
@@ -244,15 +256,8 @@ extern "C" int tgt_sparse_attn_bwd_strided(const void* dout, int64_t dout_row_by
       using S = decltype(sh);
       bwd_stats_kernel<typename S::T, S::LPH><<<blocks, 256, 0, stream>>>(p);
     });
+    link = kLinkWalk;
   }
-  const bool second_kernel = stitch_in_second_kernel(hs.g);      // pass A
-  const bool second_kernel_b = stitch_in_second_kernel(hsb.g);   // pass B
-  int* counters_a = second_kernel ? nullptr : reinterpret_cast<int*>(base + sc.counters);
-  int* counters_b = second_kernel_b ? nullptr
-                                    : reinterpret_cast<int*>(base + sc.counters + sc.counter_bytes -
-                                                             sc.plan_b.counter_bytes);
-  if ((passes & 6) && !(second_kernel && second_kernel_b))
-    TGT_CHECK_CUDA(cudaMemsetAsync(base + sc.counters, 0, sc.counter_bytes, stream));
   // one walk kernel per pass, plus the kernel that finishes cross-tile rows when the lane group is narrow
   bool built = true;
   if ((passes & 2) && dbias == nullptr) {
@@ -260,18 +265,20 @@ extern "C" int tgt_sparse_attn_bwd_strided(const void* dout, int64_t dout_row_by
     fill_walk(&p.walk, *by_dst, sc.plan_a_fused, reinterpret_cast<float*>(base + sc.carry_a), counters_a,
               bias != nullptr);
     const dim3 grid(sc.plan_a_fused.n_tiles, hs.groups);
-    built = bwd::launch_dq_fused(p, dtype, hs, grid, second_kernel, stream);
+    built = bwd::launch_dq_fused(p, dtype, hs, grid, second_kernel, link, stream);
+    link = second_kernel && grid.x > 1 ? kLinkAfterStitch : kLinkWalk;
   } else if (passes & 2) {
     // pass A with per-edge dbias: uses the statistics of the pre-pass (stage 1)
     fill_walk(&p.walk, *by_dst, sc.plan_a, reinterpret_cast<float*>(base + sc.carry_a), counters_a, true);
     const dim3 grid(sc.plan_a.n_tiles, hs.groups);
-    built = bwd::launch_dq(p, dtype, hs, grid, second_kernel, stream);
+    built = bwd::launch_dq(p, dtype, hs, grid, second_kernel, link, stream);
+    link = second_kernel && grid.x > 1 ? kLinkAfterStitch : kLinkWalk;
   }
   if (built && (passes & 4)) {
     fill_walk(&p.walk, *by_src, sc.plan_b, reinterpret_cast<float*>(base + sc.carry_b), counters_b,
               bias != nullptr);
     const dim3 grid(sc.plan_b.n_tiles, hsb.groups);
-    built = bwd::launch_dkv(p, dtype, hsb, grid, second_kernel_b, stream);
+    built = bwd::launch_dkv(p, dtype, hsb, grid, second_kernel_b, link, stream);
   }
   if (!built) return set_error(TGT_ERR_UNSUPPORTED, "no kernel is built for this head layout");
   TGT_CHECK_CUDA(cudaGetLastError());

@@ -44,11 +44,15 @@ struct BwdParams {
 };
 
 // What sparse_attn_bwd.cu asks of each pass: launch it (plus the kernel that finishes cross-tile rows when
-// `second_kernel`), and the resident CTAs per SM of its walk kernel.  Both return false / 0 when no kernel
+// `second_kernel`; `link` != 0 = the kernel enqueued just before on the stream belongs to the same call, so
+// the walk kernel is launched as its dependent, see launch_chained), and the resident CTAs per SM of its walk kernel.  Both return false / 0 when no kernel
 // is built for the lane layout.
-bool launch_dq(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, cudaStream_t stream);
-bool launch_dq_fused(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, cudaStream_t stream);
-bool launch_dkv(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, cudaStream_t stream);
+bool launch_dq(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, int link,
+               cudaStream_t stream);
+bool launch_dq_fused(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, int link,
+                     cudaStream_t stream);
+bool launch_dkv(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, int link,
+                cudaStream_t stream);
 int occupancy_dq(int dtype, const HeadSplit& hs, int* cache_slot);
 int occupancy_dq_fused(int dtype, const HeadSplit& hs, int* cache_slot);
 int occupancy_dkv(int dtype, const HeadSplit& hs, int* cache_slot);

@@ -142,12 +142,13 @@ __global__ void __launch_bounds__(kBlockThreads) bwd_dkv_stitch_kernel(const Bwd
 
 }  // namespace
 
-bool launch_dkv(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, cudaStream_t stream) {
+bool launch_dkv(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, int link,
+                cudaStream_t stream) {
   return dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
     using S = decltype(sh);
-    bwd_dkv_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+    launch_chained(bwd_dkv_kernel<typename S::T, S::W, S::LPH, S::G>, grid, kBlockThreads, stream, link, p);
     if (second_kernel && grid.x > 1)
-      bwd_dkv_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+      launch_chained(bwd_dkv_stitch_kernel<typename S::T, S::W, S::LPH, S::G>, grid, kBlockThreads, stream, kLinkStitch, p);
   });
 }
 

@@ -136,12 +136,13 @@ __global__ void __launch_bounds__(kBlockThreads) bwd_dq_fused_stitch_kernel(cons
 
 }  // namespace
 
-bool launch_dq_fused(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, cudaStream_t stream) {
+bool launch_dq_fused(const BwdParams& p, int dtype, const HeadSplit& hs, dim3 grid, bool second_kernel, int link,
+                     cudaStream_t stream) {
   return dispatch_shape(dtype, hs.w, hs.lph, hs.g, [&](auto sh) {
     using S = decltype(sh);
-    bwd_dq_fused_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+    launch_chained(bwd_dq_fused_kernel<typename S::T, S::W, S::LPH, S::G>, grid, kBlockThreads, stream, link, p);
     if (second_kernel && grid.x > 1)
-      bwd_dq_fused_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+      launch_chained(bwd_dq_fused_stitch_kernel<typename S::T, S::W, S::LPH, S::G>, grid, kBlockThreads, stream, kLinkStitch, p);
   });
 }
 

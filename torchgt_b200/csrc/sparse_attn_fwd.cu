@@ -259,7 +259,7 @@ extern "C" int tgt_sparse_attn_fwd_strided(const void* q, int64_t q_row_bytes, c
     using S = decltype(sh);
     fwd_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
     if (second_kernel && tp.n_tiles > 1)
-      fwd_stitch_kernel<typename S::T, S::W, S::LPH, S::G><<<grid, kBlockThreads, 0, stream>>>(p);
+      launch_chained(fwd_stitch_kernel<typename S::T, S::W, S::LPH, S::G>, grid, kBlockThreads, stream, kLinkStitch, p);
   });
   if (!built) return set_error(TGT_ERR_UNSUPPORTED, "no kernel is built for this head layout");
   TGT_CHECK_CUDA(cudaGetLastError());

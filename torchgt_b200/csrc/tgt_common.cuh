@@ -41,6 +41,44 @@ int sm_count();
 
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// ---- programmatic dependent launch ----------------------------------------------------------------
+// Consecutive kernels of one entry point are chained so that the next kernel's CTAs are placed on an SM as
+// soon as the previous kernel's CTAs leave it, and do the part of their prologue that reads nothing the
+// previous kernel writes (staging edge indices) while the previous kernel drains.  Every kernel launched
+// this way executes dependent_wait() in all its CTAs before it touches such data and before it exits (so
+// completion stays transitive along the chain); in a kernel launched the ordinary way both calls do nothing.
+int dependent_launch_mask();   // tgt_debug_set_dependent_launch(): bits of the kinds of link that are chained
+enum {
+  kLinkWalk = 1,         // a walk kernel after the statistics kernel or after another walk kernel
+  kLinkStitch = 2,       // the kernel that finishes cross-tile rows after its walk kernel
+  kLinkAfterStitch = 4,  // a walk kernel after such a kernel
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void dependent_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launches kernel<<<grid, block, 0, stream>>>(params); a non-zero `link` (one of the kinds above) marks it as
+// the dependent of the kernel enqueued just before it on the stream, which must be one of this library's own.
+template <class P>
+inline cudaError_t launch_chained(void (*kernel)(const P), dim3 grid, unsigned block, cudaStream_t stream,
+                                  int link, const P& params) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  if (link & dependent_launch_mask()) {
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+#endif
+
 // ---- lane-wide vector access --------------------------------------------------------------------
 // One lane moves W bytes of a row, W = 16 (4 fp32 or 8 bf16 values) or 32 (8 fp32 / 16 bf16 values,
 // fetched with the 256-bit global loads and stores of sm_100), widened to fp32 registers.
