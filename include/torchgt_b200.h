@@ -399,6 +399,23 @@ TGT_API int tgt_pull_out_proj(void* const* peer_slots, size_t slot_bytes, const 
                               int64_t rows, int world, int rank, const int32_t* alias_rows, int n_alias,
                               void* stream);
 
+/*
+ * LayerNorm over short rows, fp32, forward and backward: the normalisation on both sides of the attention
+ * block (models/graphormer_dist_node_level.py:301,306,395; nn.LayerNorm(hidden) with weight and bias) and
+ * the backward of the LayerNorm inside tgt_ln_qkv_push.  hidden must be a multiple of 4, at most 512.
+ *   forward:  y = (x - mean) / sqrt(var + eps) * gamma + beta (biased variance, as torch.nn.LayerNorm);
+ *             stats (may be NULL) receives [rows][2] = mean, 1 / sqrt(var + eps) for the backward.
+ *   backward: dx, dgamma [hidden], dbeta [hidden] from dy, x, gamma and the forward's stats; scratch of
+ *             tgt_layer_norm_bwd_scratch_bytes holds per-CTA sums that a second kernel adds in a fixed
+ *             order (no atomics: results are bitwise reproducible).
+ */
+TGT_API int tgt_layer_norm_fwd(const float* x, const float* gamma, const float* beta, float eps, int64_t rows,
+                               int hidden, float* y, float* stats, void* stream);
+TGT_API int tgt_layer_norm_bwd_scratch_bytes(int64_t rows, int hidden, size_t* bytes);
+TGT_API int tgt_layer_norm_bwd(const float* dy, const float* x, const float* gamma, const float* stats,
+                               int64_t rows, int hidden, float* dx, float* dgamma, float* dbeta, void* scratch,
+                               size_t scratch_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,7 +17,9 @@ Outputs (all small .npz files, committed):
   layer_variants_P*.npz  the four Ulysses layer variants no reference model instantiates (global tokens
                  merged by mean), around a toy local attention: outputs and gradients, P ranks
   graphormer_node_level.npz  the reference's node-level Graphormer: parameters, log-probabilities, loss and
-                 parameter gradients of one training step (3 layers, dropout 0, one rank)
+                 parameter gradients of one training step (3 layers, dropout 0, one rank), in fp32 and (keys
+                 out64, loss64, grad64/...) with the model converted to fp64; the fp32 gradients differ by
+                 about 1e-6 from run to run (multi-threaded index_add_ in the CPU backward)
   gt_node_level.npz   the same for the reference's node-level GT (3 layers, no global token, one rank)
   gt_graph_level.npz  the reference's graph-level GT on two ranks (3 padded graphs of 40 integer-featured
                  nodes): output, loss and the gradient of one copy of the loss
@@ -329,6 +331,18 @@ def _model_worker(rank, world, ref_path, port, out_path):
     for name, p_ in model.named_parameters():
         if p_.grad is not None:
             rec["grad/" + name] = p_.grad.numpy()
+    # the same step of the same model in fp64: what both fp32 evaluations (the reference's above and the
+    # CUDA path's) approximate; gradients that are sums of cancelling terms are compared with this one
+    model64 = model.double()          # in place: the fp32 parameters and gradients are recorded above
+    model64.zero_grad(set_to_none=True)
+    out64 = model64(x.double(), None, ei, attn_type="sparse")
+    loss64 = torch.nn.functional.nll_loss(out64, y)
+    loss64.backward()
+    rec["out64"] = out64.detach().numpy()
+    rec["loss64"] = np.float64(loss64.item())
+    for name, p_ in model64.named_parameters():
+        if p_.grad is not None:
+            rec["grad64/" + name] = p_.grad.numpy()
     n_params = sum(p_.numel() for p_ in Graphormer(4, 8, 128, 64, 40, 1, 0.0, 0.0, 0.0, 64, 1).parameters())
     rec["params_of_the_readme_model"] = np.int64(n_params)     # the reference's README logs 111913
     np.savez_compressed(out_path, **rec)
@@ -716,13 +730,17 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of zxmeng98/torchgt")
     ap.add_argument("--only", default="", help="'gt' regenerates the GT and graph-level model files only, "
-                                               "'p8' the eight-rank exchange and layer files only, 'batching' the batch-construction file only")
+                                               "'p8' the eight-rank exchange and layer files only, 'batching' the batch-construction file only, "
+                                               "'model' the node-level Graphormer file only")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     install_shims()
     torch.set_num_threads(1)
     if args.only == "gt":
         make_gt_cases(args.reference)
+        return
+    if args.only == "model":
+        make_model_case(args.reference)
         return
     if args.only == "batching":
         make_batch_cases(args.reference)

@@ -9,9 +9,16 @@ from helpers import load_golden, rel_err
 
 pytestmark = pytest.mark.gpu
 
-# Through three encoder layers of library fp32 GEMMs / LayerNorms with other reduction orders than the
-# CPU run that produced the vectors; the attention itself is held to 1e-5 in test_gpu_attention.py.
+# Through three encoder layers of fp32 GEMMs / LayerNorms with other reduction orders than the CPU run
+# that produced the vectors; the attention itself is held to 1e-5 in test_gpu_attention.py.
 TOL_MODEL = 1e-4
+# Parameter gradients of the node-level Graphormer, where the vectors also hold the reference model's fp64
+# evaluation of the same step: the reference's own fp32 gradients are up to 1.8e-4 away from its fp64 ones
+# (graph_token.weight, linear_q.weight of layer 0: sums of cancelling terms through three layers) and differ
+# by 1e-6 between two runs on the same CPU, so an fp32 evaluation is held to 2e-4 against fp64 (as close as
+# the reference's own) and two fp32 evaluations to 3e-4 against each other.
+TOL_GRAD_VS_FP64 = 2e-4
+TOL_FP32_VS_FP32 = 3e-4
 
 
 def test_training_step_matches_the_reference_model():
@@ -30,11 +37,14 @@ def test_training_step_matches_the_reference_model():
     loss.backward()
     assert rel_err(out, g["out"]) < TOL_MODEL
     assert abs(float(loss) - float(g["loss"])) < TOL_MODEL * abs(float(g["loss"]))
+    assert rel_err(out, g["out64"]) < TOL_MODEL
+    assert abs(float(loss) - float(g["loss64"])) < TOL_MODEL * abs(float(g["loss64"]))
     checked = 0
     for name, p in model.named_parameters():
         key = "grad/" + name
         if key in g:
-            assert rel_err(p.grad, g[key]) < TOL_MODEL, name
+            assert rel_err(p.grad, g["grad64/" + name]) < TOL_GRAD_VS_FP64, name  # the reference model in fp64
+            assert rel_err(p.grad, g[key]) < TOL_FP32_VS_FP32, name             # the reference model in fp32
             checked += 1
         else:
             assert p.grad is None or float(p.grad.abs().max()) == 0.0, name   # graph_token_virtual_distance

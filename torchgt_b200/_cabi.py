@@ -5,7 +5,7 @@ There is no CPU fallback: if the library is missing or a call fails this module 
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_char_p, c_int, c_int64, c_size_t, c_uint32, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtorchgt_b200.so"
@@ -97,6 +97,10 @@ SIGNATURES = {
                                 c_int, c_void_p]),
     "tgt_pull_out_proj": (c_int, [POINTER(c_void_p), c_size_t, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                   c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "tgt_layer_norm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "tgt_layer_norm_bwd_scratch_bytes": (c_int, [c_int64, c_int, POINTER(c_size_t)]),
+    "tgt_layer_norm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_size_t, c_void_p]),
     "tgt_p2p_control_bytes": (c_size_t, []),
     "tgt_p2p_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), c_size_t, c_int64, c_int64,
                              c_int64, c_int, c_int, c_void_p, c_int, c_int64, c_int, c_void_p]),

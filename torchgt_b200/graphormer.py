@@ -18,6 +18,7 @@ from torch.nn import functional as F
 
 from .attn_module import CoreAttention
 from .gt_sp.initialize import get_sequence_parallel_group, sequence_parallel_is_initialized
+from .layer_norm import LayerNorm
 from .gt_sp.layer import DistributedAttentionNoMerge
 
 
@@ -84,10 +85,10 @@ class EncoderLayer(nn.Module):
 
     def __init__(self, hidden_size, ffn_size, dropout_rate, attention_dropout_rate, num_heads, attn_bias_dim=1):
         super().__init__()
-        self.self_attention_norm = nn.LayerNorm(hidden_size)
+        self.self_attention_norm = LayerNorm(hidden_size)
         self.self_attention = MultiHeadAttention(hidden_size, attention_dropout_rate, num_heads, attn_bias_dim)
         self.self_attention_dropout = nn.Dropout(dropout_rate)
-        self.ffn_norm = nn.LayerNorm(hidden_size)
+        self.ffn_norm = LayerNorm(hidden_size)
         self.ffn = FeedForwardNetwork(hidden_size, ffn_size, dropout_rate)
         self.ffn_dropout = nn.Dropout(dropout_rate)
 
@@ -139,7 +140,7 @@ class Graphormer(nn.Module):
             [EncoderLayer(hidden_dim, ffn_dim, dropout_rate, attention_dropout_rate, num_heads, attn_bias_dim)
              for _ in range(n_layers)])
         self.n_layers = n_layers
-        self.final_ln = nn.LayerNorm(hidden_dim)
+        self.final_ln = LayerNorm(hidden_dim)
         self.downstream_out_proj = nn.Linear(hidden_dim, output_dim)
         self.hidden_dim = hidden_dim
         self.num_global_node = num_global_node
@@ -204,7 +205,7 @@ class GraphormerGraphLevel(nn.Module):
         self.layers = nn.ModuleList(
             [EncoderLayer(hidden_dim, ffn_dim, dropout_rate, attention_dropout_rate, num_heads)
              for _ in range(n_layers)])
-        self.final_ln = nn.LayerNorm(hidden_dim)
+        self.final_ln = LayerNorm(hidden_dim)
         if dataset_name == "PCQM4M-LSC":
             self.out_proj = nn.Linear(hidden_dim, 1)
         else:

@@ -19,6 +19,7 @@ from torch.nn import functional as F
 from .attn_module import CoreAttentionQKV as CoreAttention  # (q, k, v) order, as models/gt_dist_node_level.py:83
 from .gt_sp.gt_layer import DistributedAttention, DistributedAttentionNodeLevel, _SeqGather
 from .gt_sp.initialize import get_sequence_parallel_group, sequence_parallel_is_initialized
+from .layer_norm import LayerNorm
 
 
 def _init_params(module: nn.Module, n_layers: int) -> None:
@@ -70,14 +71,14 @@ class EncoderLayer(nn.Module):
 
     def __init__(self, hidden_size, ffn_size, dropout_rate, attention_dropout_rate, num_heads, node_level=True):
         super().__init__()
-        self.self_attention_norm = nn.LayerNorm(hidden_size)   # a parameter of the reference, never applied
+        self.self_attention_norm = LayerNorm(hidden_size)   # a parameter of the reference, never applied
         self.self_attention = MultiHeadAttention(hidden_size, attention_dropout_rate, num_heads, node_level)
         self.self_attention_dropout = nn.Dropout(dropout_rate)
         self.O = nn.Linear(hidden_size, hidden_size)
-        self.layer_norm1 = nn.LayerNorm(hidden_size)
+        self.layer_norm1 = LayerNorm(hidden_size)
         self.FFN_layer1 = nn.Linear(hidden_size, hidden_size * 2)
         self.FFN_layer2 = nn.Linear(hidden_size * 2, hidden_size)
-        self.layer_norm2 = nn.LayerNorm(hidden_size)
+        self.layer_norm2 = LayerNorm(hidden_size)
 
     def forward(self, x, attn_bias=None, mask=None, edge_index=None, attn_type=None):
         y = self.self_attention(x, attn_bias, mask=mask, edge_index=edge_index, attn_type=attn_type)

@@ -23,7 +23,7 @@ from typing import Optional
 import torch
 from torch import Tensor
 
-from .. import _cabi
+from .. import _cabi, layer_norm
 from ..graph import SparseGraph, graph_for
 from ..sparse_attn import _DTYPES, _scratch, _stream
 from . import p2p
@@ -208,8 +208,9 @@ class _UlyssesAttentionBlock(torch.autograd.Function):
     in one kernel) -> barrier -> attention on the slot -> barrier -> ``tgt_pull_out_proj`` (gather over
     NVLink, global-token copy and output projection in one kernel).  No q, k, v tensor exists.
     Backward: the output projection's gradients (library GEMMs), then push dO -> barrier -> both attention
-    backward passes -> barrier -> pull dQ, dK, dV, then the gradients of the three projections and of the
-    LayerNorm from the saved layer input (the normalised input is recomputed, not stored)."""
+    backward passes -> barrier -> pull dQ, dK, dV, then the gradients of the three projections (library GEMMs)
+    and of the LayerNorm (csrc/layer_norm.cu) from the saved layer input (the normalised input is recomputed,
+    not stored)."""
 
     @staticmethod
     def forward(ctx, x, gamma, beta, wq, bq, wk, bk, wv, bv, wo, bo, eps, heads, graph, px, alias_rows):
@@ -297,16 +298,16 @@ class _UlyssesAttentionBlock(torch.autograd.Function):
         px.mark("pull dq,dk,dv")
         px.release(grads)
         px.check()
-        # the three projections and the LayerNorm (its output recomputed from the saved layer input)
-        with torch.enable_grad():
-            x_leaf = x.detach().requires_grad_()
-            g_leaf, b_leaf = gamma.detach().requires_grad_(), beta.detach().requires_grad_()
-            xn = torch.nn.functional.layer_norm(x_leaf, (hidden,), g_leaf, b_leaf, eps)
-        xn2 = xn.detach().view(-1, hidden)
+        # the three projections and the LayerNorm (its output recomputed from the saved layer input, not
+        # stored).  Running the dO push and the three pulls on a side stream under these library GEMMs was
+        # measured slower (5.67 against 5.57 ms per training iteration on two GPUs): the transfers are 20-50 us
+        # each and the extra graph edges and the contention for SMs cost more than the overlap hides.
+        xn, stats = layer_norm.forward_with_stats(x, gamma, beta, eps)
+        xn2 = xn.view(-1, hidden)
         d_wq, d_wk, d_wv = dq.t() @ xn2, dk.t() @ xn2, dv.t() @ xn2
         d_bq, d_bk, d_bv = dq.sum(dim=0), dk.sum(dim=0), dv.sum(dim=0)
         dxn = (dq @ wq).addmm_(dk, wk).addmm_(dv, wv).view(b, rows, hidden)
-        dx, d_gamma, d_beta = torch.autograd.grad(xn, (x_leaf, g_leaf, b_leaf), dxn)
+        dx, d_gamma, d_beta = layer_norm.backward(dxn, x, gamma, stats)
         return (dx, d_gamma, d_beta, d_wq, d_bq, d_wk, d_bk, d_wv, d_bv, d_wo, d_bo,
                 None, None, None, None, None)
 

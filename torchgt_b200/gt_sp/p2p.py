@@ -168,12 +168,13 @@ class PeerExchange:
                                      mode, self._stream()))
 
     def pull(self, slot: Slot, outs: Sequence[Tensor], outer: int, rows: int, width_bytes: int,
-             alias_rows: Optional[Tensor] = None) -> None:
+             alias_rows: Optional[Tensor] = None, offset_bytes: int = 0) -> None:
+        """Enqueue the gather of this rank's rows of the tensors that start ``offset_bytes`` into the peers' slots."""
         lib = _cabi.load()
         ptrs = [t.data_ptr() for t in outs] + [None] * (3 - len(outs))
         n_alias = 0 if alias_rows is None else int(alias_rows.numel())
-        _cabi.check(lib.tgt_p2p_pull(slot.peers, slot.nbytes, len(outs), ptrs[0], ptrs[1], ptrs[2], outer, rows,
-                                     width_bytes, self.world, self.rank,
+        _cabi.check(lib.tgt_p2p_pull(slot.peers_at(offset_bytes), slot.nbytes - offset_bytes, len(outs), ptrs[0],
+                                     ptrs[1], ptrs[2], outer, rows, width_bytes, self.world, self.rank,
                                      alias_rows.data_ptr() if n_alias else None, n_alias, self._stream()))
 
     def barrier(self) -> None:
