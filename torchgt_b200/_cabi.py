@@ -101,6 +101,9 @@ SIGNATURES = {
     "tgt_layer_norm_bwd_scratch_bytes": (c_int, [c_int64, c_int, POINTER(c_size_t)]),
     "tgt_layer_norm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_size_t, c_void_p]),
+    "tgt_linear_wgrad_scratch_bytes": (c_int, [c_int64, c_int, c_int, POINTER(c_size_t)]),
+    "tgt_linear_wgrad": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t,
+                                 c_void_p]),
     "tgt_p2p_control_bytes": (c_size_t, []),
     "tgt_p2p_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), c_size_t, c_int64, c_int64,
                              c_int64, c_int, c_int, c_void_p, c_int, c_int64, c_int, c_void_p]),

@@ -19,6 +19,7 @@ from torch.nn import functional as F
 from .attn_module import CoreAttention
 from .gt_sp.initialize import get_sequence_parallel_group, sequence_parallel_is_initialized
 from .layer_norm import LayerNorm
+from .linear import Linear
 from .gt_sp.layer import DistributedAttentionNoMerge
 
 
@@ -36,9 +37,9 @@ def _init_params(module: nn.Module, n_layers: int) -> None:
 class FeedForwardNetwork(nn.Module):
     def __init__(self, hidden_size: int, ffn_size: int, dropout_rate: float):
         super().__init__()
-        self.layer1 = nn.Linear(hidden_size, ffn_size)
+        self.layer1 = Linear(hidden_size, ffn_size)
         self.gelu = nn.GELU()
-        self.layer2 = nn.Linear(ffn_size, hidden_size)
+        self.layer2 = Linear(ffn_size, hidden_size)
 
     def forward(self, x):
         return self.layer2(self.gelu(self.layer1(x)))
@@ -52,13 +53,13 @@ class MultiHeadAttention(nn.Module):
         super().__init__()
         self.num_heads = num_heads
         self.att_size = hidden_size // num_heads
-        self.linear_q = nn.Linear(hidden_size, num_heads * self.att_size)
-        self.linear_k = nn.Linear(hidden_size, num_heads * self.att_size)
-        self.linear_v = nn.Linear(hidden_size, num_heads * self.att_size)
+        self.linear_q = Linear(hidden_size, num_heads * self.att_size)
+        self.linear_k = Linear(hidden_size, num_heads * self.att_size)
+        self.linear_v = Linear(hidden_size, num_heads * self.att_size)
         core = CoreAttention(hidden_size, attention_dropout_rate, num_heads, attn_bias_dim)
         group = get_sequence_parallel_group() if sequence_parallel_is_initialized() else None
         self.dist_attn = DistributedAttentionNoMerge(core, group)
-        self.output_layer = nn.Linear(num_heads * self.att_size, hidden_size)
+        self.output_layer = Linear(num_heads * self.att_size, hidden_size)
         # None: go through the sequence-parallel layer whenever a group exists; False: always attend
         # locally over the rows given (a single-GPU model inside a multi-rank job)
         self.sequence_parallel = None
@@ -134,14 +135,14 @@ class Graphormer(nn.Module):
                  input_dropout_rate, attention_dropout_rate, ffn_dim, num_global_node):
         super().__init__()
         self.num_heads = num_heads
-        self.node_encoder = nn.Linear(input_dim, hidden_dim)
+        self.node_encoder = Linear(input_dim, hidden_dim)
         self.input_dropout = nn.Dropout(input_dropout_rate)
         self.layers = nn.ModuleList(
             [EncoderLayer(hidden_dim, ffn_dim, dropout_rate, attention_dropout_rate, num_heads, attn_bias_dim)
              for _ in range(n_layers)])
         self.n_layers = n_layers
         self.final_ln = LayerNorm(hidden_dim)
-        self.downstream_out_proj = nn.Linear(hidden_dim, output_dim)
+        self.downstream_out_proj = Linear(hidden_dim, output_dim)
         self.hidden_dim = hidden_dim
         self.num_global_node = num_global_node
         self.graph_token = nn.Embedding(num_global_node, hidden_dim)
@@ -207,9 +208,9 @@ class GraphormerGraphLevel(nn.Module):
              for _ in range(n_layers)])
         self.final_ln = LayerNorm(hidden_dim)
         if dataset_name == "PCQM4M-LSC":
-            self.out_proj = nn.Linear(hidden_dim, 1)
+            self.out_proj = Linear(hidden_dim, 1)
         else:
-            self.downstream_out_proj = nn.Linear(hidden_dim, output_dim)
+            self.downstream_out_proj = Linear(hidden_dim, output_dim)
         self.apply(lambda m: _init_params(m, n_layers))   # embeddings are drawn over their padding row too
 
     def forward(self, batched_data, perturb=None, attn_type=None):

@@ -20,6 +20,7 @@ from .attn_module import CoreAttentionQKV as CoreAttention  # (q, k, v) order, a
 from .gt_sp.gt_layer import DistributedAttention, DistributedAttentionNodeLevel, _SeqGather
 from .gt_sp.initialize import get_sequence_parallel_group, sequence_parallel_is_initialized
 from .layer_norm import LayerNorm
+from .linear import Linear
 
 
 def _init_params(module: nn.Module, n_layers: int) -> None:
@@ -40,9 +41,9 @@ class MultiHeadAttention(nn.Module):
         super().__init__()
         self.num_heads = num_heads
         self.att_size = hidden_size // num_heads
-        self.linear_q = nn.Linear(hidden_size, num_heads * self.att_size)
-        self.linear_k = nn.Linear(hidden_size, num_heads * self.att_size)
-        self.linear_v = nn.Linear(hidden_size, num_heads * self.att_size)
+        self.linear_q = Linear(hidden_size, num_heads * self.att_size)
+        self.linear_k = Linear(hidden_size, num_heads * self.att_size)
+        self.linear_v = Linear(hidden_size, num_heads * self.att_size)
         core = CoreAttention(hidden_size, attention_dropout_rate, num_heads)
         group = get_sequence_parallel_group() if sequence_parallel_is_initialized() else None
         self.dist_attn = (DistributedAttentionNodeLevel if node_level else DistributedAttention)(core, group)
@@ -74,10 +75,10 @@ class EncoderLayer(nn.Module):
         self.self_attention_norm = LayerNorm(hidden_size)   # a parameter of the reference, never applied
         self.self_attention = MultiHeadAttention(hidden_size, attention_dropout_rate, num_heads, node_level)
         self.self_attention_dropout = nn.Dropout(dropout_rate)
-        self.O = nn.Linear(hidden_size, hidden_size)
+        self.O = Linear(hidden_size, hidden_size)
         self.layer_norm1 = LayerNorm(hidden_size)
-        self.FFN_layer1 = nn.Linear(hidden_size, hidden_size * 2)
-        self.FFN_layer2 = nn.Linear(hidden_size * 2, hidden_size)
+        self.FFN_layer1 = Linear(hidden_size, hidden_size * 2)
+        self.FFN_layer2 = Linear(hidden_size * 2, hidden_size)
         self.layer_norm2 = LayerNorm(hidden_size)
 
     def forward(self, x, attn_bias=None, mask=None, edge_index=None, attn_type=None):
@@ -95,8 +96,8 @@ class MLPReadout(nn.Module):
     def __init__(self, input_dim: int, output_dim: int, L: int = 2):
         super().__init__()
         dims = [input_dim // 2 ** i for i in range(L + 1)]
-        self.FC_layers = nn.ModuleList([nn.Linear(a, b) for a, b in zip(dims[:-1], dims[1:])] +
-                                       [nn.Linear(dims[-1], output_dim)])
+        self.FC_layers = nn.ModuleList([Linear(a, b) for a, b in zip(dims[:-1], dims[1:])] +
+                                       [Linear(dims[-1], output_dim)])
         self.L = L
 
     def forward(self, x):
@@ -113,13 +114,13 @@ class GTNodeLevel(nn.Module):
     def __init__(self, n_layers, num_heads, input_dim, hidden_dim, output_dim, attn_bias_dim, dropout_rate,
                  input_dropout_rate, attention_dropout_rate, ffn_dim, num_global_node):
         super().__init__()
-        self.node_encoder = nn.Linear(input_dim, hidden_dim)
+        self.node_encoder = Linear(input_dim, hidden_dim)
         self.input_dropout = nn.Dropout(input_dropout_rate)
         self.layers = nn.ModuleList(
             [EncoderLayer(hidden_dim, ffn_dim, dropout_rate, attention_dropout_rate, num_heads, node_level=True)
              for _ in range(n_layers)])
         self.MLP_layer = MLPReadout(hidden_dim, output_dim)
-        self.downstream_out_proj = nn.Linear(hidden_dim, output_dim)   # a parameter of the reference, never applied
+        self.downstream_out_proj = Linear(hidden_dim, output_dim)   # a parameter of the reference, never applied
         self.apply(lambda m: _init_params(m, n_layers))
 
     def forward(self, x, attn_bias, edge_index, perturb=None, attn_type=None):

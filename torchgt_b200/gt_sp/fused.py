@@ -23,7 +23,7 @@ from typing import Optional
 import torch
 from torch import Tensor
 
-from .. import _cabi, layer_norm
+from .. import _cabi, layer_norm, linear
 from ..graph import SparseGraph, graph_for
 from ..sparse_attn import _DTYPES, _scratch, _stream
 from . import p2p
@@ -207,10 +207,10 @@ class _UlyssesAttentionBlock(torch.autograd.Function):
     Forward: ``tgt_ln_qkv_push`` (LayerNorm, the three projections and the stores into the peers' slots
     in one kernel) -> barrier -> attention on the slot -> barrier -> ``tgt_pull_out_proj`` (gather over
     NVLink, global-token copy and output projection in one kernel).  No q, k, v tensor exists.
-    Backward: the output projection's gradients (library GEMMs), then push dO -> barrier -> both attention
-    backward passes -> barrier -> pull dQ, dK, dV, then the gradients of the three projections (library GEMMs)
-    and of the LayerNorm (csrc/layer_norm.cu) from the saved layer input (the normalised input is recomputed,
-    not stored)."""
+    Backward: the output projection's gradients, then push dO -> barrier -> both attention backward passes ->
+    barrier -> pull dQ, dK, dV, then the gradients of the three projections and of the LayerNorm from the saved
+    layer input (the normalised input is recomputed, not stored).  Input gradients are library GEMMs, weight
+    and bias gradients csrc/linear_wgrad.cu, the LayerNorm csrc/layer_norm.cu."""
 
     @staticmethod
     def forward(ctx, x, gamma, beta, wq, bq, wk, bk, wv, bv, wo, bo, eps, heads, graph, px, alias_rows):
@@ -266,8 +266,7 @@ class _UlyssesAttentionBlock(torch.autograd.Function):
         world, dev = px.world, x.device
         dy2 = dy.contiguous().view(-1, hidden)
         # output projection
-        d_wo = dy2.t() @ attn.view(-1, hidden)
-        d_bo = dy2.sum(dim=0)
+        d_wo, d_bo = linear.wgrad(dy2, attn.view(-1, hidden))
         dout = (dy2 @ wo).view(b, rows, hidden)
         px.check()
         landing = px.acquire(tensor_bytes)
@@ -304,8 +303,7 @@ class _UlyssesAttentionBlock(torch.autograd.Function):
         # each and the extra graph edges and the contention for SMs cost more than the overlap hides.
         xn, stats = layer_norm.forward_with_stats(x, gamma, beta, eps)
         xn2 = xn.view(-1, hidden)
-        d_wq, d_wk, d_wv = dq.t() @ xn2, dk.t() @ xn2, dv.t() @ xn2
-        d_bq, d_bk, d_bv = dq.sum(dim=0), dk.sum(dim=0), dv.sum(dim=0)
+        (d_wq, d_bq), (d_wk, d_bk), (d_wv, d_bv) = (linear.wgrad(g, xn2) for g in (dq, dk, dv))
         dxn = (dq @ wq).addmm_(dk, wk).addmm_(dv, wv).view(b, rows, hidden)
         dx, d_gamma, d_beta = layer_norm.backward(dxn, x, gamma, stats)
         return (dx, d_gamma, d_beta, d_wq, d_bq, d_wk, d_bk, d_wv, d_bv, d_wo, d_bo,
