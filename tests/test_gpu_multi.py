@@ -153,10 +153,10 @@ def test_gt_graph_level_model_on_two_gpus_matches_the_reference_on_two_ranks():
             assert ret[rank]["out"] < 1e-4 and ret[rank]["grads"] < 1e-4, (rank, dict(ret[rank]))
 
 
-def _graphormer_graph_worker(rank, world, port, ret):
+def _graphormer_graph_worker(rank, world, port, fused_block, ret):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
-                      TGT_P2P_SPIN_LIMIT="4000000")
+                      TGT_P2P_SPIN_LIMIT="4000000", TGT_FUSED_BLOCK=fused_block)
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -201,15 +201,17 @@ def _graphormer_graph_worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_graphormer_graph_level_model_on_two_gpus_matches_the_reference_rank_by_rank():
+@pytest.mark.parametrize("fused_block", ["1", "0"], ids=["fused-block", "layer-node"])
+def test_graphormer_graph_level_model_on_two_gpus_matches_the_reference_rank_by_rank(fused_block):
     """Batch of three graphs, every rank's own graph token in front of its slice: exercises the exchange and
-    the global-token copy with a batch dimension."""
+    the global-token copy with a batch dimension.  fused-block: LayerNorm, projections and exchange in the
+    kernels of csrc/fused_projection.cu; layer-node: library projections with the pushes started beside them."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     ctx = mp.get_context("spawn")
     with ctx.Manager() as manager:
         ret = manager.dict()
-        mp.spawn(_graphormer_graph_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+        mp.spawn(_graphormer_graph_worker, args=(2, _free_port(), fused_block, ret), nprocs=2, join=True)
         for rank in range(2):
             errs = dict(ret[rank])
             assert errs["out"] < 1e-4 and errs["grads"] < 1e-4 and errs["checked"] >= 35, (rank, errs)
