@@ -939,6 +939,23 @@ def run_multi_gpu(args, dtype, rank, world):
     p2p.check_peer_exchanges()           # a barrier that gave up on a peer invalidates the timing
     note(f"graph {ms_per_step:.3f} ms")
 
+    # TGT_BENCH_KERNEL_LIST=1: device time of every kernel of the replayed step on rank 0, from the CUPTI
+    # activity records torch.profiler collects (a per-rank tool: every rank runs the same replays).  The
+    # kernels of a chain of dependent launches start before their predecessor ends, so their times overlap.
+    kernel_list = None
+    if os.environ.get("TGT_BENCH_KERNEL_LIST"):
+        from torch.profiler import ProfilerActivity, profile
+        reps = 2 * ROTATING_SETS
+        torch.cuda.synchronize(); dist.barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(reps):
+                graphs[i % ROTATING_SETS].replay()
+            torch.cuda.synchronize()
+        rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+        kernel_list = [{"kernel": e.key[:100], "launches_per_step": e.count / reps,
+                        "us_per_step": e.device_time_total / reps} for e in rows if e.device_time_total > 0]
+        dist.barrier()
+
     # the exchange alone: the data movement of one step (both pushes, four barriers, both pulls) with the
     # attention kernels left out, captured and replayed like the step itself
     exchange_ms = None
@@ -1082,6 +1099,7 @@ def run_multi_gpu(args, dtype, rank, world):
                         "(CUDA graph); the pulls read slots nobody wrote in this leg, the bytes moved are the step's"},
             "epoch": epoch,
             "weak_scaling_training_step": weak,
+            "kernel_list": kernel_list,
             "attention_only": {"ms_per_step": op_ms, "value": n_edges / (op_ms * 1e-3), "unit": "edges/s",
                                "note": "same graph, this rank's head slice, no exchange (CUDA graph)",
                                "frac_of_hbm_peak": step_bytes / (op_ms * 1e-3) / 1e9 / peak},
