@@ -126,7 +126,7 @@ def make_inputs(n_rows, n_edges, dtype, seed, device):
     return cast(q), cast(k), cast(v), cast(dout), (bias.to(device) if device is not None else bias)
 
 
-def cpu_reference_rate(edge_index, n_rows, steps, warmup, budget_s=20.0, seed=1234, with_bias=True):
+def cpu_reference_rate(edge_index, n_rows, steps, warmup, time_limit_s=20.0, seed=1234, with_bias=True):
     """Edges/s of the reference's CPU operation sequence (oracle/sparse_attn_oracle.sparse_attention_ops,
     float32, autograd backward) with all host threads, on a bounded edge sample of the workload."""
     from oracle.sparse_attn_oracle import sparse_attention_ops
@@ -147,7 +147,7 @@ def cpu_reference_rate(edge_index, n_rows, steps, warmup, budget_s=20.0, seed=12
     one(probe, bias[:probe_edges])
     t_probe = one(probe, bias[:probe_edges])
     per_edge = t_probe / probe_edges
-    sample_edges = int(min(n_edges, max(probe_edges, budget_s / max(steps + warmup, 1) / per_edge)))
+    sample_edges = int(min(n_edges, max(probe_edges, time_limit_s / max(steps + warmup, 1) / per_edge)))
     if sample_edges >= n_edges:
         ei, b, what = edge_index, bias, f"full workload ({n_edges} edges, {n_rows} rows)"
     else:
@@ -171,7 +171,7 @@ def run_reference_arm(args, rank):
         edge_index = adjust_edge_index_nomerge(edge_index, NODES_PER_RANK)
         n_rows = args.gpus * (NODES_PER_RANK + 1)
     # N = 1 times the op with a scalar edge bias (gradient included), N > 1 the layer's own call: no bias
-    base, mean = cpu_reference_rate(edge_index, n_rows, args.steps, max(args.warmup, 1), budget_s=150.0,
+    base, mean = cpu_reference_rate(edge_index, n_rows, args.steps, max(args.warmup, 1), time_limit_s=150.0,
                                     with_bias=args.gpus == 1)
     line = {
         "impl": "reference", "metric": "sparse_graph_attention_fwd_bwd_edges_per_s", "value": base["value"],
@@ -710,7 +710,7 @@ def run_single_gpu(args, dtype):
     achieved = bytes_[dominant] / (phase_ms[dominant] * 1e-3) / 1e9
     step_bytes = sum(bytes_.values())
     step_achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
-    cpu, _ = cpu_reference_rate(edge_index, n_rows, steps=5, warmup=2, budget_s=20.0)
+    cpu, _ = cpu_reference_rate(edge_index, n_rows, steps=5, warmup=2, time_limit_s=20.0)
     epoch = None
     if dtype == torch.float32 and os.environ.get("TGT_BENCH_EPOCH", "1") != "0":
         try:
@@ -951,9 +951,16 @@ def run_multi_gpu(args, dtype, rank, world):
             for i in range(reps):
                 graphs[i % ROTATING_SETS].replay()
             torch.cuda.synchronize()
-        rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
-        kernel_list = [{"kernel": e.key[:100], "launches_per_step": e.count / reps,
-                        "us_per_step": e.device_time_total / reps} for e in rows if e.device_time_total > 0]
+        # median duration per kernel name (the first replays wait at their barriers for the rank whose
+        # profiler started last, which a mean would charge to the barrier kernel)
+        from torch.autograd import DeviceType
+        per_name = {}
+        for e in prof.events():
+            if e.device_type == DeviceType.CUDA and e.device_time_total > 0:
+                per_name.setdefault(e.name, []).append(e.device_time_total)
+        kernel_list = sorted(({"kernel": name[:100], "launches_per_step": len(d) / reps,
+                               "us_per_step": statistics.median(d) * len(d) / reps} for name, d in per_name.items()),
+                             key=lambda r: -r["us_per_step"])
         dist.barrier()
 
     # the exchange alone: the data movement of one step (both pushes, four barriers, both pulls) with the

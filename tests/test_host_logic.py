@@ -156,3 +156,25 @@ def test_gt_and_graph_level_shells_load_reference_checkpoints(sp_state):
         state = {k[len("param/"):]: torch.from_numpy(v) for k, v in g.items() if k.startswith("param/")}
         assert set(state) == set(model.state_dict())
         model.load_state_dict(state, strict=True)
+
+
+def test_layer_norm_and_linear_modules_are_torch_modules_on_the_cpu():
+    """On host tensors (and for shapes the kernels do not cover) the two dense modules of the model shells
+    are ``nn.LayerNorm`` / ``nn.Linear`` themselves: same parameters, same ``state_dict`` keys, same numbers."""
+    from torchgt_b200.layer_norm import LayerNorm
+    from torchgt_b200.linear import Linear
+    torch.manual_seed(5)
+    ln, ref_ln = LayerNorm(64), torch.nn.LayerNorm(64)
+    lin, ref_lin = Linear(64, 64), torch.nn.Linear(64, 64)
+    assert list(ln.state_dict()) == list(ref_ln.state_dict()) and list(lin.state_dict()) == list(ref_lin.state_dict())
+    assert isinstance(ln, torch.nn.LayerNorm) and isinstance(lin, torch.nn.Linear)
+    ref_ln.load_state_dict(ln.state_dict())
+    ref_lin.load_state_dict(lin.state_dict())
+    x = torch.randn(7, 64, requires_grad=True)
+    y = lin(ln(x))
+    y.sum().backward()
+    x2 = x.detach().clone().requires_grad_()
+    y2 = ref_lin(ref_ln(x2))
+    y2.sum().backward()
+    assert torch.equal(y, y2) and torch.equal(x.grad, x2.grad)
+    assert torch.equal(lin.weight.grad, ref_lin.weight.grad) and torch.equal(ln.weight.grad, ref_ln.weight.grad)
