@@ -182,30 +182,16 @@ __global__ void __launch_bounds__(kLnThreads) layer_norm_bwd_kernel(const LnBwdP
   }
 }
 
-// dgamma[j] = sum over CTAs of partial[cta][0][j], dbeta likewise.  A block owns 32 consecutive values; its
-// warp w adds the CTAs w, w + 8, ... (two running sums), then the eight sums are added in warp order: a
-// fixed association, whatever the timing.
-__global__ void __launch_bounds__(256) layer_norm_param_grad_kernel(const float* __restrict__ partial, int ctas,
-                                                                    int hidden, float* __restrict__ dgamma,
-                                                                    float* __restrict__ dbeta) {
-  __shared__ float s_part[8][32];
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int i = blockIdx.x * 32 + lane;
-  float s0 = 0.f, s1 = 0.f;
-  if (i < 2 * hidden) {
-    int b = warp;
-    for (; b + 8 < ctas; b += 16) {
-      s0 += __ldg(partial + int64_t(b) * 2 * hidden + i);
-      s1 += __ldg(partial + int64_t(b + 8) * 2 * hidden + i);
-    }
-    if (b < ctas) s0 += __ldg(partial + int64_t(b) * 2 * hidden + i);
-  }
-  s_part[warp][lane] = s0 + s1;
-  __syncthreads();
-  if (warp == 0 && i < 2 * hidden) {
-    float s = s_part[0][lane];
-#pragma unroll
-    for (int w = 1; w < 8; ++w) s += s_part[w][lane];
+// dgamma[j] = sum over CTAs of partial[cta][0][j], dbeta likewise (sum_partials: fixed association).
+__global__ void __launch_bounds__(kPartialSumThreads) layer_norm_param_grad_kernel(const float* __restrict__ partial,
+                                                                                   int ctas, int hidden,
+                                                                                   float* __restrict__ dgamma,
+                                                                                   float* __restrict__ dbeta) {
+  __shared__ float s_part[16][32];
+  const int i = blockIdx.x * 32 + threadIdx.x % 32;
+  const bool live = i < 2 * hidden;
+  const float s = sum_partials(partial, ctas, int64_t(2) * hidden, i, live, s_part);
+  if (threadIdx.x < 32 && live) {
     if (i < hidden) dgamma[i] = s;
     else dbeta[i - hidden] = s;
   }
@@ -307,7 +293,7 @@ extern "C" int tgt_layer_norm_bwd(const float* dy, const float* x, const float* 
     layer_norm_bwd_kernel<decltype(L)::value, decltype(P)::value><<<grid, kLnThreads, 0, stream>>>(p);
   });
   if (!built) return set_error(TGT_ERR_UNSUPPORTED, "no LayerNorm kernel for hidden=%d", hidden);
-  layer_norm_param_grad_kernel<<<(2 * hidden + 31) / 32, 256, 0, stream>>>(p.partial, grid, hidden, dgamma, dbeta);
+  layer_norm_param_grad_kernel<<<(2 * hidden + 31) / 32, kPartialSumThreads, 0, stream>>>(p.partial, grid, hidden, dgamma, dbeta);
   TGT_CHECK_CUDA(cudaGetLastError());
   return TGT_OK;
 }

@@ -79,6 +79,39 @@ inline cudaError_t launch_chained(void (*kernel)(const P), dim3 grid, unsigned b
 }
 #endif
 
+// ---- sums of per-CTA partial results -----------------------------------------------------------------
+// out[i] = sum over b < n_parts of partial[b * pitch + i] for the 32 consecutive values a block of
+// kPartialSumThreads threads owns (i = blockIdx.x * 32 + lane).  Warp w adds the parts w, w + 16, ... with
+// eight loads in flight and eight running sums, the sixteen warps' results are added in warp order: the
+// association is fixed, so the result does not depend on timing.  Returns the sum in warp 0's lanes.
+constexpr int kPartialSumThreads = 512;
+#ifdef __CUDACC__
+__device__ __forceinline__ float sum_partials(const float* __restrict__ partial, int n_parts, int64_t pitch, int i,
+                                              bool live, float (&s_part)[16][32]) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.f;
+  if (live) {
+    for (int b = warp; b < n_parts; b += 16 * 8) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int bb = b + 16 * j;
+        if (bb < n_parts) s[j] += __ldg(partial + int64_t(bb) * pitch + i);
+      }
+    }
+  }
+  s_part[warp][lane] = ((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]));
+  __syncthreads();
+  float total = 0.f;
+  if (warp == 0) {
+#pragma unroll
+    for (int w = 0; w < 16; ++w) total += s_part[w][lane];
+  }
+  return total;
+}
+#endif
+
 // ---- lane-wide vector access --------------------------------------------------------------------
 // One lane moves W bytes of a row, W = 16 (4 fp32 or 8 bf16 values) or 32 (8 fp32 / 16 bf16 values,
 // fetched with the 256-bit global loads and stores of sm_100), widened to fp32 registers.
