@@ -27,6 +27,7 @@ namespace {
 constexpr int kMaxWorld = 16;
 constexpr int kThreads = 256;
 constexpr int kTileRows = 32;
+static_assert(kTileRows == 4 * (kThreads / 32), "tile_gemm gives every warp four rows of the tile");
 
 struct PeerTable {
   void* p[kMaxWorld];
@@ -46,34 +47,33 @@ struct QkvParams {
   int world, rank;
 };
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  return v;
-}
-
-// out[r][c] = sum_k a[r][k] * w[c][k] for the thread's rows {2 ty, 2 ty + 1} and columns {j * 16 + tx}.
-// a: [kTileRows][K + 4], w: [COLS][K + 4] in shared memory (the padding keeps quarter-warps of 128-bit
-// loads on different banks).
+// out[r][c] = sum_k a[r][k] * w[c][k] for the thread's rows {4 warp .. 4 warp + 3} and columns {j * 32 + lane}.
+// a: [kTileRows][K + 4], w: [COLS][K + 4] in shared memory.  Per step of four k a warp reads four row pieces
+// (one address for all lanes: one shared-memory wavefront each) and NJ weight pieces (32 different rows whose
+// pitch of K + 4 words puts every quarter warp on all 32 banks once: four wavefronts each) for 16 NJ FMAs per
+// thread.  With two rows x 16 column groups per warp instead, both halves of the warp fetched the same weight
+// pieces and the kernel spent twice the shared-memory wavefronts per FMA (LayerNorm + projections 90 us).
 template <int K, int NJ>
-__device__ __forceinline__ void tile_gemm(const float* __restrict__ a, const float* __restrict__ w, int ty, int tx,
-                                          float (&acc)[2][NJ]) {
+__device__ __forceinline__ void tile_gemm(const float* __restrict__ a, const float* __restrict__ w, int warp, int lane,
+                                          float (&acc)[4][NJ]) {
   constexpr int LD = K + 4;
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < NJ; ++j) acc[i][j] = 0.f;
-#pragma unroll 4
+#pragma unroll 2
   for (int k = 0; k < K; k += 4) {
-    const float4 a0 = *reinterpret_cast<const float4*>(a + (2 * ty) * LD + k);
-    const float4 a1 = *reinterpret_cast<const float4*>(a + (2 * ty + 1) * LD + k);
+    float4 av[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(a + (4 * warp + i) * LD + k);
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
-      const float4 b = *reinterpret_cast<const float4*>(w + (j * 16 + tx) * LD + k);
-      acc[0][j] = fmaf(a0.x, b.x, acc[0][j]); acc[0][j] = fmaf(a0.y, b.y, acc[0][j]);
-      acc[0][j] = fmaf(a0.z, b.z, acc[0][j]); acc[0][j] = fmaf(a0.w, b.w, acc[0][j]);
-      acc[1][j] = fmaf(a1.x, b.x, acc[1][j]); acc[1][j] = fmaf(a1.y, b.y, acc[1][j]);
-      acc[1][j] = fmaf(a1.z, b.z, acc[1][j]); acc[1][j] = fmaf(a1.w, b.w, acc[1][j]);
+      const float4 b = *reinterpret_cast<const float4*>(w + (j * 32 + lane) * LD + k);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i][j] = fmaf(av[i].x, b.x, acc[i][j]); acc[i][j] = fmaf(av[i].y, b.y, acc[i][j]);
+        acc[i][j] = fmaf(av[i].z, b.z, acc[i][j]); acc[i][j] = fmaf(av[i].w, b.w, acc[i][j]);
+      }
     }
   }
 }
@@ -91,7 +91,7 @@ template <int HIDDEN, int OUT>
 __global__ void __launch_bounds__(kThreads) ln_qkv_push_kernel(const QkvParams p) {
   constexpr int LD = HIDDEN + 4;
   constexpr int LDO = QkvSmem<HIDDEN, OUT>::LDO;
-  constexpr int NJ = 3 * OUT / 16;                 // output columns per thread
+  constexpr int NJ = 3 * OUT / 32;                 // output columns per thread
   extern __shared__ __align__(16) float smem[];
   float* s_w = smem;                               // [3 * OUT][LD]
   float* s_b = s_w + 3 * OUT * LD;                 // [3 * OUT]
@@ -109,65 +109,87 @@ __global__ void __launch_bounds__(kThreads) ln_qkv_push_kernel(const QkvParams p
     s_g[HIDDEN + i] = p.gamma != nullptr ? __ldg(p.beta + i) : 0.f;
   }
   const int warp = tid / 32, lane = tid % 32;
-  const int ty = tid / 16, tx = tid % 16;
   const int cols_per_peer = OUT / p.world;         // floats of one head slice
   const int units_per_row = cols_per_peer / 4;     // 16-byte units one peer gets from one row and tensor
   const int64_t n_tiles = (p.rows_total + kTileRows - 1) / kTileRows;
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int64_t row0 = tile * kTileRows;
-    const int n = int(min(int64_t(kTileRows), p.rows_total - row0));
-    __syncthreads();                               // the previous tile's stores have read s_o; weights are in place
-    for (int i = tid; i < kTileRows * (HIDDEN / 4); i += kThreads) {
-      const int r = i / (HIDDEN / 4), k4 = i % (HIDDEN / 4);
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < n) v = __ldg(reinterpret_cast<const float4*>(p.x + (row0 + r) * HIDDEN) + k4);
-      *reinterpret_cast<float4*>(s_x + r * LD + 4 * k4) = v;
+  // A thread owns two 16-byte pieces of the input tile: column piece k4 of rows r_a and r_a + 16; the 16
+  // threads with the same r_a are half a warp and hold whole rows, so the LayerNorm is two shuffle sums.  The
+  // pieces of the NEXT tile are fetched into registers before the arithmetic of this one.
+  static_assert(HIDDEN == 64 && kTileRows == 32 && kThreads == 256, "the tile's pieces are dealt two per thread");
+  const int r_a = tid / 16, k4 = tid % 16;
+  float4 nx[2];
+  auto fetch = [&](int64_t tile) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t row = tile * kTileRows + r_a + 16 * h;
+      nx[h] = tile < n_tiles && row < p.rows_total ? __ldg(reinterpret_cast<const float4*>(p.x + row * HIDDEN) + k4)
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    __syncthreads();
-    if (p.gamma != nullptr) {
-      // LayerNorm, one warp per row: biased variance, as torch.nn.LayerNorm
-      for (int r = warp; r < n; r += kThreads / 32) {
-        float v[HIDDEN / 32];
-        float s = 0.f;
+  };
+  auto half_warp_sum = [](float v) {
 #pragma unroll
-        for (int i = 0; i < HIDDEN / 32; ++i) { v[i] = s_x[r * LD + lane + 32 * i]; s += v[i]; }
-        const float mean = warp_sum(s) * (1.0f / HIDDEN);
-        float q = 0.f;
-#pragma unroll
-        for (int i = 0; i < HIDDEN / 32; ++i) { v[i] -= mean; q += v[i] * v[i]; }
-        const float rstd = 1.0f / sqrtf(warp_sum(q) * (1.0f / HIDDEN) + p.eps);
-#pragma unroll
-        for (int i = 0; i < HIDDEN / 32; ++i) {
-          const int k = lane + 32 * i;
-          s_x[r * LD + k] = v[i] * rstd * s_g[k] + s_g[HIDDEN + k];
-        }
-      }
-      __syncthreads();
-    }
-    float acc[2][NJ];
-    tile_gemm<HIDDEN, NJ>(s_x, s_w, ty, tx, acc);
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int j = 0; j < NJ; ++j) s_o[(2 * ty + i) * LDO + j * 16 + tx] = acc[i][j] + s_b[j * 16 + tx];
-    __syncthreads();
-    // Store the tile: for every tensor and peer the rows of the tile are one contiguous run on the peer
-    // (gathered row = (batch entry * world + rank) * rows + l, row width = one head slice).
+    for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+  };
+  // Which pieces of the output tile this thread stores, and where to: the same for every tile (3 * 32 * 16
+  // pieces of 16 bytes = 6 per thread), so the divisions are done once.
+  constexpr int kStores = 3 * kTileRows * (OUT / 4) / kThreads;
+  int st_row[kStores], st_from[kStores];       // row inside the tile; word offset inside s_o
+  float4* st_base[kStores];                     // the peer's tensor, at this piece's position inside a row
+  {
     const int units_per_run = kTileRows * units_per_row;
-    const int total_units = 3 * p.world * units_per_run;
-    for (int u = tid; u < total_units; u += kThreads) {
+#pragma unroll
+    for (int j = 0; j < kStores; ++j) {
+      const int u = tid + j * kThreads;
       const int run = u / units_per_run, in_run = u % units_per_run;
       const int t = run / p.world;
       const int peer = (p.rank + 1 + run % p.world) % p.world;     // start with the next rank
       const int r = in_run / units_per_row, w = in_run % units_per_row;
-      if (r >= n) continue;
-      const int64_t gi = row0 + r;
-      const int64_t bi = gi / p.rows, l = gi % p.rows;
-      const int64_t dest_row = (bi * p.world + p.rank) * p.rows + l;
-      const float4 val = *reinterpret_cast<const float4*>(s_o + r * LDO + t * OUT + peer * cols_per_peer + 4 * w);
-      float4* dst = reinterpret_cast<float4*>(static_cast<char*>(p.slots.p[peer]) + t * p.tensor_bytes) +
-                    dest_row * units_per_row + w;
-      *dst = val;
+      st_row[j] = r;
+      st_from[j] = r * LDO + t * OUT + peer * cols_per_peer + 4 * w;
+      st_base[j] = reinterpret_cast<float4*>(static_cast<char*>(p.slots.p[peer]) + t * p.tensor_bytes) + w;
+    }
+  }
+  const unsigned rows_u = unsigned(p.rows);
+  fetch(blockIdx.x);
+  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int64_t row0 = tile * kTileRows;
+    const int n = int(min(int64_t(kTileRows), p.rows_total - row0));
+    __syncthreads();               // the previous tile's arithmetic has read s_x, its stores s_o; weights are in place
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float4 v = nx[h];
+      if (p.gamma != nullptr) {
+        // LayerNorm: biased variance, as torch.nn.LayerNorm
+        const float mean = half_warp_sum((v.x + v.y) + (v.z + v.w)) * (1.0f / HIDDEN);
+        v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
+        const float var = half_warp_sum((v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w)) * (1.0f / HIDDEN);
+        const float rstd = 1.0f / sqrtf(var + p.eps);
+        const float4 g = *reinterpret_cast<const float4*>(s_g + 4 * k4);
+        const float4 bt = *reinterpret_cast<const float4*>(s_g + HIDDEN + 4 * k4);
+        v.x = v.x * rstd * g.x + bt.x; v.y = v.y * rstd * g.y + bt.y;
+        v.z = v.z * rstd * g.z + bt.z; v.w = v.w * rstd * g.w + bt.w;
+      }
+      *reinterpret_cast<float4*>(s_x + (r_a + 16 * h) * LD + 4 * k4) = v;
+    }
+    __syncthreads();
+    fetch(tile + gridDim.x);
+    float acc[4][NJ];
+    tile_gemm<HIDDEN, NJ>(s_x, s_w, warp, lane, acc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) s_o[(4 * warp + i) * LDO + j * 32 + lane] = acc[i][j] + s_b[j * 32 + lane];
+    __syncthreads();
+    // Store the tile: for every tensor and peer the rows of the tile are one contiguous run on the peer
+    // (gathered row = (batch entry * world + rank) * rows + l, row width = one head slice).
+#pragma unroll
+    for (int j = 0; j < kStores; ++j) {
+      if (st_row[j] >= n) continue;
+      const unsigned gi = unsigned(row0) + unsigned(st_row[j]);
+      const unsigned bi = gi / rows_u, l = gi - bi * rows_u;
+      const int64_t dest_row = (int64_t(bi) * p.world + p.rank) * p.rows + l;
+      st_base[j][dest_row * units_per_row] = *reinterpret_cast<const float4*>(s_o + st_from[j]);
     }
   }
 }
@@ -193,7 +215,7 @@ struct OutSmem {
 template <int HIDDEN, int OUT>
 __global__ void __launch_bounds__(kThreads) pull_out_proj_kernel(const OutProjParams p) {
   constexpr int LD = OUT + 4;
-  constexpr int NJ = HIDDEN / 16;
+  constexpr int NJ = HIDDEN / 32;
   extern __shared__ __align__(16) float smem[];
   float* s_w = smem;                  // [HIDDEN][LD]
   float* s_b = s_w + HIDDEN * LD;     // [HIDDEN]
@@ -201,44 +223,65 @@ __global__ void __launch_bounds__(kThreads) pull_out_proj_kernel(const OutProjPa
   const int tid = threadIdx.x;
   for (int i = tid; i < HIDDEN * OUT; i += kThreads) s_w[(i / OUT) * LD + i % OUT] = __ldg(p.w + i);
   for (int i = tid; i < HIDDEN; i += kThreads) s_b[i] = __ldg(p.b + i);
-  const int ty = tid / 16, tx = tid % 16;
+  const int warp = tid / 32, lane = tid % 32;
   const int cols_per_peer = OUT / p.world;
   const int units_per_row = cols_per_peer / 4;
   const int64_t n_tiles = (p.rows_total + kTileRows - 1) / kTileRows;
-  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int64_t row0 = tile * kTileRows;
-    const int n = int(min(int64_t(kTileRows), p.rows_total - row0));
-    __syncthreads();
-    // gather: for every peer the tile's rows are one contiguous run in the peer's slot
-    const int units_per_run = kTileRows * units_per_row;
-    for (int u = tid; u < p.world * units_per_run; u += kThreads) {
-      const int run = u / units_per_run, in_run = u % units_per_run;
-      const int peer = (p.rank + 1 + run) % p.world;
-      const int r = in_run / units_per_row, w = in_run % units_per_row;
-      float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < n) {
-        const int64_t gi = row0 + r;
-        const int64_t bi = gi / p.rows, l = gi % p.rows;
+  // gather: for every peer the tile's rows are one contiguous run in the peer's slot; a thread owns two
+  // 16-byte pieces of the tile and fetches those of the NEXT tile (over NVLink) before the arithmetic of this one
+  static_assert(OUT == 64 && kTileRows == 32 && kThreads == 256, "the tile's pieces are dealt two per thread");
+  const int units_per_run = kTileRows * units_per_row;
+  int g_peer[2], g_row[2], g_unit[2];           // the same for every tile
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int u = tid + h * kThreads;
+    const int run = u / units_per_run, in_run = u % units_per_run;
+    g_peer[h] = (p.rank + 1 + run) % p.world;
+    g_row[h] = in_run / units_per_row;
+    g_unit[h] = in_run % units_per_row;
+  }
+  const unsigned rows_u = unsigned(p.rows);
+  float4 nv[2];
+  auto fetch = [&](int64_t tile) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t gi64 = tile * kTileRows + g_row[h];
+      nv[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tile < n_tiles && gi64 < p.rows_total) {
+        const unsigned gi = unsigned(gi64);
+        const unsigned bi = gi / rows_u, l = gi - bi * rows_u;
         int64_t src_row = int64_t(p.rank) * p.rows + l;
         for (int j = 0; j < p.n_alias; ++j)
           if (src_row == p.alias_rows[j]) {   // global-token slots take row 0's output
             src_row = 0;
             break;
           }
-        val = *(reinterpret_cast<const float4*>(p.slots.p[peer]) + (bi * p.world * p.rows + src_row) * units_per_row + w);
-        *(reinterpret_cast<float4*>(p.ctx + gi * OUT + peer * cols_per_peer) + w) = val;
+        nv[h] = *(reinterpret_cast<const float4*>(p.slots.p[g_peer[h]]) +
+                  (int64_t(bi) * p.world * p.rows + src_row) * units_per_row + g_unit[h]);
       }
-      *reinterpret_cast<float4*>(s_c + r * LD + peer * cols_per_peer + 4 * w) = val;
+    }
+  };
+  fetch(blockIdx.x);
+  for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int64_t row0 = tile * kTileRows;
+    const int n = int(min(int64_t(kTileRows), p.rows_total - row0));
+    __syncthreads();               // the previous tile's arithmetic has read s_c
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = g_row[h], col = g_peer[h] * cols_per_peer + 4 * g_unit[h];
+      if (r < n) *reinterpret_cast<float4*>(p.ctx + (row0 + r) * OUT + col) = nv[h];
+      *reinterpret_cast<float4*>(s_c + r * LD + col) = nv[h];
     }
     __syncthreads();
-    float acc[2][NJ];
-    tile_gemm<OUT, NJ>(s_c, s_w, ty, tx, acc);
+    fetch(tile + gridDim.x);
+    float acc[4][NJ];
+    tile_gemm<OUT, NJ>(s_c, s_w, warp, lane, acc);
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int r = 2 * ty + i;
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * warp + i;
       if (r < n) {
 #pragma unroll
-        for (int j = 0; j < NJ; ++j) p.y[(row0 + r) * HIDDEN + j * 16 + tx] = acc[i][j] + s_b[j * 16 + tx];
+        for (int j = 0; j < NJ; ++j) p.y[(row0 + r) * HIDDEN + j * 32 + lane] = acc[i][j] + s_b[j * 32 + lane];
       }
     }
   }
@@ -279,7 +322,7 @@ extern "C" int tgt_ln_qkv_push(const float* x, const float* gamma, const float* 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(x && wq && bq && wk && bk && wv && bv, "x, the three weights and the three biases must not be null");
   TGT_CHECK_ARG((gamma == nullptr) == (beta == nullptr), "give both LayerNorm parameters or neither");
-  TGT_CHECK_ARG(batch >= 1 && rows >= 1, "batch and rows must be positive");
+  TGT_CHECK_ARG(batch >= 1 && rows >= 1 && batch * rows < (int64_t(1) << 31), "batch and rows must be positive, batch * rows below 2^31");
   TGT_CHECK_ARG(rank >= 0 && rank < world, "rank outside the world");
   if (!(hidden == 64 && out_features == 64))
     return set_error(TGT_ERR_UNSUPPORTED, "the fused projection is built for hidden = projection width = 64");
@@ -312,7 +355,7 @@ extern "C" int tgt_pull_out_proj(void* const* peer_slots, size_t slot_bytes, con
   using namespace tgt;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(w && b && ctx && y, "w, b, ctx and y must not be null");
-  TGT_CHECK_ARG(batch >= 1 && rows >= 1, "batch and rows must be positive");
+  TGT_CHECK_ARG(batch >= 1 && rows >= 1 && batch * rows < (int64_t(1) << 31), "batch and rows must be positive, batch * rows below 2^31");
   TGT_CHECK_ARG(rank >= 0 && rank < world, "rank outside the world");
   if (!(hidden == 64 && in_features == 64))
     return set_error(TGT_ERR_UNSUPPORTED, "the fused projection is built for hidden = projection width = 64");

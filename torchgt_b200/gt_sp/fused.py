@@ -196,17 +196,13 @@ def ulysses_sparse_attention(px: "p2p.PeerExchange", query: Tensor, key: Tensor,
 
 # ---- the attention half of an encoder layer as one node -----------------------------------------------
 def fused_block_enabled() -> bool:
-    """Whether the encoder layers take ``_UlyssesAttentionBlock``.  ``TGT_FUSED_BLOCK=1`` / ``0`` in the
-    environment decides; without it the block is used when matrix products are kept in fp32
-    (``torch.backends.cuda.matmul.allow_tf32`` off, torch's default): its projections are fp32 FMA inside the
-    kernels that store to and gather from the peers, which beats separate fp32 library GEMMs plus the
-    exchange by far (LayerNorm + three projections 90 us against 193 us before any transfer), but not TF32
-    tensor-core GEMMs with the pushes running beside them (training iteration on two GPUs 3.62 ms with the
-    block, 3.50 ms without, TF32 allowed)."""
-    choice = os.environ.get("TGT_FUSED_BLOCK")
-    if choice is not None:
-        return choice != "0"
-    return not torch.backends.cuda.matmul.allow_tf32
+    """Whether the encoder layers take ``_UlyssesAttentionBlock`` (default; ``TGT_FUSED_BLOCK=0`` in the
+    environment selects the layer node with library projections and the q and k pushes beside them instead).
+    Whole training iteration on two GPUs, 64,000 nodes each: 3.36 ms with the block, 3.38 ms without when the
+    library may use TF32 tensor cores; with fp32 library products the block is far ahead (its LayerNorm + three
+    projections take 57 us in fp32 FMA including the stores, the library's fp32 path 190 us before any
+    transfer)."""
+    return os.environ.get("TGT_FUSED_BLOCK", "1") != "0"
 
 
 class _UlyssesAttentionBlock(torch.autograd.Function):
