@@ -17,6 +17,10 @@ __global__ void __launch_bounds__(256) bwd_stats_kernel(const BwdParams p) {
   const int64_t total = p.n_rows * chunks;
   const bool live = idx < total;
   release_dependents();   // pass A stages its edge indices while this kernel drains
+  // the arrival counters of both walks, which start only after this kernel has completed: saves the memset
+  // node in front of the call
+  if (blockIdx.x == 0 && p.clear_words != nullptr)
+    for (int i = threadIdx.x; i < p.n_clear_words; i += blockDim.x) p.clear_words[i] = 0;
   float g[VEC], o[VEC];
 #pragma unroll
   for (int j = 0; j < VEC; ++j) g[j] = o[j] = 0.f;
@@ -242,8 +246,16 @@ extern "C" int tgt_sparse_attn_bwd_strided(const void* dout, int64_t dout_row_by
   int* counters_b = second_kernel_b ? nullptr
                                     : reinterpret_cast<int*>(base + sc.counters + sc.counter_bytes -
                                                              sc.plan_b.counter_bytes);
-  if ((passes & 6) && !(second_kernel && second_kernel_b))
-    TGT_CHECK_CUDA(cudaMemsetAsync(base + sc.counters, 0, sc.counter_bytes, stream));
+  p.clear_words = nullptr;
+  p.n_clear_words = 0;
+  if ((passes & 6) && !(second_kernel && second_kernel_b)) {
+    if (passes & 1) {   // the statistics kernel clears them on its way
+      p.clear_words = reinterpret_cast<int*>(base + sc.counters);
+      p.n_clear_words = int(sc.counter_bytes / sizeof(int));
+    } else {
+      TGT_CHECK_CUDA(cudaMemsetAsync(base + sc.counters, 0, sc.counter_bytes, stream));
+    }
+  }
   // from here on the kernels of this call follow one another on the stream without anything in between, and
   // each is launched as the dependent of the one before
   int link = 0;

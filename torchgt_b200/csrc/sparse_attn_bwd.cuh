@@ -40,6 +40,8 @@ struct BwdParams {
   int64_t q_row_bytes, kv_row_bytes, g_row_bytes;   // distance between rows of q, of k / v and of dout
   int64_t n_rows;
   float inv_scale;
+  int* clear_words;      // arrival counters the statistics pre-pass zeroes for the two walks (or null)
+  int n_clear_words;
   SegWalk walk;
 };
 
