@@ -420,8 +420,8 @@ TGT_API int tgt_layer_norm_bwd(const float* dy, const float* x, const float* gam
  * Weight and bias gradient of a narrow nn.Linear over many rows, fp32: dw [out_features, in_features] =
  * dy^T x and db [out_features] (may be NULL) = column sums of dy, for dy [rows, out_features] and x [rows,
  * in_features] — the backward of the models' projections and FFN layers (models/graphormer_dist_node_level.py:
- * 241-245,281-286,343) with respect to their parameters.  in_features and out_features must be multiples of
- * 64, at most 1024 (TGT_ERR_UNSUPPORTED otherwise: the caller uses a library GEMM).  Per-CTA tiles are added
+ * 241-245,281-286,343) with respect to their parameters.  in_features must be a multiple of 64, out_features
+ * of 4, both at most 1024 (TGT_ERR_UNSUPPORTED otherwise: the caller uses a library GEMM).  Per-CTA tiles are added
  * in a fixed order by a second kernel (no atomics, bitwise reproducible); scratch of
  * tgt_linear_wgrad_scratch_bytes holds them.
  */

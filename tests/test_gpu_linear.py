@@ -12,7 +12,8 @@ def _err(got, ref):
     return float((got.double().cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
 
 
-@pytest.mark.parametrize("in_features,out_features", [(64, 64), (128, 64), (64, 128), (192, 64)])
+@pytest.mark.parametrize("in_features,out_features", [(64, 64), (128, 64), (64, 128), (192, 64), (64, 40), (128, 4),
+                                                      (64, 100)])
 @pytest.mark.parametrize("rows", [1, 31, 33, 4099, 64001])
 def test_weight_and_bias_gradients_match_fp64(rows, in_features, out_features):
     from torchgt_b200.linear import wgrad
@@ -49,7 +50,7 @@ def test_linear_module_matches_nn_linear_and_keeps_its_state_dict():
 def test_linear_falls_back_to_torch_for_what_the_kernel_does_not_cover():
     from torchgt_b200.linear import Linear
     torch.manual_seed(4)
-    for mod, x in ((Linear(64, 40).cuda(), torch.randn(9, 64).cuda()),               # 40 outputs
+    for mod, x in ((Linear(64, 42).cuda(), torch.randn(9, 64).cuda()),               # 42 outputs
                    (Linear(24, 64).cuda(), torch.randn(9, 24).cuda()),               # 24 inputs
                    (Linear(64, 64).cuda().double(), torch.randn(9, 64).cuda().double()),
                    (Linear(64, 64, bias=False).cuda(), torch.randn(9, 64).cuda())):
@@ -68,5 +69,6 @@ def test_linear_wgrad_argument_errors_come_back_as_codes():
     t = torch.randn(8, 64).cuda()
     nb = ctypes.c_size_t()
     assert lib.tgt_linear_wgrad_scratch_bytes(8, 40, 64, ctypes.byref(nb)) == 3       # TGT_ERR_UNSUPPORTED
+    assert lib.tgt_linear_wgrad_scratch_bytes(8, 64, 42, ctypes.byref(nb)) == 3
     assert lib.tgt_linear_wgrad(t.data_ptr(), t.data_ptr(), 8, 64, 64, None, None, None, 0, None) == 1   # INVALID
     assert lib.tgt_linear_wgrad(t.data_ptr(), t.data_ptr(), 8, 64, 64, t.data_ptr(), None, None, 0, None) == 4   # WORKSPACE

@@ -56,7 +56,8 @@ __global__ void __launch_bounds__(kWgThreads) linear_wgrad_kernel(const WgradPar
       const int64_t row = chunk * kWgChunk + r;
       const bool live = row < p.rows;
       const int64_t from = live ? row : 0;
-      copy_async_16(&s_dy[buf][r][4 * c4], p.dy + from * p.out + o0 + 4 * c4, live ? 16 : 0);
+      const bool col = o0 + 4 * c4 < p.out;          // the last tile of outputs may be narrower than 64
+      copy_async_16(&s_dy[buf][r][4 * c4], p.dy + from * p.out + (col ? o0 + 4 * c4 : 0), live && col ? 16 : 0);
       copy_async_16(&s_x[buf][r][4 * c4], p.x + from * p.in + i0 + 4 * c4, live ? 16 : 0);
     }
   };
@@ -92,10 +93,11 @@ __global__ void __launch_bounds__(kWgThreads) linear_wgrad_kernel(const WgradPar
 #pragma unroll
   for (int a = 0; a < 8; ++a) {
     const int o = o0 + (a < 4 ? 4 * ty + a : 32 + 4 * ty + a - 4);
+    if (o >= p.out) continue;
     *reinterpret_cast<float4*>(out + int64_t(o) * p.in + i0 + 4 * tx) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
     *reinterpret_cast<float4*>(out + int64_t(o) * p.in + i0 + 32 + 4 * tx) = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
   }
-  if (i0 == 0) out[int64_t(p.out) * p.in + o0 + tid] = bias_acc;
+  if (i0 == 0 && o0 + tid < p.out) out[int64_t(p.out) * p.in + o0 + tid] = bias_acc;
 }
 
 // dw[j] = sum over CTAs of partial[cta][j], db likewise (db may be null); sum_partials: fixed association.
@@ -113,12 +115,15 @@ __global__ void __launch_bounds__(kPartialSumThreads) linear_wgrad_sum_kernel(co
   }
 }
 
+// inputs in whole tiles of 64; outputs any multiple of 4 (a classifier head of 40 classes, say): the last tile
+// of outputs is padded with zero columns that are never stored
 bool wgrad_supported(int in, int out) {
-  return in >= kWgTile && out >= kWgTile && in % kWgTile == 0 && out % kWgTile == 0 && in <= 1024 && out <= 1024;
+  return in >= kWgTile && in % kWgTile == 0 && in <= 1024 && out >= 4 && out % 4 == 0 && out <= 1024;
 }
+int wgrad_out_tiles(int out) { return (out + kWgTile - 1) / kWgTile; }
 
 int wgrad_grid(int64_t rows, int in, int out) {
-  const int tiles = (in / kWgTile) * (out / kWgTile);
+  const int tiles = (in / kWgTile) * wgrad_out_tiles(out);
   const int64_t chunks = (rows + kWgChunk - 1) / kWgChunk;
   int64_t g = int64_t(sm_count()) * 4 / tiles;     // about four CTAs (of two warps) per SM over all tiles
   if (g < 1) g = 1;
@@ -134,7 +139,7 @@ extern "C" int tgt_linear_wgrad_scratch_bytes(int64_t rows, int in_features, int
   TGT_CHECK_ARG(bytes != nullptr, "bytes is null");
   TGT_CHECK_ARG(rows >= 0, "rows must be >= 0");
   if (!wgrad_supported(in_features, out_features))
-    return set_error(TGT_ERR_UNSUPPORTED, "in_features=%d out_features=%d: both must be multiples of 64, at most 1024",
+    return set_error(TGT_ERR_UNSUPPORTED, "in_features=%d out_features=%d: in_features must be a multiple of 64, out_features of 4, both at most 1024",
                      in_features, out_features);
   *bytes = size_t(wgrad_grid(rows, in_features, out_features)) *
            (size_t(in_features) * out_features + out_features) * sizeof(float);
@@ -147,7 +152,7 @@ extern "C" int tgt_linear_wgrad(const float* dy, const float* x, int64_t rows, i
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   TGT_CHECK_ARG(rows >= 0, "rows must be >= 0");
   if (!wgrad_supported(in_features, out_features))
-    return set_error(TGT_ERR_UNSUPPORTED, "in_features=%d out_features=%d: both must be multiples of 64, at most 1024",
+    return set_error(TGT_ERR_UNSUPPORTED, "in_features=%d out_features=%d: in_features must be a multiple of 64, out_features of 4, both at most 1024",
                      in_features, out_features);
   TGT_CHECK_ARG(dw != nullptr, "dw must not be null");
   const size_t n_w = size_t(in_features) * out_features;
@@ -163,7 +168,7 @@ extern "C" int tgt_linear_wgrad(const float* dy, const float* x, int64_t rows, i
   if (scratch == nullptr || scratch_bytes < need)
     return set_error(TGT_ERR_WORKSPACE, "scratch holds %zu bytes, %zu needed", scratch_bytes, need);
   WgradParams p{dy, x, static_cast<float*>(scratch), rows, in_features, out_features};
-  const dim3 g(grid, (in_features / kWgTile) * (out_features / kWgTile));
+  const dim3 g(grid, (in_features / kWgTile) * wgrad_out_tiles(out_features));
   linear_wgrad_kernel<<<g, kWgThreads, 0, stream>>>(p);
   const int n = int(n_w) + out_features;
   linear_wgrad_sum_kernel<<<(n + 31) / 32, kPartialSumThreads, 0, stream>>>(p.partial, grid, int(n_w), out_features, dw, db);

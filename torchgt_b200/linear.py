@@ -2,8 +2,8 @@
 weight and bias gradients from ``csrc/linear_wgrad.cu`` when the layer is narrow and the rows are many (the
 models' 64 x 64 projections and FFN layers over 64,000 to 870,000 rows: a product with a 64 x 64 result and a
 reduction over every row, which a library GEMM runs on a few CTAs).  The forward product and the input
-gradient stay library GEMMs; CPU tensors, other dtypes and sizes that are not multiples of 64 take
-``torch.nn.functional.linear`` end to end."""
+gradient stay library GEMMs; CPU tensors, other dtypes, inputs that are not a multiple of 64 wide and outputs
+that are not a multiple of 4 wide take ``torch.nn.functional.linear`` end to end."""
 from __future__ import annotations
 
 import ctypes
@@ -17,8 +17,8 @@ _scratch_bytes: dict = {}
 
 
 def supported(x: torch.Tensor, in_features: int, out_features: int) -> bool:
-    return (x.is_cuda and x.dtype == torch.float32 and in_features % 64 == 0 and out_features % 64 == 0 and
-            64 <= in_features <= 1024 and 64 <= out_features <= 1024)
+    return (x.is_cuda and x.dtype == torch.float32 and in_features % 64 == 0 and out_features % 4 == 0 and
+            64 <= in_features <= 1024 and 4 <= out_features <= 1024)
 
 
 def wgrad(dy: torch.Tensor, x: torch.Tensor, with_bias: bool = True):
