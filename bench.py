@@ -18,6 +18,13 @@ N > 1   One process per GPU under torchrun.  Weak scaling of the Ulysses layer: 
 
 ``--impl reference`` times the reference's own CPU implementation of the path (its PyTorch operation
 sequence restated in oracle/, all host threads) on the same workload, rank 0 only.
+
+Further legs of the default run: ``more_workloads`` (64K bf16, 870K fp32 / bf16; ``TGT_BENCH_MORE=0`` skips),
+``epoch`` (the reference's training epoch; ``TGT_BENCH_EPOCH=0`` skips it and, at N > 1, the
+``weak_scaling_training_step`` leg), at N > 1 also the parity self-check, ``attention_only``, ``exchange_only``.
+``TGT_BENCH_KERNEL_LIST=1`` (N > 1) adds the device time of every kernel of the replayed step on rank 0;
+``--workload 870k`` (N = 1) makes the long-sequence batch the headline; ``--profile`` keeps the run short for
+profilers.
 """
 from __future__ import annotations
 
