@@ -86,3 +86,27 @@ def test_layer_norm_argument_errors_come_back_as_codes():
                                   None) == 3
     assert lib.tgt_layer_norm_bwd(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 4, 64, x.data_ptr(),
                                   x.data_ptr(), x.data_ptr(), None, 0, None) == 4
+
+
+def test_layer_norm_and_linear_accept_views_that_start_off_a_16_byte_boundary():
+    """A contiguous view four bytes into its storage cannot be read 16 bytes at a time: the modules copy it."""
+    from torchgt_b200.layer_norm import LayerNorm
+    from torchgt_b200.linear import Linear
+    torch.manual_seed(9)
+    rows = 300
+    flat = torch.randn(rows * 64 + 1, device="cuda")
+    x = flat[1:].view(rows, 64)
+    assert x.data_ptr() % 16 != 0 and x.is_contiguous()
+    ln, lin = LayerNorm(64).cuda(), Linear(64, 64).cuda()
+    xa = x.detach().requires_grad_()
+    y = lin(ln(xa))
+    gflat = torch.randn(rows * 64 + 1, device="cuda")
+    y.backward(gflat[1:].view(rows, 64))
+    xd = x.detach().double().requires_grad_()
+    ref = torch.nn.functional.linear(
+        torch.nn.functional.layer_norm(xd, (64,), ln.weight.double(), ln.bias.double(), ln.eps),
+        lin.weight.double(), lin.bias.double())
+    ref.backward(gflat[1:].view(rows, 64).double())
+    tol = 2e-3 if torch.backends.cuda.matmul.allow_tf32 else 1e-5
+    assert _close(y, ref.detach().cpu(), tol)[0]
+    assert _close(xa.grad, xd.grad.cpu(), tol)[0]

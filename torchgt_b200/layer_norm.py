@@ -58,11 +58,17 @@ def backward(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, stats: tor
     return dx, dgamma, dbeta
 
 
+def _aligned(t: torch.Tensor) -> torch.Tensor:
+    """Contiguous ``t``, copied when it is a view that starts off a 16-byte boundary (the kernels move 16 bytes
+    at a time)."""
+    t = t.contiguous()
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, eps):
-        x = x.contiguous()
-        weight, bias = weight.contiguous(), bias.contiguous()
+        x, weight, bias = _aligned(x), _aligned(weight), _aligned(bias)
         y, stats = forward_with_stats(x, weight, bias, eps)
         ctx.save_for_backward(x, weight, stats)
         return y
@@ -70,7 +76,7 @@ class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, weight, stats = ctx.saved_tensors
-        dx, dgamma, dbeta = backward(dy.contiguous(), x, weight, stats)
+        dx, dgamma, dbeta = backward(_aligned(dy), x, weight, stats)
         return dx, dgamma, dbeta, None
 
 

@@ -21,8 +21,15 @@ def supported(x: torch.Tensor, in_features: int, out_features: int) -> bool:
             64 <= in_features <= 1024 and 4 <= out_features <= 1024)
 
 
+def _aligned(t: torch.Tensor) -> torch.Tensor:
+    """``t`` itself, or a copy when it is a view that starts off a 16-byte boundary (the kernels load 16 bytes
+    at a time)."""
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
 def wgrad(dy: torch.Tensor, x: torch.Tensor, with_bias: bool = True):
     """``dy.t() @ x`` and ``dy.sum(0)`` for contiguous fp32 ``dy`` [rows, out] and ``x`` [rows, in] on a GPU."""
+    dy, x = _aligned(dy), _aligned(x)
     rows, out_features = dy.shape
     in_features = x.shape[1]
     key = (rows, in_features, out_features)
